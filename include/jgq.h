@@ -1,0 +1,121 @@
+/*
+ * jgq.h - C ABI of the B200 (sm_100a) GPTQ / packed-int4 hot path.
+ *
+ * One shared library (libjgq.so) exports the plain-C entry points below.  They
+ * are what a foreign-function binding of the reference's hot path binds: each
+ * one replaces a piece of jax_gptq/gptq.py or the Triton launch in
+ * jax_gptq/op.py:46-63 (citations are paths inside the reference project).
+ *
+ * Conventions shared by every entry point
+ *   - all pointers are DEVICE pointers unless the name says "host";
+ *   - `stream` is a cudaStream_t passed as void*; the call only enqueues work on
+ *     it, never synchronises and never allocates.  Scratch memory is supplied by
+ *     the caller (`ws`, `ws_bytes`; size from the matching *_workspace_bytes);
+ *   - return value 0 = enqueued, negative = host-side validation error, nothing
+ *     was launched; jgq_last_error() returns the thread-local message;
+ *   - device-side conditions (non-positive pivot / NaN in the Cholesky) are
+ *     written to a caller-supplied int32 status word in device memory;
+ *   - matrices are dense row-major.  W is (K, N): K = contraction / input
+ *     features, N = output channels.  Packed weights hold two 4-bit codes per
+ *     byte along the contraction axis, low nibble = even index (gptq.py:246-247).
+ */
+#ifndef JGQ_H_
+#define JGQ_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* element types of activations / outputs */
+enum { JGQ_F32 = 0, JGQ_F16 = 1, JGQ_BF16 = 2, JGQ_U8 = 3, JGQ_I32 = 4 };
+
+/* error codes (negative returns) */
+enum {
+  JGQ_OK = 0,
+  JGQ_ERR_ARG = -1,        /* bad shape / dtype / null pointer          */
+  JGQ_ERR_ALIGN = -2,      /* pointer alignment requirement not met     */
+  JGQ_ERR_WORKSPACE = -3,  /* workspace too small                       */
+  JGQ_ERR_CUDA = -4,       /* a CUDA runtime call failed at enqueue     */
+  JGQ_ERR_LIMIT = -5       /* size beyond a documented maximum          */
+};
+
+/* bits of the device status word */
+enum { JGQ_STATUS_NOT_PD = 1, JGQ_STATUS_NAN = 2, JGQ_STATUS_TIMEOUT = 4 };
+
+int jgq_version(void);
+const char* jgq_last_error(void);
+
+/* ---- int4 pack / unpack ---------------------------------------------------
+ * The array is viewed as (outer, axis_len, inner) with the packed axis in the
+ * middle, which covers packing along any axis of an N-D array.
+ * Replaces _pack/_unpack + pack_along_axis/unpack_along_axis
+ * (gptq.py:237-263, 265-292).  `codes_dtype` is JGQ_U8 or JGQ_I32. */
+int jgq_pack_int4(const void* codes, int codes_dtype, uint8_t* packed,
+                  int64_t outer, int64_t axis_len, int64_t inner, void* stream);
+int jgq_unpack_int4(const uint8_t* packed, uint8_t* codes,
+                    int64_t outer, int64_t packed_len, int64_t inner, void* stream);
+
+/* pack_matrix (gptq.py:214-228): codes = round(Q/scale + zero) -> uint8 -> packed.
+ * Q is (outer, axis_len, inner) of q_dtype (F32/F16/BF16); scale and zero are
+ * fp32 arrays of shape (outer, inner). */
+int jgq_pack_matrix(const void* Q, int q_dtype, const float* scale, const float* zero,
+                    uint8_t* packed, int64_t outer, int64_t axis_len, int64_t inner,
+                    void* stream);
+/* unpack_matrix (gptq.py:230-235): out = (code - zero) * scale, out_dtype F32/F16/BF16. */
+int jgq_unpack_matrix(const uint8_t* packed, const float* zero, const float* scale,
+                      void* out, int out_dtype, int64_t outer, int64_t packed_len,
+                      int64_t inner, void* stream);
+
+/* ---- per-output-channel scale / zero (gptq.py:105-118) --------------------
+ * W is (K, N) fp32; scale, zero are fp32[N]; maxq = 2^bits - 1. */
+int jgq_col_params(const float* W, int64_t K, int64_t N, int maxq,
+                   float* scale, float* zero, void* stream);
+
+/* ---- Hessian accumulation (gptq.py:57-103) --------------------------------
+ * H (K x K fp32, lower triangle significant until finalize) += X^T X for one
+ * calibration batch X of n rows (x_dtype F32/F16/BF16, row-major n x K).
+ * jgq_hessian_finalize divides by the total sample count and mirrors the
+ * lower triangle, giving (1/n) sum x x^T, which accumulate_H returns. */
+size_t jgq_hessian_workspace_bytes(int64_t n, int64_t K, int x_dtype);
+int jgq_hessian_accum(const void* X, int x_dtype, int64_t n, int64_t K, float* H,
+                      void* ws, size_t ws_bytes, void* stream);
+int jgq_hessian_finalize(float* H, int64_t K, double n_total, void* stream);
+
+/* ---- damping + Cholesky factor of the inverse (gptq.py:44-48, 155-168) ----
+ * In: W (K x N fp32, rows of dead features are zeroed in place), H (K x K fp32,
+ * destroyed).  Out: L (K x K fp32, lower, L L^T = (H + damp)^-1, upper = 0),
+ * *dev_status |= JGQ_STATUS_NOT_PD / JGQ_STATUS_NAN (mirrors any_nan). */
+size_t jgq_damp_invert_workspace_bytes(int64_t K);
+int jgq_damp_invert(float* W, int64_t N, float* H, int64_t K, float damping, float* L,
+                    void* ws, size_t ws_bytes, int32_t* dev_status, void* stream);
+
+/* ---- blocked quantize + error propagation (gptq.py:120-153, 199-208) ------
+ * In: W (K x N fp32, destroyed), L from jgq_damp_invert, scale/zero fp32[N].
+ * Out: Q (K x N of q_dtype: dequantised values, what gptq() returns) and,
+ * when `codes` is non-null, the integer codes (K x N uint8).
+ * K must be a multiple of block_size (the reference slices fixed-size blocks,
+ * gptq.py:132-133); block_size <= 128. */
+size_t jgq_gptq_quantize_workspace_bytes(int64_t K, int64_t N, int block_size);
+int jgq_gptq_quantize(float* W, const float* L, const float* scale, const float* zero,
+                      int64_t K, int64_t N, int block_size, int maxq,
+                      void* Q, int q_dtype, uint8_t* codes,
+                      void* ws, size_t ws_bytes, void* stream);
+
+/* ---- packed-int4 matmul (op.py:21-69, kernel.py:17-127 and :142-253) ------
+ * forward:      out[M, N]  = x[M, K]  @ dequant(packed[K/2, N])
+ * transpose_b:  out[M, K]  = x[M, N]  @ dequant(packed[K/2, N])^T
+ * x and out share x_dtype (F32/F16/BF16); zero/scale have zs_dtype (F32/F16),
+ * one entry per output channel n.  Accumulation is fp32. */
+size_t jgq_w4_matmul_workspace_bytes(int64_t M, int64_t N, int64_t K, int transpose_b);
+int jgq_w4_matmul(const void* x, int x_dtype, const uint8_t* packed,
+                  const void* zero, const void* scale, int zs_dtype,
+                  void* out, int64_t M, int64_t N, int64_t K, int transpose_b,
+                  void* ws, size_t ws_bytes, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* JGQ_H_ */

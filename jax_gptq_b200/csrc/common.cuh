@@ -1,0 +1,61 @@
+// Shared host/device helpers for the jgq kernels (sm_100a only).
+#pragma once
+#include <cuda_runtime.h>
+#include <cuda_fp16.h>
+#include <cuda_bf16.h>
+#include <stdint.h>
+#include <stdio.h>
+#include <stdarg.h>
+#include "../../include/jgq.h"
+
+namespace jgq {
+
+// Thread-local message returned by jgq_last_error().
+char* error_buffer();
+
+inline int fail(int code, const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(error_buffer(), 512, fmt, ap);
+  va_end(ap);
+  return code;
+}
+
+#define JGQ_REQUIRE(cond, code, ...) \
+  do { if (!(cond)) return ::jgq::fail((code), __VA_ARGS__); } while (0)
+
+// Called after each launch: reports (and clears) a launch-configuration error.
+inline int check_launch(const char* what) {
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return fail(JGQ_ERR_CUDA, "%s: %s", what, cudaGetErrorString(e));
+  return JGQ_OK;
+}
+
+inline bool aligned(const void* p, size_t a) { return (reinterpret_cast<uintptr_t>(p) % a) == 0; }
+inline int64_t cdiv(int64_t a, int64_t b) { return (a + b - 1) / b; }
+inline size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
+
+inline int dtype_size(int dt) {
+  switch (dt) {
+    case JGQ_F32: case JGQ_I32: return 4;
+    case JGQ_F16: case JGQ_BF16: return 2;
+    case JGQ_U8: return 1;
+    default: return 0;
+  }
+}
+
+// Number of SMs of the current device (cached per device index).
+int sm_count();
+
+// ---- typed load/store used by kernels templated on the element type ----
+template <typename T> __device__ __forceinline__ float to_f32(T v);
+template <> __device__ __forceinline__ float to_f32<float>(float v) { return v; }
+template <> __device__ __forceinline__ float to_f32<__half>(__half v) { return __half2float(v); }
+template <> __device__ __forceinline__ float to_f32<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }
+
+template <typename T> __device__ __forceinline__ T from_f32(float v);
+template <> __device__ __forceinline__ float from_f32<float>(float v) { return v; }
+template <> __device__ __forceinline__ __half from_f32<__half>(float v) { return __float2half_rn(v); }
+template <> __device__ __forceinline__ __nv_bfloat16 from_f32<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
+
+}  // namespace jgq

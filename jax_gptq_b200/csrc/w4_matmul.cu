@@ -1,0 +1,455 @@
+// Packed-int4 dequant matmul (reference op.py:21-69, kernel.py:17-127 / :142-253).
+//
+//   forward:      out[M, N] = x[M, K] @ ((code[K, N] - zero[N]) * scale[N])
+//   transpose_b:  out[M, K] = x[M, N] @ ((code[K, N] - zero[N]) * scale[N])^T
+//
+// packed[K/2, N] holds code[2j, n] in the low and code[2j+1, n] in the high
+// nibble of byte (j, n).
+//
+// Forward kernel.  Scale and zero depend on the output channel only, so they
+// leave the contraction loop:
+//     out[m, n] = scale[n] * ( sum_k x[m,k] code[k,n]  -  zero[n] * sum_k x[m,k] ).
+// The loop therefore streams raw codes.  At decode-sized M the kernel is
+// HBM-bound (one pass over K*N/2 bytes); the multiply-adds are handed to the
+// tensor pipe (mma.sync m16n8k16, fp32 accumulate) so that the issue slots go
+// to the loads and the nibble expansion.  A byte already holds the two
+// consecutive-k codes an MMA B-fragment register wants, so a thread's 16-byte
+// load (16 channels of one byte row) feeds 16 MMAs without any shuffle:
+// lane (g, q) loads byte rows j0+q and j0+4+q of channels 16g..16g+15, and MMA
+// number b uses byte b of both, which makes n-slot g of MMA b channel 16g+b.
+// sum_k x[m,k] comes from one more MMA against a fragment of ones.
+//
+// A CTA is 4 warps on one 128-channel group; the warps interleave over the
+// CTA's slice of the contraction range and are reduced through shared memory.
+// Slices of different CTAs (split-K, needed to occupy 148 SMs when N is small)
+// are written to the workspace; the CTA that takes the last ticket of a
+// channel group adds the slices in slice order and writes the result.
+#include "common.cuh"
+#include <type_traits>
+#include <algorithm>
+
+namespace jgq {
+
+constexpr int WCOLS = 128;          // channels per CTA
+constexpr int WWARPS = 4;
+constexpr int PSTRIDE = WCOLS + 4;  // floats per partial row: 128 sums + sum_k x (+pad)
+
+template <typename XT> struct MmaType;
+template <> struct MmaType<__half> {
+  static constexpr uint32_t kMagic = 0x64006400u;  // 1024 | code
+  __device__ static __forceinline__ uint32_t expand(uint32_t v) {
+    uint32_t r = (v & 0x000F000Fu) | kMagic;
+    __half2 h = __hsub2(*reinterpret_cast<__half2*>(&r), __half2half2(__float2half_rn(1024.f)));
+    return *reinterpret_cast<uint32_t*>(&h);
+  }
+  __device__ static __forceinline__ uint32_t ones() { return 0x3C003C00u; }
+  __device__ static __forceinline__ void mma(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+                 : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+  }
+};
+template <> struct MmaType<__nv_bfloat16> {
+  static constexpr uint32_t kMagic = 0x43004300u;  // 128 | code
+  __device__ static __forceinline__ uint32_t expand(uint32_t v) {
+    uint32_t r = (v & 0x000F000Fu) | kMagic;
+    __nv_bfloat162 h = __hsub2(*reinterpret_cast<__nv_bfloat162*>(&r), __float2bfloat162_rn(128.f));
+    return *reinterpret_cast<uint32_t*>(&h);
+  }
+  __device__ static __forceinline__ uint32_t ones() { return 0x3F803F80u; }
+  __device__ static __forceinline__ void mma(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+                 : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+  }
+};
+
+// 16 packed bytes of byte row `row`, channels c0..c0+15 (zero outside the matrix).
+__device__ __forceinline__ uint4 load_codes16(const uint8_t* __restrict__ packed, int64_t row, int64_t KB,
+                                              int64_t c0, int64_t N, bool vec) {
+  uint4 r = make_uint4(0, 0, 0, 0);
+  if (row >= KB || c0 >= N) return r;
+  const uint8_t* p = packed + row * N + c0;
+  if (vec && c0 + 15 < N) {
+    r = __ldg(reinterpret_cast<const uint4*>(p));
+  } else {
+    uint32_t w[4] = {0, 0, 0, 0};
+    for (int b = 0; b < 16; ++b)
+      if (c0 + b < N) w[b >> 2] |= (uint32_t)p[b] << (8 * (b & 3));
+    r = make_uint4(w[0], w[1], w[2], w[3]);
+  }
+  return r;
+}
+
+// Two consecutive activations x[m, k], x[m, k+1] as one MMA operand register (zero outside).
+template <typename XT>
+__device__ __forceinline__ uint32_t load_x2(const XT* __restrict__ x, int64_t m, int64_t M, int64_t k, int64_t K) {
+  if (m >= M || k >= K) return 0u;      // K is even and k is even: k+1 < K as well
+  return *reinterpret_cast<const uint32_t*>(x + m * K + k);
+}
+
+// fp32 activations: split into bf16 high and low parts (x = hi + lo + O(2^-17 |x|)).
+__device__ __forceinline__ void load_x2_split(const float* __restrict__ x, int64_t m, int64_t M, int64_t k, int64_t K,
+                                              uint32_t& hi, uint32_t& lo) {
+  hi = 0u; lo = 0u;
+  if (m >= M || k >= K) return;
+  const float2 v = *reinterpret_cast<const float2*>(x + m * K + k);
+  const __nv_bfloat16 h0 = __float2bfloat16_rn(v.x), h1 = __float2bfloat16_rn(v.y);
+  const __nv_bfloat16 l0 = __float2bfloat16_rn(v.x - __bfloat162float(h0));
+  const __nv_bfloat16 l1 = __float2bfloat16_rn(v.y - __bfloat162float(h1));
+  hi = (uint32_t)__bfloat16_as_ushort(h0) | ((uint32_t)__bfloat16_as_ushort(h1) << 16);
+  lo = (uint32_t)__bfloat16_as_ushort(l0) | ((uint32_t)__bfloat16_as_ushort(l1) << 16);
+}
+
+template <typename T> __device__ __forceinline__ float zs_to_f32(const void* p, int64_t i);
+template <> __device__ __forceinline__ float zs_to_f32<float>(const void* p, int64_t i) { return ((const float*)p)[i]; }
+template <> __device__ __forceinline__ float zs_to_f32<__half>(const void* p, int64_t i) { return __half2float(((const __half*)p)[i]); }
+
+// XT: activation/output element type.  MT: 16-row tiles per CTA.
+// CT: MMA operand type (XT itself for f16/bf16, bf16 for fp32 activations).
+template <typename XT, typename CT, int MT, typename ZST>
+__global__ void __launch_bounds__(WWARPS * 32)
+w4_fwd_kernel(const XT* __restrict__ x, const uint8_t* __restrict__ packed,
+              const void* __restrict__ zero, const void* __restrict__ scale,
+              XT* __restrict__ out, int64_t M, int64_t N, int64_t K,
+              int steps_per_split, int ksplit, float* __restrict__ partials, int* __restrict__ tickets,
+              int vec) {
+  constexpr bool kSplitX = std::is_same<XT, float>::value;
+  constexpr int ROWS = 16 * MT;
+  __shared__ __align__(16) float red[ROWS][PSTRIDE];
+  __shared__ int s_last;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int g = lane >> 2, q = lane & 3;
+  const int cg = blockIdx.x, split = blockIdx.y, mtile = blockIdx.z;
+  const int ncg = gridDim.x;
+  const int64_t KB = K / 2;
+  const int64_t cbase = (int64_t)cg * WCOLS;
+  const int64_t m0 = (int64_t)mtile * ROWS;
+  const int64_t total_steps = (KB + 7) / 8;
+  const int64_t step_begin = (int64_t)split * steps_per_split;
+  const int64_t step_end = min(total_steps, step_begin + steps_per_split);
+
+  float acc[MT][16][4];
+  float accx[MT][4];
+#pragma unroll
+  for (int t = 0; t < MT; ++t) {
+#pragma unroll
+    for (int b = 0; b < 16; ++b)
+#pragma unroll
+      for (int i = 0; i < 4; ++i) acc[t][b][i] = 0.f;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) accx[t][i] = 0.f;
+  }
+
+  const int64_t c0 = cbase + 16 * g;
+  for (int64_t step = step_begin + warp; step < step_end; step += WWARPS) {
+    const int64_t j0 = step * 8;
+    const uint4 r0 = load_codes16(packed, j0 + q, KB, c0, N, vec);
+    const uint4 r1 = load_codes16(packed, j0 + 4 + q, KB, c0, N, vec);
+    const int64_t k0 = 2 * j0;
+    uint32_t a[MT][4], alo[MT][4];
+#pragma unroll
+    for (int t = 0; t < MT; ++t) {
+      const int64_t ma = m0 + 16 * t + g, mb = ma + 8;
+      if (kSplitX) {
+        load_x2_split((const float*)x, ma, M, k0 + 2 * q, K, a[t][0], alo[t][0]);
+        load_x2_split((const float*)x, mb, M, k0 + 2 * q, K, a[t][1], alo[t][1]);
+        load_x2_split((const float*)x, ma, M, k0 + 8 + 2 * q, K, a[t][2], alo[t][2]);
+        load_x2_split((const float*)x, mb, M, k0 + 8 + 2 * q, K, a[t][3], alo[t][3]);
+      } else {
+        a[t][0] = load_x2<XT>(x, ma, M, k0 + 2 * q, K);
+        a[t][1] = load_x2<XT>(x, mb, M, k0 + 2 * q, K);
+        a[t][2] = load_x2<XT>(x, ma, M, k0 + 8 + 2 * q, K);
+        a[t][3] = load_x2<XT>(x, mb, M, k0 + 8 + 2 * q, K);
+      }
+    }
+    const uint32_t w0[4] = {r0.x, r0.y, r0.z, r0.w};
+    const uint32_t w1[4] = {r1.x, r1.y, r1.z, r1.w};
+#pragma unroll
+    for (int wi = 0; wi < 4; ++wi) {
+      const uint32_t u0 = w0[wi], u0s = u0 >> 4, u1 = w1[wi], u1s = u1 >> 4;
+#pragma unroll
+      for (int bi = 0; bi < 4; ++bi) {
+        const uint32_t sel = (uint32_t)bi | ((uint32_t)bi << 4) | ((uint32_t)(4 + bi) << 8) | ((uint32_t)(4 + bi) << 12);
+        const uint32_t b0 = MmaType<CT>::expand(__byte_perm(u0, u0s, sel));
+        const uint32_t b1 = MmaType<CT>::expand(__byte_perm(u1, u1s, sel));
+#pragma unroll
+        for (int t = 0; t < MT; ++t) {
+          MmaType<CT>::mma(acc[t][wi * 4 + bi], a[t], b0, b1);
+          if (kSplitX) MmaType<CT>::mma(acc[t][wi * 4 + bi], alo[t], b0, b1);
+        }
+      }
+    }
+#pragma unroll
+    for (int t = 0; t < MT; ++t) {
+      MmaType<CT>::mma(accx[t], a[t], MmaType<CT>::ones(), MmaType<CT>::ones());
+      if (kSplitX) MmaType<CT>::mma(accx[t], alo[t], MmaType<CT>::ones(), MmaType<CT>::ones());
+    }
+  }
+
+  // ---- reduce the 4 warps into warp 0 through shared memory --------------------
+  // fragment element (t, b, i): row 16t + g + 8*(i>>1), channel 32q + 16*(i&1) + b
+  for (int w = 1; w < WWARPS; ++w) {
+    if (warp == w) {
+#pragma unroll
+      for (int t = 0; t < MT; ++t) {
+#pragma unroll
+        for (int b = 0; b < 16; ++b)
+#pragma unroll
+          for (int i = 0; i < 4; ++i)
+            red[16 * t + g + 8 * (i >> 1)][32 * q + 16 * (i & 1) + b] = acc[t][b][i];
+        if (q == 0) { red[16 * t + g][WCOLS] = accx[t][0]; red[16 * t + g + 8][WCOLS] = accx[t][2]; }
+      }
+    }
+    __syncthreads();
+    if (warp == 0) {
+#pragma unroll
+      for (int t = 0; t < MT; ++t) {
+#pragma unroll
+        for (int b = 0; b < 16; ++b)
+#pragma unroll
+          for (int i = 0; i < 4; ++i)
+            acc[t][b][i] += red[16 * t + g + 8 * (i >> 1)][32 * q + 16 * (i & 1) + b];
+        accx[t][0] += red[16 * t + g][WCOLS];
+        accx[t][2] += red[16 * t + g + 8][WCOLS];
+      }
+    }
+    __syncthreads();
+  }
+
+  // ---- split-K: publish this CTA's slice, last ticket holder sums all slices ----
+  if (ksplit > 1) {
+    if (warp == 0) {
+#pragma unroll
+      for (int t = 0; t < MT; ++t)
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          const int64_t m = m0 + 16 * t + g + 8 * h;
+          if (m < M) {
+            float* dst = partials + (((int64_t)split * M + m) * ncg + cg) * PSTRIDE;
+#pragma unroll
+            for (int i = 0; i < 2; ++i)
+#pragma unroll
+              for (int b4 = 0; b4 < 4; ++b4)
+                *reinterpret_cast<float4*>(dst + 32 * q + 16 * i + 4 * b4) =
+                    make_float4(acc[t][4 * b4 + 0][2 * h + i], acc[t][4 * b4 + 1][2 * h + i],
+                                acc[t][4 * b4 + 2][2 * h + i], acc[t][4 * b4 + 3][2 * h + i]);
+            if (q == 0) dst[WCOLS] = accx[t][2 * h];
+          }
+        }
+      __threadfence();
+      __syncwarp();
+      if (lane == 0) {
+        const int old = atomicAdd(&tickets[mtile * ncg + cg], 1);
+        s_last = (old == ksplit - 1);
+      }
+    }
+    __syncthreads();
+    if (!s_last) return;
+    if (warp != 0) return;
+    __threadfence();
+#pragma unroll
+    for (int t = 0; t < MT; ++t)
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        const int64_t m = m0 + 16 * t + g + 8 * h;
+#pragma unroll
+        for (int b = 0; b < 16; ++b) { acc[t][b][2 * h] = 0.f; acc[t][b][2 * h + 1] = 0.f; }
+        float xs = 0.f;
+        if (m < M) {
+          for (int z = 0; z < ksplit; ++z) {
+            const float* src = partials + (((int64_t)z * M + m) * ncg + cg) * PSTRIDE;
+#pragma unroll
+            for (int i = 0; i < 2; ++i)
+#pragma unroll
+              for (int b4 = 0; b4 < 4; ++b4) {
+                const float4 v = __ldcg(reinterpret_cast<const float4*>(src + 32 * q + 16 * i + 4 * b4));
+                acc[t][4 * b4 + 0][2 * h + i] += v.x; acc[t][4 * b4 + 1][2 * h + i] += v.y;
+                acc[t][4 * b4 + 2][2 * h + i] += v.z; acc[t][4 * b4 + 3][2 * h + i] += v.w;
+              }
+            xs += __ldcg(src + WCOLS);
+          }
+        }
+        accx[t][2 * h] = xs;
+      }
+    if (lane == 0) tickets[mtile * ncg + cg] = 0;   // ready for the next launch
+  } else {
+    if (warp != 0) return;
+    // sum_k x is identical in every n-slot; take it from this lane's own fragment
+  }
+
+  // ---- epilogue (warp 0): out = scale * (acc - zero * sum_k x) -------------------
+  // all lanes of a quad hold the same rows; accx[t][0] / [2] are rows g / g+8 (valid in every lane)
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    const int64_t ccol = cbase + 32 * q + 16 * i;
+#pragma unroll
+    for (int b = 0; b < 16; ++b) {
+      const int64_t n = ccol + b;
+      if (n >= N) continue;
+      const float s = zs_to_f32<ZST>(scale, n), z = zs_to_f32<ZST>(zero, n);
+#pragma unroll
+      for (int t = 0; t < MT; ++t)
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          const int64_t m = m0 + 16 * t + g + 8 * h;
+          if (m < M) out[m * N + n] = from_f32<XT>(s * (acc[t][b][2 * h + i] - z * accx[t][2 * h]));
+        }
+    }
+  }
+}
+
+// ---- transpose_b: out[m, kk] = sum_n x[m, n] * (code[kk, n] - zero[n]) * scale[n] ------
+// fp32 FFMA tile kernel (64 x 64 outputs, 32-channel contraction slices); the
+// dequantised values are formed exactly as the reference kernel does
+// ((code - zero) * scale in fp32, kernel.py:216-217).
+template <typename XT, typename ZST>
+__global__ void __launch_bounds__(256)
+w4_tb_kernel(const XT* __restrict__ x, const uint8_t* __restrict__ packed,
+             const void* __restrict__ zero, const void* __restrict__ scale,
+             XT* __restrict__ out, int64_t M, int64_t N, int64_t K) {
+  __shared__ float xs[32][64 + 1];   // [n][m]
+  __shared__ float ws[32][64 + 1];   // [n][kk]
+  const int64_t m0 = (int64_t)blockIdx.y * 64, kk0 = (int64_t)blockIdx.x * 64;
+  const int tid = threadIdx.x;
+  const int tr = (tid >> 4) * 4, tc = (tid & 15) * 4;
+  float acc[4][4] = {};
+  for (int64_t n0 = 0; n0 < N; n0 += 32) {
+    for (int idx = tid; idx < 64 * 32; idx += 256) {
+      const int mm = idx >> 5, nn = idx & 31;
+      const int64_t m = m0 + mm, n = n0 + nn;
+      xs[nn][mm] = (m < M && n < N) ? to_f32<XT>(x[m * N + n]) : 0.f;
+    }
+    for (int idx = tid; idx < 32 * 32; idx += 256) {
+      const int jj = idx >> 5, nn = idx & 31;
+      const int64_t j = kk0 / 2 + jj, n = n0 + nn;
+      float lo = 0.f, hi = 0.f;
+      if (j < K / 2 && n < N) {
+        const uint32_t b = packed[j * N + n];
+        const float z = zs_to_f32<ZST>(zero, n), s = zs_to_f32<ZST>(scale, n);
+        lo = __fmul_rn(__fsub_rn((float)(b & 0xF), z), s);
+        hi = __fmul_rn(__fsub_rn((float)(b >> 4), z), s);
+      }
+      ws[nn][2 * jj] = lo;
+      ws[nn][2 * jj + 1] = hi;
+    }
+    __syncthreads();
+#pragma unroll 8
+    for (int nn = 0; nn < 32; ++nn) {
+      float a[4], b[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) { a[i] = xs[nn][tr + i]; b[i] = ws[nn][tc + i]; }
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(a[i], b[j], acc[i][j]);
+    }
+    __syncthreads();
+  }
+#pragma unroll
+  for (int i = 0; i < 4; ++i)
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int64_t m = m0 + tr + i, kk = kk0 + tc + j;
+      if (m < M && kk < K) out[m * K + kk] = from_f32<XT>(acc[i][j]);
+    }
+}
+
+constexpr size_t kTicketBytes = 4096;   // 1024 tickets; split-K is only planned below 4 * #SM CTAs
+
+struct FwdPlan { int mt; int mtiles; int ncg; int ksplit; int steps_per_split; };
+
+static FwdPlan plan_fwd(int64_t M, int64_t N, int64_t K) {
+  FwdPlan p;
+  p.mt = (M <= 16) ? 1 : 2;
+  p.mtiles = (int)cdiv(M, 16 * p.mt);
+  p.ncg = (int)cdiv(N, WCOLS);
+  const int64_t total_steps = cdiv(K / 2, 8);
+  const int64_t base = (int64_t)p.ncg * p.mtiles;
+  int64_t want = cdiv(4 * (int64_t)sm_count(), base);
+  const int64_t max_split = std::max<int64_t>(1, total_steps / (2 * WWARPS));
+  if (want > max_split) want = max_split;
+  if (want < 1) want = 1;
+  if (base > (int64_t)(kTicketBytes / sizeof(int))) want = 1;
+  p.steps_per_split = (int)cdiv(total_steps, want);
+  p.ksplit = (int)cdiv(total_steps, p.steps_per_split);
+  return p;
+}
+
+template <typename XT, typename CT, typename ZST>
+static int launch_fwd(const void* x, const uint8_t* packed, const void* zero, const void* scale, void* out,
+                      int64_t M, int64_t N, int64_t K, void* ws, cudaStream_t s) {
+  const FwdPlan p = plan_fwd(M, N, K);
+  int* tickets = (int*)ws;                                   // kTicketBytes, zero between launches
+  float* partials = (float*)((char*)ws + kTicketBytes);
+  const int vec = (N % 16 == 0) && aligned(packed, 16);
+  dim3 grid((unsigned)p.ncg, (unsigned)p.ksplit, (unsigned)p.mtiles);
+  if (p.mt == 1)
+    w4_fwd_kernel<XT, CT, 1, ZST><<<grid, WWARPS * 32, 0, s>>>((const XT*)x, packed, zero, scale, (XT*)out, M, N, K,
+                                                               p.steps_per_split, p.ksplit, partials, tickets, vec);
+  else
+    w4_fwd_kernel<XT, CT, 2, ZST><<<grid, WWARPS * 32, 0, s>>>((const XT*)x, packed, zero, scale, (XT*)out, M, N, K,
+                                                               p.steps_per_split, p.ksplit, partials, tickets, vec);
+  return check_launch("w4_matmul");
+}
+
+template <typename XT, typename ZST>
+static int launch_tb(const void* x, const uint8_t* packed, const void* zero, const void* scale, void* out,
+                     int64_t M, int64_t N, int64_t K, cudaStream_t s) {
+  dim3 grid((unsigned)cdiv(K, 64), (unsigned)cdiv(M, 64));
+  w4_tb_kernel<XT, ZST><<<grid, 256, 0, s>>>((const XT*)x, packed, zero, scale, (XT*)out, M, N, K);
+  return check_launch("w4_matmul_tb");
+}
+
+}  // namespace jgq
+
+using namespace jgq;
+
+// Workspace layout (forward): 4096 bytes of int32 tickets, one per (row tile,
+// channel group), then [ksplit][M][channel groups][132] fp32 slices.  The ticket
+// bytes must be zero before the first launch that uses a workspace; every launch
+// leaves them zero again.  The slices need no initialisation.
+extern "C" size_t jgq_w4_matmul_workspace_bytes(int64_t M, int64_t N, int64_t K, int transpose_b) {
+  if (transpose_b || M <= 0 || N <= 0 || K <= 0) return 0;
+  const FwdPlan p = plan_fwd(M, N, K);
+  size_t bytes = kTicketBytes;
+  if (p.ksplit > 1) bytes += align_up((size_t)p.ksplit * M * p.ncg * PSTRIDE * sizeof(float), 256);
+  return bytes;
+}
+
+extern "C" int jgq_w4_matmul(const void* x, int x_dtype, const uint8_t* packed,
+                             const void* zero, const void* scale, int zs_dtype,
+                             void* out, int64_t M, int64_t N, int64_t K, int transpose_b,
+                             void* ws, size_t ws_bytes, void* stream) {
+  JGQ_REQUIRE(x_dtype == JGQ_F32 || x_dtype == JGQ_F16 || x_dtype == JGQ_BF16, JGQ_ERR_ARG,
+              "w4_matmul: activation dtype must be f32/f16/bf16");
+  JGQ_REQUIRE(zs_dtype == JGQ_F32 || zs_dtype == JGQ_F16, JGQ_ERR_ARG, "w4_matmul: zero/scale dtype must be f32/f16");
+  JGQ_REQUIRE(M >= 0 && N > 0 && K > 0, JGQ_ERR_ARG, "w4_matmul: bad shape M=%lld N=%lld K=%lld",
+              (long long)M, (long long)N, (long long)K);
+  JGQ_REQUIRE(K % 2 == 0, JGQ_ERR_ARG, "w4_matmul: K=%lld must be even (two codes per byte)", (long long)K);
+  JGQ_REQUIRE(M <= 2147483647LL / 2 && N <= 2147483647LL && K <= 2147483647LL, JGQ_ERR_LIMIT, "w4_matmul: shape too large");
+  if (M == 0) return JGQ_OK;
+  JGQ_REQUIRE(x && packed && zero && scale && out, JGQ_ERR_ARG, "w4_matmul: null pointer");
+  cudaStream_t s = (cudaStream_t)stream;
+  if (transpose_b) {
+#define JGQ_TB(XT)                                                                                       \
+  return zs_dtype == JGQ_F32 ? launch_tb<XT, float>(x, packed, zero, scale, out, M, N, K, s)             \
+                             : launch_tb<XT, __half>(x, packed, zero, scale, out, M, N, K, s)
+    if (x_dtype == JGQ_F32) { JGQ_TB(float); }
+    if (x_dtype == JGQ_F16) { JGQ_TB(__half); }
+    JGQ_TB(__nv_bfloat16);
+#undef JGQ_TB
+  }
+  JGQ_REQUIRE(aligned(x, 8), JGQ_ERR_ALIGN, "w4_matmul: x must be 8-byte aligned");
+  const size_t need = jgq_w4_matmul_workspace_bytes(M, N, K, 0);
+  JGQ_REQUIRE(ws && ws_bytes >= need, JGQ_ERR_WORKSPACE, "w4_matmul: workspace %zu < %zu bytes", ws_bytes, need);
+  JGQ_REQUIRE(aligned(ws, 256), JGQ_ERR_ALIGN, "w4_matmul: workspace must be 256-byte aligned");
+#define JGQ_FWD(XT, CT)                                                                                  \
+  return zs_dtype == JGQ_F32 ? launch_fwd<XT, CT, float>(x, packed, zero, scale, out, M, N, K, ws, s)    \
+                             : launch_fwd<XT, CT, __half>(x, packed, zero, scale, out, M, N, K, ws, s)
+  if (x_dtype == JGQ_F32) { JGQ_FWD(float, __nv_bfloat16); }
+  if (x_dtype == JGQ_F16) { JGQ_FWD(__half, __half); }
+  JGQ_FWD(__nv_bfloat16, __nv_bfloat16);
+#undef JGQ_FWD
+}

@@ -1,0 +1,361 @@
+"""Host-side mirror of the reference's ``jax_gptq/gptq.py`` over the CUDA C ABI.
+
+Same function names, argument meaning and error behaviour as the reference
+module; arrays are torch CUDA tensors (device memory + streams are the only
+things torch is used for).  NumPy arrays and CPU tensors are accepted too:
+they are copied to the current CUDA device, and the results come back as
+NumPy arrays when every array argument was NumPy.  Every computation runs in
+libjgq.so; there is no PyTorch or CPU implementation behind these functions.
+"""
+from __future__ import annotations
+
+import numpy as np
+import torch
+
+from . import _lib
+from ._lib import lib, check
+
+_DT = {torch.float32: _lib.F32, torch.float16: _lib.F16, torch.bfloat16: _lib.BF16}
+_MAX_CONVERT_BYTES = 1 << 30     # fp32 staging cap for non-fp32 calibration batches
+
+
+# --------------------------------------------------------------------------
+# plumbing
+# --------------------------------------------------------------------------
+def _stream():
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _dev():
+    if not torch.cuda.is_available():
+        raise RuntimeError('jax_gptq_b200 needs a CUDA device (sm_100a); there is no CPU path')
+    return torch.device('cuda', torch.cuda.current_device())
+
+
+def _is_np(a):
+    return isinstance(a, np.ndarray) or np.isscalar(a)
+
+
+def _to_dev(a, dtype=None):
+    """torch CUDA tensor for `a` (NumPy array, CPU tensor or CUDA tensor)."""
+    if isinstance(a, torch.Tensor):
+        t = a
+    else:
+        arr = np.asarray(a)
+        if arr.dtype == np.float64 and dtype is None:
+            dtype = torch.float32
+        t = torch.from_numpy(np.ascontiguousarray(arr))
+    if t.device.type != 'cuda':
+        t = t.to(_dev(), non_blocking=True)
+    if dtype is not None and t.dtype != dtype:
+        t = t.to(dtype)
+    return t
+
+
+def _out(t, as_numpy):
+    return t.cpu().numpy() if as_numpy else t
+
+
+def _ptr(t):
+    return 0 if t is None else t.data_ptr()
+
+
+_ws_cache = {}
+
+
+def _workspace(nbytes, zeroed=False, tag='ws'):
+    """Per (device, stream) scratch buffer, grown on demand.  `zeroed` buffers are
+    created with zeros and handed only to kernels that restore the zeros."""
+    key = (torch.cuda.current_device(), _stream(), tag)
+    buf = _ws_cache.get(key)
+    if buf is None or buf.numel() < nbytes:
+        size = max(int(nbytes), 1 << 20)
+        buf = (torch.zeros if zeroed else torch.empty)(size, dtype=torch.uint8, device=_dev())
+        _ws_cache[key] = buf
+    return buf
+
+
+def _view3(shape, axis):
+    outer = int(np.prod(shape[:axis], dtype=np.int64)) if axis > 0 else 1
+    inner = int(np.prod(shape[axis + 1:], dtype=np.int64)) if axis + 1 < len(shape) else 1
+    return outer, int(shape[axis]), inner
+
+
+# --------------------------------------------------------------------------
+# QuantizedMatrix                                      reference gptq.py:8-42
+# --------------------------------------------------------------------------
+class QuantizedMatrix:
+    """Packed uint8 codes + per-channel zero/scale (fp32) + contraction axis."""
+
+    def __init__(self, int_weight, zero, scale, contraction_axis=0):
+        self.int_weight = int_weight
+        self.zero = zero
+        self.scale = scale
+        self.contraction_axis = contraction_axis
+
+    @property
+    def shape(self):
+        return quant_matrix_shape(self)
+
+    @property
+    def dtype(self):
+        return self.zero.dtype
+
+    def tree_flatten(self):
+        """Children / aux data in the reference's pytree order (gptq.py:24-32)."""
+        return (self.int_weight, self.zero, self.scale), self.contraction_axis
+
+    @classmethod
+    def tree_unflatten(cls, contraction_axis, children):
+        return cls(*children, contraction_axis=contraction_axis)
+
+
+def quant_matrix_shape(quantized_matrix, bits=4):
+    mat = quantized_matrix.int_weight
+    ele_width = mat.element_size() * 8 if isinstance(mat, torch.Tensor) else mat.dtype.itemsize * 8
+    shape = list(mat.shape)
+    shape[quantized_matrix.contraction_axis] *= ele_width // bits
+    return tuple(shape)
+
+
+# --------------------------------------------------------------------------
+# Hessian                                               reference gptq.py:57-103
+# --------------------------------------------------------------------------
+def _accumulate_raw(xs, H=None):
+    """H (K x K fp32, lower triangle) += sum over batches of X^T X; returns (H, n)."""
+    n_total = 0
+    for batch in xs:
+        b = _to_dev(batch)
+        if b.dtype not in _DT:
+            b = b.to(torch.float32)          # gptq.py:65: batch.astype(H.dtype)
+        K = b.shape[-1]
+        b = b.reshape(-1, K)
+        if not b.is_contiguous():
+            b = b.contiguous()
+        if H is None:
+            H = torch.zeros((K, K), dtype=torch.float32, device=b.device)
+        n = b.shape[0]
+        rows = n
+        if b.dtype != torch.float32:
+            rows = max(1, min(n, _MAX_CONVERT_BYTES // (4 * K)))
+        for r0 in range(0, n, rows):
+            chunk = b[r0:r0 + rows]
+            m = chunk.shape[0]
+            need = lib.jgq_hessian_workspace_bytes(m, K, _DT[chunk.dtype])
+            ws = _workspace(need) if need else None
+            check(lib.jgq_hessian_accum(chunk.data_ptr(), _DT[chunk.dtype], m, K, H.data_ptr(),
+                                        _ptr(ws), need, _stream()))
+        n_total += n
+    return H, n_total
+
+
+def _finalize_H(H, n_total):
+    check(lib.jgq_hessian_finalize(H.data_ptr(), H.shape[0], float(n_total), _stream()))
+    return H
+
+
+def accumulate_H(xs, use_fp64=False):
+    """(1/n) sum_t x_t x_t^T over a list of calibration batches (gptq.py:76-103)."""
+    if use_fp64:
+        raise NotImplementedError('use_fp64=True is not available in the CUDA path')
+    as_np = all(_is_np(x) for x in xs)
+    H, n = _accumulate_raw(xs)
+    return _out(_finalize_H(H, n), as_np)
+
+
+# --------------------------------------------------------------------------
+# quantization parameters                             reference gptq.py:105-118
+# --------------------------------------------------------------------------
+def _col_params(Wf, bits=4):
+    K, N = Wf.shape
+    scale = torch.empty(N, dtype=torch.float32, device=Wf.device)
+    zero = torch.empty(N, dtype=torch.float32, device=Wf.device)
+    maxq = 2 ** bits - 1
+    check(lib.jgq_col_params(Wf.data_ptr(), K, N, maxq, scale.data_ptr(), zero.data_ptr(), _stream()))
+    return {'scale': scale, 'zero': zero, 'maxq': maxq}
+
+
+def get_col_quantize_params(W, bits=4):
+    """Per-output-channel scale / zero of a (K, N) matrix (gptq.py:118)."""
+    as_np = _is_np(W)
+    Wf = _to_dev(W, torch.float32).contiguous()
+    if Wf.dim() != 2:
+        raise ValueError('get_col_quantize_params expects a 2-D matrix')
+    p = _col_params(Wf, bits)
+    return {'scale': _out(p['scale'], as_np), 'zero': _out(p['zero'], as_np), 'maxq': p['maxq']}
+
+
+# --------------------------------------------------------------------------
+# GPTQ driver                                         reference gptq.py:182-212
+# --------------------------------------------------------------------------
+def _damp_and_invert(Wf, H, damping):
+    """In place on Wf (dead rows zeroed) and H (destroyed).  Returns (L, status tensor)."""
+    K, N = Wf.shape
+    L = torch.empty((K, K), dtype=torch.float32, device=Wf.device)
+    status = torch.zeros(1, dtype=torch.int32, device=Wf.device)
+    need = lib.jgq_damp_invert_workspace_bytes(K)
+    ws = _workspace(need)
+    check(lib.jgq_damp_invert(Wf.data_ptr(), N, H.data_ptr(), K, float(damping), L.data_ptr(),
+                              ws.data_ptr(), need, status.data_ptr(), _stream()))
+    return L, status
+
+
+def _quantize(Wf, L, params, block_size, out_dtype, want_codes=False):
+    K, N = Wf.shape
+    Q = torch.empty((K, N), dtype=out_dtype, device=Wf.device)
+    codes = torch.empty((K, N), dtype=torch.uint8, device=Wf.device) if want_codes else None
+    need = lib.jgq_gptq_quantize_workspace_bytes(K, N, block_size)
+    ws = _workspace(need)
+    check(lib.jgq_gptq_quantize(Wf.data_ptr(), L.data_ptr(), params['scale'].data_ptr(),
+                                params['zero'].data_ptr(), K, N, block_size, params['maxq'],
+                                Q.data_ptr(), _DT[out_dtype], _ptr(codes), ws.data_ptr(), need, _stream()))
+    return Q, codes
+
+
+def gptq(W, xs, block_size=128, actorder=False, damping=0.01, use_fp64=False, *,
+         bits=4, H=None, return_codes=False):
+    """Quantize W (K x N) with calibration batches xs.  Returns (Q, params) like the
+    reference (gptq.py:182-212): Q holds the dequantised values in W's dtype and
+    params = {'scale', 'zero', 'maxq'}.
+
+    Keyword-only extras (not in the reference): ``bits`` (3-bit uses maxq=7 with
+    the same nibble container), ``H`` (a finalized Hessian to reuse, e.g. for
+    linears fed by the same activation), ``return_codes`` (also return the uint8
+    codes the kernel produced alongside Q).
+    """
+    if use_fp64:
+        raise NotImplementedError('use_fp64=True is not available in the CUDA path')
+    as_np = _is_np(W)
+    Wd = _to_dev(W)
+    if Wd.dim() != 2:
+        raise ValueError('gptq expects a 2-D weight (K, N)')
+    orig_dtype = Wd.dtype if Wd.dtype in _DT else torch.float32
+    Wf = Wd.to(torch.float32, copy=True).contiguous()        # gptq.py:184 (private copy, updated in place)
+    K, N = Wf.shape
+    if K % block_size != 0:
+        raise ValueError(f'K={K} must be a multiple of block_size={block_size}')
+    params = _col_params(Wf, bits)                           # gptq.py:185 (before any fix-up)
+    if H is None:
+        Hd, n = _accumulate_raw(xs)
+        Hd = _finalize_H(Hd, n)                              # gptq.py:187
+    else:
+        Hd = _to_dev(H, torch.float32).clone().contiguous()
+    if Hd.shape != (K, K):
+        raise AssertionError(f'Hessian shape {tuple(Hd.shape)} does not match K={K}')
+    perm = None
+    if actorder:                                             # gptq.py:170-175
+        d = torch.diagonal(Hd)
+        perm = torch.flip(torch.argsort(d, stable=True), dims=(0,))
+        Wf = Wf[perm, :].contiguous()
+        Hd = Hd[perm][:, perm].contiguous()
+    L, status = _damp_and_invert(Wf, Hd, damping)            # gptq.py:193
+    Q, codes = _quantize(Wf, L, params, block_size, orig_dtype, return_codes)
+    if perm is not None:                                     # gptq.py:177-180
+        invperm = torch.argsort(perm)
+        Q = Q[invperm, :].contiguous()
+        if codes is not None:
+            codes = codes[invperm, :].contiguous()
+    if int(status.item()) != 0:                              # gptq.py:194-196 (one host sync per call)
+        raise ValueError('NaN when computing Hinv. Features NaN?')
+    out_params = {'scale': _out(params['scale'], as_np), 'zero': _out(params['zero'], as_np),
+                  'maxq': params['maxq']}
+    if return_codes:
+        return _out(Q, as_np), out_params, _out(codes, as_np)
+    return _out(Q, as_np), out_params
+
+
+# --------------------------------------------------------------------------
+# pack / unpack                                       reference gptq.py:214-292
+# --------------------------------------------------------------------------
+def pack_along_axis(axis, w):
+    """byte j = w[2j] | w[2j+1] << 4 along `axis` (gptq.py:237-249, 282-283)."""
+    as_np = _is_np(w)
+    t = _to_dev(w)
+    if axis >= t.dim():
+        raise ValueError(f'Axis {axis} is out of bounds for array of dimension {t.dim()}')
+    if t.dtype == torch.uint8:
+        code_dt = _lib.U8
+    else:
+        t = t.to(torch.int32)
+        code_dt = _lib.I32
+    t = t.contiguous()
+    outer, alen, inner = _view3(t.shape, axis)
+    shape = list(t.shape)
+    shape[axis] = alen // 2
+    out = torch.empty(shape, dtype=torch.uint8, device=t.device)
+    check(lib.jgq_pack_int4(t.data_ptr(), code_dt, out.data_ptr(), outer, alen, inner, _stream()))
+    return _out(out, as_np)
+
+
+def unpack_along_axis(axis, w):
+    """Inverse of pack_along_axis (gptq.py:251-263, 285-286)."""
+    as_np = _is_np(w)
+    t = _to_dev(w)
+    if axis >= t.dim():
+        raise ValueError(f'Axis {axis} is out of bounds for array of dimension {t.dim()}')
+    if t.dtype != torch.uint8:
+        raise TypeError('packed weights must be uint8')
+    t = t.contiguous()
+    outer, plen, inner = _view3(t.shape, axis)
+    shape = list(t.shape)
+    shape[axis] = plen * 2
+    out = torch.empty(shape, dtype=torch.uint8, device=t.device)
+    check(lib.jgq_unpack_int4(t.data_ptr(), out.data_ptr(), outer, plen, inner, _stream()))
+    return _out(out, as_np)
+
+
+def pack_rowwise(w):
+    return pack_along_axis(1, w)
+
+
+def pack_colwise(w):
+    return pack_along_axis(0, w)
+
+
+def unpack_rowwise(w):
+    return unpack_along_axis(1, w)
+
+
+def unpack_colwise(w):
+    return unpack_along_axis(0, w)
+
+
+def pack_matrix(Q, params, contraction_axis=0):
+    """codes = round(Q / scale + zero) packed along `contraction_axis` (gptq.py:214-228)."""
+    as_np = _is_np(Q)
+    Qd = _to_dev(Q)
+    if Qd.dtype not in _DT:
+        Qd = Qd.to(torch.float32)
+    Qd = Qd.contiguous()
+    if contraction_axis >= Qd.dim():
+        raise ValueError(f'Axis {contraction_axis} is out of bounds for array of dimension {Qd.dim()}')
+    scale = _to_dev(params['scale'], torch.float32).contiguous()
+    zero = _to_dev(params['zero'], torch.float32).contiguous()
+    outer, alen, inner = _view3(Qd.shape, contraction_axis)
+    if scale.numel() != outer * inner or zero.numel() != outer * inner:
+        raise ValueError('scale/zero must have the shape of Q without the contraction axis')
+    shape = list(Qd.shape)
+    shape[contraction_axis] = alen // 2
+    packed = torch.empty(shape, dtype=torch.uint8, device=Qd.device)
+    check(lib.jgq_pack_matrix(Qd.data_ptr(), _DT[Qd.dtype], scale.data_ptr(), zero.data_ptr(),
+                              packed.data_ptr(), outer, alen, inner, _stream()))
+    return QuantizedMatrix(int_weight=_out(packed, as_np), zero=_out(zero, as_np), scale=_out(scale, as_np),
+                           contraction_axis=contraction_axis)
+
+
+def unpack_matrix(weight, dtype=None):
+    """(codes - zero) * scale as fp32 (gptq.py:230-235).  `dtype` (not in the
+    reference) selects an fp16/bf16 result instead."""
+    as_np = _is_np(weight.int_weight)
+    packed = _to_dev(weight.int_weight).contiguous()
+    zero = _to_dev(weight.zero, torch.float32).contiguous()
+    scale = _to_dev(weight.scale, torch.float32).contiguous()
+    axis = weight.contraction_axis
+    outer, plen, inner = _view3(packed.shape, axis)
+    shape = list(packed.shape)
+    shape[axis] = plen * 2
+    out_dtype = dtype or torch.float32
+    out = torch.empty(shape, dtype=out_dtype, device=packed.device)
+    check(lib.jgq_unpack_matrix(packed.data_ptr(), zero.data_ptr(), scale.data_ptr(), out.data_ptr(),
+                                _DT[out_dtype], outer, plen, inner, _stream()))
+    return _out(out, as_np)
