@@ -136,7 +136,7 @@ def test_accumulate_H_large_split(G):
 # ------------------------------------------------------- damp + Cholesky inverse ----
 @pytest.mark.parametrize('K', [32, 64, 100, 256, 768])
 def test_damp_invert_matches_oracle(G, K):
-    from jax_gptq_b200 import gptq as gg
+    import importlib; gg = importlib.import_module('jax_gptq_b200.gptq')
     rng = np.random.default_rng(30 + K)
     A = rng.standard_normal((K, K)).astype(np.float32) / np.sqrt(K)
     X = (rng.standard_normal((4 * K, K)).astype(np.float32) @ A).astype(np.float32)
@@ -159,7 +159,7 @@ def test_damp_invert_matches_oracle(G, K):
 
 
 def test_damp_invert_dead_feature_and_not_pd(G):
-    from jax_gptq_b200 import gptq as gg
+    import importlib; gg = importlib.import_module('jax_gptq_b200.gptq')
     rng = np.random.default_rng(33)
     K = 96
     X = rng.standard_normal((512, K)).astype(np.float32)
@@ -186,7 +186,7 @@ def test_damp_invert_dead_feature_and_not_pd(G):
 def test_single_block_bit_exact(G, K, N, bs):
     """One block (K == bs) with the oracle's own L: every rounding is pinned, so Q and the
     codes must match the oracle bit for bit."""
-    from jax_gptq_b200 import gptq as gg
+    import importlib; gg = importlib.import_module('jax_gptq_b200.gptq')
     rng = np.random.default_rng(40 + K + N)
     W = (0.05 * rng.standard_normal((K, N))).astype(np.float32)
     X = rng.standard_normal((4 * K + 16, K)).astype(np.float32)
