@@ -1,0 +1,439 @@
+#!/usr/bin/env python
+"""Benchmark of the GPTQ hot path on B200.
+
+Workload (one "step"): GPTQ-quantize every block linear of a GPT-2-small-shaped
+model (12 blocks x {768x2304, 768x768, 768x3072, 3072x768}, fp32 weights
+~0.02*N(0,1)) to 4 bits from 65536 calibration tokens (128 sequences x 512
+uniform-random ids), blocksize 128, damping 0.01, then pack the result.
+Calibration activations are produced once, outside the timed region, by a plain
+torch forward of that architecture with each linear replaced by its quantized
+weight as soon as it exists (the reference's default calibration mode).
+
+  value : weights quantized per second, activations and weights resident in HBM
+  e2e   : the same through the public host API with pinned HOST buffers: every
+          step copies weights + activations host->device and the packed result
+          device->host inside the timed region
+
+`--impl reference` times the CPU oracle (NumPy/SciPy restatement of the reference,
+all host cores) on a bounded sample of the same workload: one block (4 linears).
+Multi-GPU (`torchrun`, one rank per GPU): ranks quantize independent models
+(layer-parallel, no data-path collective): weak scaling.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+METRIC = 'gptq_weights_quantized_per_s'
+UNIT = 'weights/s'
+LINEARS = (('attn.c_attn', 768, 2304), ('attn.c_proj', 768, 768), ('mlp.c_fc', 768, 3072), ('mlp.c_proj', 3072, 768))
+N_LAYERS, D_MODEL, N_HEADS, VOCAB, SEQ, N_SEQ, CALIB_BATCHES = 12, 768, 12, 50257, 512, 128, 16
+BLOCK_SIZE, DAMP = 128, 0.01
+
+
+def workload_name(layers):
+    return (f'gpt2-small-shaped GPTQ: {layers} blocks x 4 linears (768x2304, 768x768, 768x3072, 3072x768), '
+            f'{N_SEQ * SEQ} calibration tokens in {CALIB_BATCHES} batches, 4-bit, blocksize {BLOCK_SIZE}, '
+            f'damp {DAMP}, pack included; lm_head not quantized')
+
+
+# --------------------------------------------------------------------------
+# caller side: a minimal GPT-2-shaped forward that yields each linear's input
+# --------------------------------------------------------------------------
+def init_block(torch, gen, device):
+    return {name: (0.02 * torch.randn((k, n), generator=gen, device=device, dtype=torch.float32))
+            for name, k, n in LINEARS}
+
+
+def block_forward(torch, h, weights, quantize_fn):
+    """One transformer block.  `quantize_fn(name, W, x)` returns the weight to continue with
+    (and may record x, the calibration input of that linear)."""
+    F = torch.nn.functional
+    B, T, D = h.shape
+    x = F.layer_norm(h, (D,))
+    w = quantize_fn('attn.c_attn', weights['attn.c_attn'], x)
+    qkv = (x.reshape(-1, D) @ w).reshape(B, T, 3, N_HEADS, D // N_HEADS).permute(2, 0, 3, 1, 4)
+    a = F.scaled_dot_product_attention(qkv[0], qkv[1], qkv[2], is_causal=True)
+    a = a.transpose(1, 2).reshape(B, T, D)
+    w = quantize_fn('attn.c_proj', weights['attn.c_proj'], a)
+    h = h + (a.reshape(-1, D) @ w).reshape(B, T, D)
+    x = F.layer_norm(h, (D,))
+    w = quantize_fn('mlp.c_fc', weights['mlp.c_fc'], x)
+    m = F.gelu((x.reshape(-1, D) @ w), approximate='tanh')
+    w = quantize_fn('mlp.c_proj', weights['mlp.c_proj'], m.reshape(B, T, 4 * D))
+    h = h + (m @ w).reshape(B, T, D)
+    return h
+
+
+def embed(torch, gen, device):
+    ids = torch.randint(0, VOCAB, (N_SEQ, SEQ), generator=gen, device=device)
+    wte = 0.02 * torch.randn((VOCAB, D_MODEL), generator=gen, device=device)
+    wpe = 0.02 * torch.randn((1024, D_MODEL), generator=gen, device=device)
+    return wte[ids] + wpe[:SEQ][None]
+
+
+# --------------------------------------------------------------------------
+# clocks
+# --------------------------------------------------------------------------
+class ClockSampler:
+    FIELDS = ('clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,'
+              'clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap')
+
+    def __init__(self, index):
+        self.index, self.proc, self.lines = index, None, []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(['nvidia-smi', '-i', str(self.index), f'--query-gpu={self.FIELDS}',
+                                          '--format=csv,noheader,nounits', '-lms', '100'],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self):
+        if self.proc is None:
+            return {'sm_mhz': None, 'sm_max_mhz': None, 'reasons': ['nvidia-smi unavailable']}
+        time.sleep(0.15)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        names = ('hw_slowdown', 'hw_thermal_slowdown', 'sw_thermal_slowdown', 'sw_power_cap')
+        for ln in self.lines:
+            parts = [p.strip() for p in ln.split(',')]
+            if len(parts) < 6:
+                continue
+            try:
+                sm.append(float(parts[0])); mx.append(float(parts[1]))
+            except ValueError:
+                continue
+            for name, val in zip(names, parts[2:6]):
+                if val.lower().startswith('active'):
+                    reasons.add(name)
+        return {'sm_mhz': statistics.median(sm) if sm else None, 'sm_max_mhz': max(mx) if mx else None,
+                'samples': len(sm), 'reasons': sorted(reasons)}
+
+
+# --------------------------------------------------------------------------
+# reference arm / CPU baseline: the oracle on one block
+# --------------------------------------------------------------------------
+def cpu_block_inputs(seed):
+    """Block-0 weights and per-linear calibration inputs (fp32 forward, torch CPU ops)."""
+    import torch
+    gen = torch.Generator(device='cpu').manual_seed(seed)
+    h = embed(torch, gen, 'cpu')
+    weights = init_block(torch, gen, 'cpu')
+    captured = {}
+
+    def grab(name, W, x):
+        captured[name] = x.reshape(-1, x.shape[-1]).numpy()
+        return W
+    block_forward(torch, h, weights, grab)
+    return [(name, weights[name].numpy(), np.array_split(captured[name], CALIB_BATCHES)) for name, _, _ in LINEARS]
+
+
+def cpu_block_step(items):
+    from oracle import ref_gptq as R
+    for _, W, xs in items:
+        Q, params = R.gptq(W, xs, block_size=BLOCK_SIZE, damping=DAMP)
+        R.pack_matrix(Q, params)
+
+
+def cpu_threads():
+    try:
+        return len(os.sched_getaffinity(0))
+    except AttributeError:
+        return os.cpu_count() or 1
+
+
+def run_reference(args):
+    rank = int(os.environ.get('RANK', '0'))
+    if rank != 0:
+        return
+    items = cpu_block_inputs(2002)
+    weights = sum(W.size for _, W, _ in items)
+    for _ in range(args.warmup):
+        cpu_block_step(items)
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        cpu_block_step(items)
+    dt = (time.perf_counter() - t0) / args.steps
+    val = weights / dt
+    sample = 'one block (4 linears, 7.08 M weights) of the workload per step, 65536 calibration tokens'
+    line = {'impl': 'reference', 'metric': METRIC, 'value': val, 'unit': UNIT, 'n_gpus': args.gpus,
+            'steps': args.steps, 'warmup': args.warmup, 'ms_per_step': dt * 1e3, 'higher_is_better': True,
+            'scaling': 'weak', 'vs_baseline': None, 'dtype': 'f32', 'data': 'synthetic',
+            'config': {'workload': workload_name(N_LAYERS), 'sample': sample},
+            'cpu_baseline': {'value': val, 'unit': UNIT, 'cores': cpu_threads(), 'kind': 'port', 'sample': sample},
+            'e2e': {'value': val, 'unit': UNIT, 'h2d_bytes_per_step': 0, 'd2h_bytes_per_step': 0}}
+    print(json.dumps(line), flush=True)
+
+
+# --------------------------------------------------------------------------
+# our arm
+# --------------------------------------------------------------------------
+def run_ours(args):
+    import torch
+    import torch.distributed as dist
+    import jax_gptq_b200 as G
+    import importlib
+    gg = importlib.import_module('jax_gptq_b200.gptq')
+    from jax_gptq_b200._lib import lib
+
+    world = int(os.environ.get('WORLD_SIZE', '1'))
+    rank = int(os.environ.get('RANK', '0'))
+    local = int(os.environ.get('LOCAL_RANK', '0'))
+    torch.cuda.set_device(local)
+    dev = torch.device('cuda', local)
+    if world > 1:
+        dist.init_process_group('nccl', device_id=dev)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    layers = args.layers
+    gen = torch.Generator(device=dev).manual_seed(2002 + rank)
+
+    # ---- untimed set-up: weights, and calibration inputs captured with quantized weights in place ----
+    h = embed(torch, gen, dev)
+    model, acts = [], []
+    t_fwd0 = time.perf_counter()
+    for _ in range(layers):
+        weights = init_block(torch, gen, dev)
+        captured = {}
+
+        def quantize_in_place(name, W, x):
+            xs = x.reshape(-1, x.shape[-1]).contiguous()
+            captured[name] = xs
+            Q, _ = G.gptq(W, list(xs.chunk(CALIB_BATCHES)), block_size=BLOCK_SIZE, damping=DAMP)
+            return Q
+        h = block_forward(torch, h, weights, quantize_in_place)
+        model.append(weights)
+        acts.append(captured)
+    torch.cuda.synchronize()
+    setup_s = time.perf_counter() - t_fwd0
+    del h
+    total_weights = layers * sum(k * n for _, k, n in LINEARS)
+
+    def step_resident():
+        out = []
+        for weights, captured in zip(model, acts):
+            for name, _, _ in LINEARS:
+                Q, params = G.gptq(weights[name], list(captured[name].chunk(CALIB_BATCHES)),
+                                   block_size=BLOCK_SIZE, damping=DAMP)
+                out.append(G.pack_matrix(Q, params))
+        return out
+
+    # ---- value: device-resident ----
+    for _ in range(args.warmup):
+        step_resident()
+    barrier()
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    launches0 = lib.jgq_launch_count()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        step_resident()
+    e1.record()
+    torch.cuda.synchronize()
+    launches = lib.jgq_launch_count() - launches0
+    ms = e0.elapsed_time(e1) / args.steps
+    clocks = sampler.stop() if rank == 0 else None
+    t = torch.tensor([ms], device=dev, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms_max = float(t.item())
+    value = world * total_weights / (ms_max * 1e-3)
+
+    # ---- roofline of the dominant kernel: Hessian accumulation of the K=3072 linear ----
+    x_big = acts[0]['mlp.c_proj']
+    n_tok, Kb = x_big.shape
+    batches = list(x_big.chunk(CALIB_BATCHES))
+    for _ in range(2):
+        gg._accumulate_raw(batches)
+    torch.cuda.synchronize()
+    reps = 5
+    l0 = lib.jgq_launch_count()
+    e0.record()
+    for _ in range(reps):
+        gg._accumulate_raw(batches)
+    e1.record()
+    torch.cuda.synchronize()
+    h_launches = (lib.jgq_launch_count() - l0) / reps
+    h_ms = e0.elapsed_time(e1) / reps
+    flops = 2.0 * n_tok * Kb * Kb
+    peaks = {}
+    try:
+        peaks = json.load(open(os.path.join(ROOT, 'MEASURED_PEAKS.json')))
+    except (OSError, ValueError):
+        pass
+    peak_tf = float(peaks.get('bf16_tflops_sustained', 1400.0))
+    achieved_tf = flops / (h_ms * 1e-3) / 1e12
+    roofline = {'kernel': 'hessian_accum (H += X^T X, K=3072, n=65536, 16 batches)', 'bound': 'tensor',
+                'achieved': achieved_tf, 'peak': peak_tf, 'unit': 'TFLOP/s', 'frac': achieved_tf / peak_tf,
+                'peak_source': 'MEASURED_PEAKS.json bf16_tflops_sustained' if peaks else 'fallback 1.4 PFLOP/s sustained',
+                'launches_per_hessian': h_launches, 'ms_per_hessian': h_ms, 'traffic': None}
+
+    # ---- e2e: pinned host buffers in, packed result out, all copies inside the timed region ----
+    free_host = 0
+    try:
+        for ln in open('/proc/meminfo'):
+            if ln.startswith('MemAvailable'):
+                free_host = int(ln.split()[1]) * 1024
+    except OSError:
+        pass
+    per_layer = sum(a.numel() * 4 for a in acts[0].values())
+    budget = min(free_host // (2 * max(world, 1)), 24 << 30) if free_host else 4 << 30
+    distinct = max(1, min(layers, budget // per_layer))
+    host_acts = [{k: v.cpu().pin_memory() for k, v in acts[i].items()} for i in range(distinct)]
+    host_w = [{k: v.cpu().pin_memory() for k, v in m.items()} for m in model]
+    host_out = [{name: (torch.empty((k // 2, n), dtype=torch.uint8).pin_memory(),
+                        torch.empty(n, dtype=torch.float32).pin_memory(),
+                        torch.empty(n, dtype=torch.float32).pin_memory()) for name, k, n in LINEARS}
+                for _ in range(layers)]
+    acts_dev_bytes = sum(v.numel() * 4 for a in acts for v in a.values())
+    del acts, model, x_big, batches
+    torch.cuda.empty_cache()
+    h2d = sum(host_acts[i % distinct][name].numel() * 4 + host_w[i][name].numel() * 4
+              for i in range(layers) for name, _, _ in LINEARS)
+    d2h = sum(sum(t.numel() * t.element_size() for t in host_out[i][name])
+              for i in range(layers) for name, _, _ in LINEARS)
+
+    def step_e2e():
+        for i in range(layers):
+            for name, _, _ in LINEARS:
+                xs = host_acts[i % distinct][name]
+                Q, params = G.gptq(host_w[i][name], list(xs.chunk(CALIB_BATCHES)),
+                                   block_size=BLOCK_SIZE, damping=DAMP)
+                qm = G.pack_matrix(Q, params)
+                p, s, z = host_out[i][name]
+                p.copy_(qm.int_weight, non_blocking=True)
+                s.copy_(qm.scale, non_blocking=True)
+                z.copy_(qm.zero, non_blocking=True)
+        torch.cuda.synchronize()
+
+    for _ in range(min(args.warmup, 3)):
+        step_e2e()
+    barrier()
+    e0.record()
+    for _ in range(args.steps):
+        step_e2e()
+    e1.record()
+    torch.cuda.synchronize()
+    t = torch.tensor([e0.elapsed_time(e1) / args.steps], device=dev, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    e2e_ms = float(t.item())
+    e2e = {'value': world * total_weights / (e2e_ms * 1e-3), 'unit': UNIT, 'ms_per_step': e2e_ms,
+           'h2d_bytes_per_step': h2d, 'd2h_bytes_per_step': d2h,
+           'distinct_activation_sets_in_pinned_memory': distinct}
+    del host_acts, host_w, host_out
+
+    # ---- packed-int4 matmul: HBM GB/s at M=1, TFLOP/s at M=2048 (single rank numbers) ----
+    w4 = []
+    if rank == 0 and not args.skip_matmul:
+        w4 = bench_w4(torch, G, dev, peaks)
+
+    cpu_baseline = None
+    if rank == 0 and world == 1 and not args.skip_cpu:
+        items = cpu_block_inputs(2002)
+        t0 = time.perf_counter()
+        cpu_block_step(items)
+        dt = time.perf_counter() - t0
+        cpu_baseline = {'value': sum(W.size for _, W, _ in items) / dt, 'unit': UNIT, 'cores': cpu_threads(),
+                        'kind': 'port', 'seconds': dt,
+                        'sample': 'one block (4 linears, 7.08 M weights), 65536 calibration tokens, NumPy/SciPy oracle'}
+
+    if rank == 0:
+        line = {'metric': METRIC, 'value': value, 'unit': UNIT, 'n_gpus': world, 'steps': args.steps,
+                'warmup': args.warmup, 'ms_per_step': ms_max, 'higher_is_better': True, 'scaling': 'weak',
+                'vs_baseline': None, 'dtype': 'f32', 'data': 'synthetic',
+                'config': {'workload': workload_name(layers), 'weights_per_step_per_gpu': total_weights,
+                           'l2': 'inputs larger than L2 (each linear reads 0.2-0.8 GB of activations)',
+                           'parallelism': f'{world} independent models, one per GPU, no data-path collective',
+                           'resident_activation_bytes_per_gpu': acts_dev_bytes, 'setup_seconds': setup_s},
+                'clocks': clocks, 'e2e': e2e, 'gpu_launches': int(launches), 'roofline': roofline,
+                'cpu_baseline': cpu_baseline, 'w4_matmul': w4}
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def bench_w4(torch, G, dev, peaks):
+    """Config-3 sweep on one GPU: fp16 activations, fp16 scale/zero; weights rotated over
+    enough distinct buffers to exceed L2 between launches."""
+    hbm = float(peaks.get('hbm_gbs', 6650.0))
+    tf = float(peaks.get('bf16_tflops_sustained', 1400.0))
+    out = []
+    gen = torch.Generator(device=dev).manual_seed(3003)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    for K, N in ((4096, 4096), (4096, 11008), (11008, 4096), (8192, 28672)):
+        wbytes = K * N // 2
+        nbuf = max(2, -(-(300 << 20) // wbytes))
+        packed = [torch.randint(0, 256, (K // 2, N), generator=gen, device=dev, dtype=torch.uint8) for _ in range(nbuf)]
+        scale = (0.001 + 0.019 * torch.rand(N, generator=gen, device=dev)).half()
+        zero = torch.randint(0, 16, (N,), generator=gen, device=dev).half()
+        qms = [G.QuantizedMatrix(p, zero, scale) for p in packed]
+        for M in (1, 16, 128, 2048):
+            x = torch.randn((M, K), generator=gen, device=dev).half()
+            iters = 20 if M <= 128 else 3
+            for i in range(3):
+                G.quantized_matmul(x, qms[i % nbuf])
+            torch.cuda.synchronize()
+            e0.record()
+            for i in range(iters):
+                G.quantized_matmul(x, qms[i % nbuf])
+            e1.record()
+            torch.cuda.synchronize()
+            ms = e0.elapsed_time(e1) / iters
+            bytes_alg = wbytes + 4 * N + 2 * M * K + 2 * M * N
+            gbs = bytes_alg / (ms * 1e-3) / 1e9
+            tflops = 2.0 * M * K * N / (ms * 1e-3) / 1e12
+            out.append({'K': K, 'N': N, 'M': M, 'us': ms * 1e3, 'GBps': gbs, 'hbm_frac': gbs / hbm,
+                        'TFLOPs': tflops, 'tensor_frac': tflops / tf})
+        del packed, qms
+        torch.cuda.empty_cache()
+    return out
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument('--gpus', type=int, default=1)
+    ap.add_argument('--steps', type=int, default=3)
+    ap.add_argument('--warmup', type=int, default=3)
+    ap.add_argument('--impl', default='ours', choices=['ours', 'reference'])
+    ap.add_argument('--layers', type=int, default=N_LAYERS, help='blocks to quantize (12 = the full workload)')
+    ap.add_argument('--skip-matmul', action='store_true')
+    ap.add_argument('--skip-cpu', action='store_true')
+    args = ap.parse_args()
+    if args.impl == 'reference':
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == '__main__':
+    main()

@@ -47,6 +47,8 @@ enum { JGQ_STATUS_NOT_PD = 1, JGQ_STATUS_NAN = 2, JGQ_STATUS_TIMEOUT = 4 };
 
 int jgq_version(void);
 const char* jgq_last_error(void);
+/* number of kernels this library has enqueued since it was loaded (all threads) */
+uint64_t jgq_launch_count(void);
 
 /* ---- int4 pack / unpack ---------------------------------------------------
  * The array is viewed as (outer, axis_len, inner) with the packed axis in the

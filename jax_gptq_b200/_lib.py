@@ -20,6 +20,7 @@ _i64, _int, _vp, _sz = C.c_int64, C.c_int, C.c_void_p, C.c_size_t
 SIGNATURES = {
     'jgq_version': (_int, []),
     'jgq_last_error': (C.c_char_p, []),
+    'jgq_launch_count': (C.c_uint64, []),
     'jgq_pack_int4': (_int, [_vp, _int, _vp, _i64, _i64, _i64, _vp]),
     'jgq_unpack_int4': (_int, [_vp, _vp, _i64, _i64, _i64, _vp]),
     'jgq_pack_matrix': (_int, [_vp, _int, _vp, _vp, _vp, _i64, _i64, _i64, _vp]),

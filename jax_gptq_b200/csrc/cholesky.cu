@@ -247,13 +247,16 @@ extern "C" int jgq_damp_invert(float* W, int64_t N, float* H, int64_t K, float d
   float* X = H;   // H's storage is reused for the triangular inverse once A is built
 
   diag_stats_kernel<<<1, 1024, 0, s>>>(H, Ki, damping, dead, damp_add);
+  JGQ_LAUNCHED();
   {
     dim3 blk(32, 8), grd((unsigned)cdiv(K, 32), (unsigned)cdiv(K, 8));
     build_reversed_kernel<<<grd, blk, 0, s>>>(H, Ki, dead, damp_add, A);
+    JGQ_LAUNCHED();
   }
   if (N > 0) {
     dim3 grd((unsigned)std::min<int64_t>(cdiv(N, 256), 64), (unsigned)K);
     zero_dead_rows_kernel<<<grd, 256, 0, s>>>(W, Ki, N, dead);
+    JGQ_LAUNCHED();
   }
   if (cudaMemsetAsync(X, 0, (size_t)K * K * sizeof(float), s) != cudaSuccess)
     return fail(JGQ_ERR_CUDA, "damp_invert: memset failed");
@@ -264,8 +267,9 @@ extern "C" int jgq_damp_invert(float* W, int64_t N, float* H, int64_t K, float d
     const int below = Ki - r1;
     const int nb = std::min(CB, Ki - kb * CB);
     potrf_diag_kernel<<<1, 256, 0, s>>>(A, X, Ki, kb, dev_status);
-    if (below > 0) trsm_panel_kernel<<<(unsigned)cdiv(below, CB), 256, 0, s>>>(A, X, Ki, kb);
-    if (kb > 0) trtri_row_kernel<<<(unsigned)kb, 256, 0, s>>>(X, Ki, kb);
+    JGQ_LAUNCHED();
+    if (below > 0) { trsm_panel_kernel<<<(unsigned)cdiv(below, CB), 256, 0, s>>>(A, X, Ki, kb); JGQ_LAUNCHED(); }
+    if (kb > 0) { trtri_row_kernel<<<(unsigned)kb, 256, 0, s>>>(X, Ki, kb); JGQ_LAUNCHED(); }
     if (below > 0) {
       const float* P = A + (int64_t)r1 * K + (int64_t)kb * CB;
       int rc = launch_sgemm(true, true, P, K, P, K, A + (int64_t)r1 * K + r1, K,

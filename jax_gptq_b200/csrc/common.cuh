@@ -24,8 +24,13 @@ inline int fail(int code, const char* fmt, ...) {
 #define JGQ_REQUIRE(cond, code, ...) \
   do { if (!(cond)) return ::jgq::fail((code), __VA_ARGS__); } while (0)
 
-// Called after each launch: reports (and clears) a launch-configuration error.
+// Kernel launches enqueued by this library since load (read by jgq_launch_count()).
+void note_launches(int n);
+#define JGQ_LAUNCHED() ::jgq::note_launches(1)
+
+// Called after each launch: counts it and reports (and clears) a launch-configuration error.
 inline int check_launch(const char* what) {
+  note_launches(1);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return fail(JGQ_ERR_CUDA, "%s: %s", what, cudaGetErrorString(e));
   return JGQ_OK;

@@ -104,6 +104,7 @@ extern "C" int jgq_hessian_accum(const void* X, int x_dtype, int64_t n, int64_t 
     const int blocks = (int)std::min<int64_t>(cdiv(total, 256), (int64_t)sm_count() * 16);
     if (x_dtype == JGQ_F16) to_f32_kernel<__half><<<blocks, 256, 0, s>>>((const __half*)X, conv, total);
     else                    to_f32_kernel<__nv_bfloat16><<<blocks, 256, 0, s>>>((const __nv_bfloat16*)X, conv, total);
+    JGQ_LAUNCHED();
     Xf = conv;
   }
   if (splits == 1) {
