@@ -226,7 +226,7 @@ def run_ours(args):
         def quantize_in_place(name, W, x):
             xs = x.reshape(-1, x.shape[-1]).contiguous()
             captured[name] = xs
-            Q, _ = G.gptq(W, list(xs.chunk(CALIB_BATCHES)), block_size=BLOCK_SIZE, damping=DAMP)
+            Q, _ = gg.gptq(W, list(xs.chunk(CALIB_BATCHES)), block_size=BLOCK_SIZE, damping=DAMP)
             return Q
         h = block_forward(torch, h, weights, quantize_in_place)
         model.append(weights)
@@ -240,7 +240,7 @@ def run_ours(args):
         out = []
         for weights, captured in zip(model, acts):
             for name, _, _ in LINEARS:
-                Q, params = G.gptq(weights[name], list(captured[name].chunk(CALIB_BATCHES)),
+                Q, params = gg.gptq(weights[name], list(captured[name].chunk(CALIB_BATCHES)),
                                    block_size=BLOCK_SIZE, damping=DAMP)
                 out.append(G.pack_matrix(Q, params))
         return out
@@ -326,7 +326,7 @@ def run_ours(args):
         for i in range(layers):
             for name, _, _ in LINEARS:
                 xs = host_acts[i % distinct][name]
-                Q, params = G.gptq(host_w[i][name], list(xs.chunk(CALIB_BATCHES)),
+                Q, params = gg.gptq(host_w[i][name], list(xs.chunk(CALIB_BATCHES)),
                                    block_size=BLOCK_SIZE, damping=DAMP)
                 qm = G.pack_matrix(Q, params)
                 p, s, z = host_out[i][name]

@@ -8,7 +8,7 @@ without the library raises ImportError - there is no fallback path.
 """
 import importlib
 
-_GPTQ_NAMES = ('QuantizedMatrix', 'accumulate_H', 'get_col_quantize_params', 'gptq', 'pack_matrix',
+_GPTQ_NAMES = ('QuantizedMatrix', 'accumulate_H', 'get_col_quantize_params', 'pack_matrix',
                'unpack_matrix', 'pack_along_axis', 'unpack_along_axis', 'pack_rowwise', 'pack_colwise',
                'unpack_rowwise', 'unpack_colwise', 'quant_matrix_shape')
 _OP_NAMES = ('quantized_matmul',)
@@ -20,12 +20,14 @@ def _load_public():
     o = importlib.import_module(__name__ + '.op')
     ns = globals()
     for n in _GPTQ_NAMES:
-        ns[n] = getattr(g, n)       # `gptq` now names the function, as in the reference's namespace
+        ns[n] = getattr(g, n)
     for n in _OP_NAMES:
         ns[n] = getattr(o, n)
 
 
 def __getattr__(name):
+    if name in ('gptq', 'op'):      # submodules, as in the reference: jax_gptq.gptq.gptq(W, xs)
+        return importlib.import_module(__name__ + '.' + name)
     if name in __all__:
         _load_public()
         return globals()[name]

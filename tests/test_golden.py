@@ -80,8 +80,8 @@ def _dev(a):
 def test_cuda_against_golden():
     import importlib
     import torch
-    import jax_gptq_b200 as G
     gg = importlib.import_module('jax_gptq_b200.gptq')
+    G = gg
     for pre in ('lit', 'par'):
         p = G.get_col_quantize_params(_dev(GOLD[f'{pre}_W']))
         assert np.array_equal(p['scale'].cpu().numpy(), GOLD[f'{pre}_scale'])

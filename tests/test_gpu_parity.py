@@ -15,8 +15,13 @@ pytestmark = pytest.mark.gpu
 
 @pytest.fixture(scope='module')
 def G():
-    import jax_gptq_b200 as g
-    return g
+    import importlib
+    import types
+    mod = importlib.import_module('jax_gptq_b200.gptq')
+    op = importlib.import_module('jax_gptq_b200.op')
+    ns = types.SimpleNamespace(**{k: getattr(mod, k) for k in dir(mod) if not k.startswith('__')})
+    ns.quantized_matmul = op.quantized_matmul
+    return ns
 
 
 def dev(a):
