@@ -297,6 +297,32 @@ def run_ours(args):
                 'peak_source': 'MEASURED_PEAKS.json bf16_tflops_sustained' if peaks else 'fallback 1.4 PFLOP/s sustained',
                 'launches_per_hessian': h_launches, 'ms_per_hessian': h_ms, 'traffic': None}
 
+    # ---- per-stage device time of one block (explains `value`; not part of it) ----
+    stages = {}
+
+    def timed(label, fn):
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        r = fn()
+        b.record()
+        torch.cuda.synchronize()
+        stages[label] = stages.get(label, 0.0) + a.elapsed_time(b)
+        return r
+    for rep in range(2):              # first pass warms up, second is recorded
+        stages.clear()
+        for name, k, n in LINEARS:
+            xs_l = list(acts[0][name].chunk(CALIB_BATCHES))
+            Wf = model[0][name].clone()
+            tag = f'K{k}xN{n}'
+            p = timed(f'{tag}.col_params', lambda: gg._col_params(Wf))
+            Hn = timed(f'{tag}.hessian', lambda: gg._accumulate_raw(xs_l))
+            Hf = timed(f'{tag}.finalize', lambda: gg._finalize_H(*Hn))
+            Ls = timed(f'{tag}.damp_invert', lambda: gg._damp_and_invert(Wf, Hf, DAMP))
+            Qc = timed(f'{tag}.quantize', lambda: gg._quantize(Wf, Ls[0], p, BLOCK_SIZE, torch.float32))
+            timed(f'{tag}.pack', lambda: G.pack_matrix(Qc[0], p))
+    stages = {k2: round(v, 4) for k2, v in stages.items()}
+
     # ---- e2e: pinned host buffers in, packed result out, all copies inside the timed region ----
     free_host = 0
     try:
@@ -376,7 +402,7 @@ def run_ours(args):
                            'parallelism': f'{world} independent models, one per GPU, no data-path collective',
                            'resident_activation_bytes_per_gpu': acts_dev_bytes, 'setup_seconds': setup_s},
                 'clocks': clocks, 'e2e': e2e, 'gpu_launches': int(launches), 'roofline': roofline,
-                'cpu_baseline': cpu_baseline, 'w4_matmul': w4}
+                'cpu_baseline': cpu_baseline, 'stage_ms_one_block': stages, 'w4_matmul': w4}
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()
@@ -387,7 +413,7 @@ def bench_w4(torch, G, dev, peaks):
     enough distinct buffers to exceed L2 between launches."""
     hbm = float(peaks.get('hbm_gbs', 6650.0))
     tf = float(peaks.get('bf16_tflops_sustained', 1400.0))
-    out = []
+    rows = []
     gen = torch.Generator(device=dev).manual_seed(3003)
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     for K, N in ((4096, 4096), (4096, 11008), (11008, 4096), (8192, 28672)):
@@ -400,23 +426,35 @@ def bench_w4(torch, G, dev, peaks):
         for M in (1, 16, 128, 2048):
             x = torch.randn((M, K), generator=gen, device=dev).half()
             iters = 20 if M <= 128 else 3
+            # launched straight through the C ABI so that host-side Python time does not
+            # leave the GPU idle between these microsecond-scale kernels
+            from jax_gptq_b200 import _lib
+            need = _lib.lib.jgq_w4_matmul_workspace_bytes(M, N, K, 0)
+            ws = torch.zeros(max(need, 1), dtype=torch.uint8, device=dev)
+            out = torch.empty((M, N), dtype=torch.float16, device=dev)
+            st = torch.cuda.current_stream().cuda_stream
+
+            def launch(i):
+                _lib.check(_lib.lib.jgq_w4_matmul(x.data_ptr(), _lib.F16, packed[i % nbuf].data_ptr(), zero.data_ptr(),
+                                                  scale.data_ptr(), _lib.F16, out.data_ptr(), M, N, K, 0,
+                                                  ws.data_ptr(), need, st))
             for i in range(3):
-                G.quantized_matmul(x, qms[i % nbuf])
+                launch(i)
             torch.cuda.synchronize()
             e0.record()
             for i in range(iters):
-                G.quantized_matmul(x, qms[i % nbuf])
+                launch(i)
             e1.record()
             torch.cuda.synchronize()
             ms = e0.elapsed_time(e1) / iters
             bytes_alg = wbytes + 4 * N + 2 * M * K + 2 * M * N
             gbs = bytes_alg / (ms * 1e-3) / 1e9
             tflops = 2.0 * M * K * N / (ms * 1e-3) / 1e12
-            out.append({'K': K, 'N': N, 'M': M, 'us': ms * 1e3, 'GBps': gbs, 'hbm_frac': gbs / hbm,
+            rows.append({'K': K, 'N': N, 'M': M, 'us': ms * 1e3, 'GBps': gbs, 'hbm_frac': gbs / hbm,
                         'TFLOPs': tflops, 'tensor_frac': tflops / tf})
         del packed, qms
         torch.cuda.empty_cache()
-    return out
+    return rows
 
 
 def main():
