@@ -117,6 +117,24 @@ int jgq_w4_matmul(const void* x, int x_dtype, const uint8_t* packed,
                   void* out, int64_t M, int64_t N, int64_t K, int transpose_b,
                   void* ws, size_t ws_bytes, void* stream);
 
+/* ---- forward matmul without a caller workspace ----------------------------
+ * (No counterpart in the reference: an addition for hosts that cannot hand this
+ * library any scratch memory - a framework-owned custom-call handler with no
+ * scratch result declared, a serving loop that must stay clear of the device
+ * allocator, code whose stream is being recorded.)
+ * Same result as jgq_w4_matmul(..., transpose_b = 0, ...).  The split-K scratch
+ * is a fixed array of jgq_w4_matmul_noalloc_max_bytes() bytes inside the library,
+ * resident on every GPU that loads it.  The call allocates nothing and frees
+ * nothing.  Shapes whose scratch need (jgq_w4_matmul_workspace_bytes) exceeds the
+ * array are refused with JGQ_ERR_LIMIT.  The first call on each device looks up
+ * the array's device address; make that first call outside any stream capture.
+ * Every call on a device shares the array: calls that can overlap on the GPU
+ * (different streams) race - keep them on one stream. */
+size_t jgq_w4_matmul_noalloc_max_bytes(void);
+int jgq_w4_matmul_noalloc(const void* x, int x_dtype, const uint8_t* packed,
+                          const void* zero, const void* scale, int zs_dtype,
+                          void* out, int64_t M, int64_t N, int64_t K, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

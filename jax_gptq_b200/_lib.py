@@ -35,6 +35,8 @@ SIGNATURES = {
     'jgq_gptq_quantize': (_int, [_vp, _vp, _vp, _vp, _i64, _i64, _int, _int, _vp, _int, _vp, _vp, _sz, _vp]),
     'jgq_w4_matmul_workspace_bytes': (_sz, [_i64, _i64, _i64, _int]),
     'jgq_w4_matmul': (_int, [_vp, _int, _vp, _vp, _vp, _int, _vp, _i64, _i64, _i64, _int, _vp, _sz, _vp]),
+    'jgq_w4_matmul_noalloc_max_bytes': (_sz, []),
+    'jgq_w4_matmul_noalloc': (_int, [_vp, _int, _vp, _vp, _vp, _int, _vp, _i64, _i64, _i64, _vp]),
 }
 
 

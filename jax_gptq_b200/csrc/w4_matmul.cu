@@ -27,6 +27,7 @@
 #include "common.cuh"
 #include <type_traits>
 #include <algorithm>
+#include <mutex>
 
 namespace jgq {
 
@@ -452,4 +453,73 @@ extern "C" int jgq_w4_matmul(const void* x, int x_dtype, const uint8_t* packed,
   if (x_dtype == JGQ_F16) { JGQ_FWD(__half, __half); }
   JGQ_FWD(__nv_bfloat16, __nv_bfloat16);
 #undef JGQ_FWD
+}
+
+// ---------------------------------------------------------------------------
+// Forward matmul for callers that cannot supply scratch memory.
+//
+// Some hosts of this library have no way to obtain device memory at the point
+// where they call in: a foreign-function handler whose framework owns every
+// buffer and was not told to reserve a scratch result, a serving loop that
+// must not touch the allocator because an allocation may synchronise the whole
+// device, or code running while its stream is being recorded.  For them the
+// split-K slices and tickets of the forward kernel live in one fixed array
+// inside the library image instead of a caller-provided workspace.
+//
+// The array costs kNoAllocScratchBytes of device memory on every GPU that loads
+// the library, for the life of the process.  All calls on a device share it and
+// it keeps whatever the previous call left there: the ticket words are cleared
+// on the stream before every launch, the slices are fully rewritten before they
+// are read.  Two calls whose kernels may overlap on the GPU (different streams)
+// would race on the array; issue them on one stream or serialise them.
+// ---------------------------------------------------------------------------
+namespace jgq {
+
+constexpr size_t kNoAllocScratchBytes = 8u << 20;
+static __device__ __align__(256) unsigned char g_w4_scratch[kNoAllocScratchBytes];
+
+// Device address of g_w4_scratch for the current device.  In host code the symbol
+// is only a handle; the address a kernel can use comes from cudaGetSymbolAddress,
+// asked for once per device with that device current.
+static int w4_scratch_address(void** out) {
+  static std::mutex mu;
+  static void* addr[64] = {nullptr};
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return fail(JGQ_ERR_CUDA, "w4_matmul_noalloc: cudaGetDevice: %s", cudaGetErrorString(e));
+  if (dev < 0 || dev >= 64) return fail(JGQ_ERR_LIMIT, "w4_matmul_noalloc: device index %d not supported", dev);
+  std::lock_guard<std::mutex> lock(mu);
+  if (addr[dev] == nullptr) {
+    void* p = nullptr;
+    e = cudaGetSymbolAddress(&p, g_w4_scratch);
+    if (e != cudaSuccess || p == nullptr)
+      return fail(JGQ_ERR_CUDA, "w4_matmul_noalloc: cudaGetSymbolAddress: %s", cudaGetErrorString(e));
+    addr[dev] = p;
+  }
+  *out = addr[dev];
+  return JGQ_OK;
+}
+
+}  // namespace jgq
+
+extern "C" size_t jgq_w4_matmul_noalloc_max_bytes(void) { return jgq::kNoAllocScratchBytes; }
+
+extern "C" int jgq_w4_matmul_noalloc(const void* x, int x_dtype, const uint8_t* packed,
+                                     const void* zero, const void* scale, int zs_dtype,
+                                     void* out, int64_t M, int64_t N, int64_t K, void* stream) {
+  JGQ_REQUIRE(M >= 0 && N > 0 && K > 0, JGQ_ERR_ARG, "w4_matmul_noalloc: bad shape M=%lld N=%lld K=%lld",
+              (long long)M, (long long)N, (long long)K);
+  if (M == 0) return JGQ_OK;
+  const size_t need = jgq_w4_matmul_workspace_bytes(M, N, K, 0);
+  JGQ_REQUIRE(need <= kNoAllocScratchBytes, JGQ_ERR_LIMIT,
+              "w4_matmul_noalloc: M=%lld N=%lld K=%lld needs %zu bytes of scratch, the built-in array holds %zu; "
+              "use jgq_w4_matmul with a caller-provided workspace",
+              (long long)M, (long long)N, (long long)K, need, (size_t)kNoAllocScratchBytes);
+  void* ws = nullptr;
+  const int rc = w4_scratch_address(&ws);
+  if (rc) return rc;
+  // tickets must read zero when the kernel starts, whatever an earlier call left behind
+  cudaError_t e = cudaMemsetAsync(ws, 0, kTicketBytes, (cudaStream_t)stream);
+  if (e != cudaSuccess) return fail(JGQ_ERR_CUDA, "w4_matmul_noalloc: cudaMemsetAsync: %s", cudaGetErrorString(e));
+  return jgq_w4_matmul(x, x_dtype, packed, zero, scale, zs_dtype, out, M, N, K, 0, ws, kNoAllocScratchBytes, stream);
 }
