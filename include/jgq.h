@@ -80,10 +80,12 @@ int jgq_col_params(const float* W, int64_t K, int64_t N, int maxq,
  * H (K x K fp32, lower triangle significant until finalize) += X^T X for one
  * calibration batch X of n rows (x_dtype F32/F16/BF16, row-major n x K).
  * jgq_hessian_finalize divides by the total sample count and mirrors the
- * lower triangle, giving (1/n) sum x x^T, which accumulate_H returns. */
+ * lower triangle, giving (1/n) sum x x^T, which accumulate_H returns.
+ * dev_status (may be null) receives JGQ_STATUS_TIMEOUT if a bounded device-side
+ * wait of the tensor-core kernel ran out. */
 size_t jgq_hessian_workspace_bytes(int64_t n, int64_t K, int x_dtype);
 int jgq_hessian_accum(const void* X, int x_dtype, int64_t n, int64_t K, float* H,
-                      void* ws, size_t ws_bytes, void* stream);
+                      void* ws, size_t ws_bytes, int32_t* dev_status, void* stream);
 int jgq_hessian_finalize(float* H, int64_t K, double n_total, void* stream);
 
 /* ---- damping + Cholesky factor of the inverse (gptq.py:44-48, 155-168) ----

@@ -27,7 +27,7 @@ SIGNATURES = {
     'jgq_unpack_matrix': (_int, [_vp, _vp, _vp, _vp, _int, _i64, _i64, _i64, _vp]),
     'jgq_col_params': (_int, [_vp, _i64, _i64, _int, _vp, _vp, _vp]),
     'jgq_hessian_workspace_bytes': (_sz, [_i64, _i64, _int]),
-    'jgq_hessian_accum': (_int, [_vp, _int, _i64, _i64, _vp, _vp, _sz, _vp]),
+    'jgq_hessian_accum': (_int, [_vp, _int, _i64, _i64, _vp, _vp, _sz, _vp, _vp]),
     'jgq_hessian_finalize': (_int, [_vp, _i64, C.c_double, _vp]),
     'jgq_damp_invert_workspace_bytes': (_sz, [_i64]),
     'jgq_damp_invert': (_int, [_vp, _i64, _vp, _i64, C.c_float, _vp, _vp, _sz, _vp, _vp]),

@@ -69,12 +69,26 @@ static int hessian_splits(int64_t n, int64_t K) {
   return (int)std::max<int64_t>(1, s);
 }
 
+// tensor-core path (hessian_umma.cu)
+struct HessPlan { int use; int planes; int nseg; int S; int tokens_per_slice; size_t plane_bytes; size_t part_bytes; };
+HessPlan plan_hessian_umma(int64_t n, int64_t K, int x_dtype);
+int launch_hessian_umma(const HessPlan& pl, const void* X, int x_dtype, int64_t n, int64_t K, float* H, void* ws,
+                        int32_t* status, cudaStream_t s);
+
+static size_t simt_workspace_bytes(int64_t n, int64_t K, int x_dtype);
+
 }  // namespace jgq
 
 using namespace jgq;
 
 extern "C" size_t jgq_hessian_workspace_bytes(int64_t n, int64_t K, int x_dtype) {
   if (n <= 0 || K <= 0) return 0;
+  const HessPlan pl = plan_hessian_umma(n, K, x_dtype);
+  const size_t simt = simt_workspace_bytes(n, K, x_dtype);
+  return pl.use ? std::max(simt, 2 * pl.plane_bytes + pl.part_bytes) : simt;
+}
+
+static size_t jgq::simt_workspace_bytes(int64_t n, int64_t K, int x_dtype) {
   size_t bytes = 0;
   const int splits = hessian_splits(n, K);
   if (splits > 1) bytes += align_up((size_t)splits * K * K * sizeof(float), 256);
@@ -83,7 +97,7 @@ extern "C" size_t jgq_hessian_workspace_bytes(int64_t n, int64_t K, int x_dtype)
 }
 
 extern "C" int jgq_hessian_accum(const void* X, int x_dtype, int64_t n, int64_t K, float* H,
-                                 void* ws, size_t ws_bytes, void* stream) {
+                                 void* ws, size_t ws_bytes, int32_t* dev_status, void* stream) {
   JGQ_REQUIRE(x_dtype == JGQ_F32 || x_dtype == JGQ_F16 || x_dtype == JGQ_BF16, JGQ_ERR_ARG,
               "hessian_accum: X dtype must be f32/f16/bf16");
   JGQ_REQUIRE(K > 0 && n >= 0, JGQ_ERR_ARG, "hessian_accum: bad shape n=%lld K=%lld", (long long)n, (long long)K);
@@ -95,6 +109,18 @@ extern "C" int jgq_hessian_accum(const void* X, int x_dtype, int64_t n, int64_t 
               "hessian_accum: workspace %zu < %zu bytes", ws_bytes, need);
   JGQ_REQUIRE(need == 0 || aligned(ws, 256), JGQ_ERR_ALIGN, "hessian_accum: workspace must be 256-byte aligned");
   cudaStream_t s = (cudaStream_t)stream;
+  const HessPlan pl = plan_hessian_umma(n, K, x_dtype);
+  if (pl.use && aligned(X, 16) && aligned(H, 16)) {
+    int rc = launch_hessian_umma(pl, X, x_dtype, n, K, H, ws, dev_status, s);
+    if (rc) return rc;
+    if (pl.S > 1) {
+      const float* part = (const float*)((const char*)ws + 2 * pl.plane_bytes);
+      dim3 blk(32, 8), grd((unsigned)cdiv(K, 32), (unsigned)cdiv(K, 8));
+      reduce_splits_kernel<<<grd, blk, 0, s>>>(H, part, (int)K, pl.S);
+      return check_launch("hessian_reduce");
+    }
+    return JGQ_OK;
+  }
   const int splits = hessian_splits(n, K);
   float* part = (float*)ws;
   const float* Xf = (const float*)X;

@@ -1,0 +1,294 @@
+// Hessian accumulation H += X^T X on the Blackwell tensor path (tcgen05 + TMEM + TMA).
+//
+// Both operands of X^T X are the calibration batch itself, read "M/N-major": a
+// TMA box of 64 features x 32 tokens lands in shared memory as 32 rows of 128
+// bytes (128-byte swizzle), which is exactly the canonical MN-major operand
+// layout of tcgen05.mma - no transpose anywhere.
+//
+// fp32 batches are first split into two bf16 planes, x = b1 + b2 + O(2^-17 |x|),
+// and each 16-token step issues three MMAs, b1^T b1 + b1^T b2 + b2^T b1, into the
+// same fp32 TMEM accumulator (the dropped b2^T b2 term is O(2^-18)).  bf16 / fp16
+// batches are used as they are, one MMA per step, products exact.
+//
+// Work decomposition: H is symmetric, only blocks on or below the diagonal are
+// produced.  A CTA owns a 128-row panel x a segment of up to 256 columns (one
+// 128 x 256 fp32 accumulator = 256 TMEM columns) and a slice of the token range.
+// Token slices exist only to fill the 148 SMs evenly; their results go to
+// separate buffers that are summed in slice order (no floating-point atomics).
+//
+// Roles inside a CTA (192 threads): warp 0 = TMA producer, warp 1 = MMA issuer
+// (one elected lane each, 4-stage mbarrier ring), warps 2-5 = epilogue
+// (TMEM -> registers -> global).
+#include "umma.cuh"
+#include <algorithm>
+#include <cstdlib>
+#include <cstring>
+
+namespace jgq {
+
+constexpr int HT_M = 128, HT_N = 256, HT_BK = 32, HT_STAGES = 4, HT_THREADS = 192;
+constexpr int HT_BOX_BYTES = 64 * HT_BK * 2;                 // 64 features x 32 tokens x 2 B = 4096
+constexpr int HT_PLANE_BYTES = (2 + 4) * HT_BOX_BYTES;       // A: 2 boxes, B: up to 4 boxes
+constexpr int HT_STAGE_BYTES = 2 * HT_PLANE_BYTES;           // two planes
+constexpr int HT_SMEM_BYTES = HT_STAGES * HT_STAGE_BYTES + 1024 /*alignment*/ + 256 /*barriers*/;
+
+struct HessParams {
+  int K, n, planes, fmt;
+  int nseg, S, tokens_per_slice;
+  float* out;              // H (S == 1, accumulated into) or slice buffers (S > 1, overwritten)
+  int64_t slice_stride;    // elements between slice buffers
+  int32_t* status;
+};
+
+template <typename T>
+__global__ void split_bf16_kernel(const T* __restrict__ X, __nv_bfloat16* __restrict__ P0,
+                                  __nv_bfloat16* __restrict__ P1, int64_t total4) {
+  for (int64_t t = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; t < total4;
+       t += (int64_t)gridDim.x * blockDim.x) {
+    const float4 v = reinterpret_cast<const float4*>(X)[t];
+    const float x[4] = {v.x, v.y, v.z, v.w};
+    __nv_bfloat16 hi[4], lo[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      hi[i] = __float2bfloat16_rn(x[i]);
+      lo[i] = __float2bfloat16_rn(x[i] - __bfloat162float(hi[i]));
+    }
+    uint2 h, l;
+    h.x = (uint32_t)__bfloat16_as_ushort(hi[0]) | ((uint32_t)__bfloat16_as_ushort(hi[1]) << 16);
+    h.y = (uint32_t)__bfloat16_as_ushort(hi[2]) | ((uint32_t)__bfloat16_as_ushort(hi[3]) << 16);
+    l.x = (uint32_t)__bfloat16_as_ushort(lo[0]) | ((uint32_t)__bfloat16_as_ushort(lo[1]) << 16);
+    l.y = (uint32_t)__bfloat16_as_ushort(lo[2]) | ((uint32_t)__bfloat16_as_ushort(lo[3]) << 16);
+    reinterpret_cast<uint2*>(P0)[t] = h;
+    reinterpret_cast<uint2*>(P1)[t] = l;
+  }
+}
+
+__global__ void __launch_bounds__(HT_THREADS, 1)
+hessian_umma_kernel(const __grid_constant__ CUtensorMap map0, const __grid_constant__ CUtensorMap map1,
+                    const HessParams p) {
+  using namespace umma;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + HT_STAGES * HT_STAGE_BYTES);
+  uint64_t* empty_bar = full_bar + HT_STAGES;
+  uint64_t* acc_bar = empty_bar + HT_STAGES;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_bar + 1);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+  // ---- which panel / segment / token slice ----
+  const int slice = blockIdx.x / p.nseg;
+  int seg = blockIdx.x % p.nseg;
+  int I = 0;
+  while (true) {
+    const int cnt = (I + 2) / 2;          // segments of panel I = ceil((I + 1) / 2)
+    if (seg < cnt) break;
+    seg -= cnt;
+    ++I;
+  }
+  const int row0 = I * HT_M;
+  const int col0 = seg * HT_N;
+  const int width = min(HT_N, (I + 1) * HT_M - col0);     // 128 or 256
+  const int groups_b = width / 64;
+  const int tok0 = slice * p.tokens_per_slice;
+  const int tok_end = min(p.n, tok0 + p.tokens_per_slice);
+  const int nchunks = (tok_end - tok0 + HT_BK - 1) / HT_BK;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < HT_STAGES; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
+    mbar_init(acc_bar, 1);
+    *abort_flag = 0;
+    fence_barrier_init();
+    prefetch_tensormap(&map0);
+    if (p.planes > 1) prefetch_tensormap(&map1);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, HT_N);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_acc = *tmem_slot;
+
+  if (warp == 0) {
+    // ===================== TMA producer =====================
+    if (lane == 0) {
+      const uint32_t stage_tx = (uint32_t)(p.planes * (2 + groups_b) * HT_BOX_BYTES);
+      int issued = 0;
+      for (int kc = 0; kc < nchunks; ++kc) {
+        const int st = kc % HT_STAGES;
+        if (kc >= HT_STAGES && !mbar_wait(&empty_bar[st], ((kc / HT_STAGES) & 1) ^ 1, abort_flag)) break;
+        mbar_expect_tx(&full_bar[st], stage_tx);
+        const int tok = tok0 + kc * HT_BK;
+        uint8_t* sb = smem + st * HT_STAGE_BYTES;
+        for (int pl = 0; pl < p.planes; ++pl) {
+          const CUtensorMap* m = pl == 0 ? &map0 : &map1;
+          uint8_t* pb = sb + pl * HT_PLANE_BYTES;
+          tma_load_2d(pb + 0 * HT_BOX_BYTES, m, row0, tok, &full_bar[st]);
+          tma_load_2d(pb + 1 * HT_BOX_BYTES, m, row0 + 64, tok, &full_bar[st]);
+          for (int g = 0; g < groups_b; ++g)
+            tma_load_2d(pb + (2 + g) * HT_BOX_BYTES, m, col0 + 64 * g, tok, &full_bar[st]);
+        }
+        issued = kc + 1;
+      }
+      if (*abort_flag) {
+        // let copies that are still in flight land before the CTA gives its shared memory back
+        for (int kc = max(0, issued - HT_STAGES); kc < issued; ++kc) {
+          const long long t0 = clock64();
+          while (!mbar_try_wait(&full_bar[kc % HT_STAGES], (kc / HT_STAGES) & 1) && clock64() - t0 < 20000000LL) {}
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ===================== MMA issuer =====================
+    if (lane == 0) {
+      const uint32_t idesc = make_idesc_f16(p.fmt, 1, 1, HT_M, width);
+      const int nterms = p.planes > 1 ? 3 : 1;
+      bool ok = true;
+      for (int kc = 0; kc < nchunks && ok; ++kc) {
+        const int st = kc % HT_STAGES;
+        ok = mbar_wait(&full_bar[st], (kc / HT_STAGES) & 1, abort_flag);
+        if (!ok) break;
+        tc_fence_after();
+        const uint32_t sb = smem_u32(smem + st * HT_STAGE_BYTES);
+#pragma unroll
+        for (int k16 = 0; k16 < HT_BK / 16; ++k16) {
+          for (int t = 0; t < nterms; ++t) {
+            const int pa = (t == 2) ? 1 : 0, pbn = (t == 1) ? 1 : 0;     // (0,0) (0,1) (1,0)
+            const uint64_t da = make_desc_sw128(sb + pa * HT_PLANE_BYTES + k16 * 2048, HT_BOX_BYTES, 1024);
+            const uint64_t db = make_desc_sw128(sb + pbn * HT_PLANE_BYTES + 2 * HT_BOX_BYTES + k16 * 2048,
+                                                HT_BOX_BYTES, 1024);
+            mma_f16_ss(tmem_acc, da, db, idesc, (kc > 0 || k16 > 0 || t > 0) ? 1u : 0u);
+          }
+        }
+        mma_commit(&empty_bar[st]);     // frees the stage once these MMAs have read it
+      }
+      if (ok) mma_commit(acc_bar);
+    }
+  } else {
+    // ===================== epilogue: TMEM -> global =====================
+    const bool ok = __all_sync(0xffffffffu, mbar_wait(acc_bar, 0, abort_flag));
+    tc_fence_after();
+    if (ok) {
+      const int q = warp & 3;                       // TMEM lane quarter this warp may read
+      const int i = row0 + 32 * q + lane;
+      float* out = p.out + (int64_t)slice * p.slice_stride;
+      for (int c = 0; c < width; c += 32) {
+        uint32_t r[32];
+        tmem_ld_32x32(tmem_acc + ((uint32_t)(32 * q) << 16) + (uint32_t)c, r);
+        tmem_ld_wait();
+        if (i < p.K) {
+          float* dst = out + (int64_t)i * p.K + col0 + c;
+#pragma unroll
+          for (int v = 0; v < 8; ++v) {
+            if (col0 + c + 4 * v < p.K) {
+              float4 o = make_float4(__uint_as_float(r[4 * v]), __uint_as_float(r[4 * v + 1]),
+                                     __uint_as_float(r[4 * v + 2]), __uint_as_float(r[4 * v + 3]));
+              if (p.S == 1) {
+                const float4 h = *reinterpret_cast<const float4*>(dst + 4 * v);
+                o.x += h.x; o.y += h.y; o.z += h.z; o.w += h.w;
+              }
+              *reinterpret_cast<float4*>(dst + 4 * v) = o;
+            }
+          }
+        }
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (threadIdx.x == 0 && *abort_flag && p.status) atomicOr(p.status, JGQ_STATUS_TIMEOUT);
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_acc, HT_N);
+  }
+}
+
+// ------------------------------------------------------------------ host ----
+struct HessPlan { int use; int planes; int nseg; int S; int tokens_per_slice; size_t plane_bytes; size_t part_bytes; };
+
+static int hessian_path_override() {      // 0 = automatic, 1 = FFMA only, 2 = tensor path whenever legal
+  static int v = -1;
+  if (v < 0) {
+    const char* e = getenv("JGQ_HESSIAN_PATH");
+    v = (e && !strcmp(e, "simt")) ? 1 : (e && !strcmp(e, "umma")) ? 2 : 0;
+  }
+  return v;
+}
+
+HessPlan plan_hessian_umma(int64_t n, int64_t K, int x_dtype) {
+  HessPlan pl;
+  memset(&pl, 0, sizeof(pl));
+  const int ov = hessian_path_override();
+  if (ov == 1 || K % 8 != 0 || n < 1) return pl;
+  if (ov != 2 && (K < 256 || n < 512)) return pl;     // tiny problems: the FFMA path is already launch-bound
+  pl.use = 1;
+  pl.planes = (x_dtype == JGQ_F32) ? 2 : 1;
+  const int64_t T = cdiv(K, HT_M);
+  int64_t nseg = 0;
+  for (int64_t I = 0; I < T; ++I) nseg += (I + 2) / 2;
+  pl.nseg = (int)nseg;
+  const int sms = sm_count();
+  int64_t smax = std::min<int64_t>(16, std::max<int64_t>(1, n / 1024));
+  while (smax > 1 && (size_t)smax * K * K * sizeof(float) > ((size_t)512 << 20)) --smax;
+  int best = 1;
+  double best_eff = 0.0;
+  for (int64_t s = 1; s <= smax; ++s) {
+    const int64_t ctas = nseg * s;
+    const double eff = (double)ctas / (double)(cdiv(ctas, sms) * sms);
+    if (eff > best_eff + 1e-9) { best_eff = eff; best = (int)s; }
+    if (eff >= 0.9) { best = (int)s; break; }
+  }
+  int64_t tps = cdiv(cdiv(n, best), HT_BK) * HT_BK;
+  pl.S = (int)cdiv(n, tps);
+  pl.tokens_per_slice = (int)tps;
+  pl.plane_bytes = pl.planes > 1 ? align_up((size_t)n * K * 2, 256) : 0;
+  pl.part_bytes = pl.S > 1 ? align_up((size_t)pl.S * K * K * sizeof(float), 256) : 0;
+  return pl;
+}
+
+// H (lower blocks) += X^T X.  `reduce` is called by the caller when S > 1 (slice buffers -> H).
+int launch_hessian_umma(const HessPlan& pl, const void* X, int x_dtype, int64_t n, int64_t K, float* H, void* ws,
+                        int32_t* status, cudaStream_t s) {
+  const void* plane0 = X;
+  const void* plane1 = X;
+  float* part = nullptr;
+  uint8_t* w = (uint8_t*)ws;
+  if (pl.planes > 1) {
+    __nv_bfloat16* P0 = (__nv_bfloat16*)w;
+    __nv_bfloat16* P1 = (__nv_bfloat16*)(w + pl.plane_bytes);
+    w += 2 * pl.plane_bytes;
+    const int64_t total4 = n * K / 4;
+    const int blocks = (int)std::min<int64_t>(cdiv(total4, 256), (int64_t)sm_count() * 16);
+    split_bf16_kernel<float><<<blocks, 256, 0, s>>>((const float*)X, P0, P1, total4);
+    JGQ_LAUNCHED();
+    plane0 = P0;
+    plane1 = P1;
+  }
+  if (pl.S > 1) part = (float*)w;
+  CUtensorMap m0, m1;
+  int rc = encode_tmap_2d_b16(&m0, plane0, (uint64_t)K, (uint64_t)n, (uint64_t)K * 2, 64, HT_BK);
+  if (rc) return rc;
+  rc = encode_tmap_2d_b16(&m1, plane1, (uint64_t)K, (uint64_t)n, (uint64_t)K * 2, 64, HT_BK);
+  if (rc) return rc;
+  HessParams p;
+  p.K = (int)K; p.n = (int)n; p.planes = pl.planes; p.fmt = (x_dtype == JGQ_F16) ? 0 : 1;
+  p.nseg = pl.nseg; p.S = pl.S; p.tokens_per_slice = pl.tokens_per_slice;
+  p.out = pl.S > 1 ? part : H;
+  p.slice_stride = pl.S > 1 ? K * K : 0;
+  p.status = status;
+  static bool attr_set[64] = {false};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev >= 0 && dev < 64 && !attr_set[dev]) {
+    cudaFuncSetAttribute(hessian_umma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, HT_SMEM_BYTES);
+    attr_set[dev] = true;
+  }
+  hessian_umma_kernel<<<(unsigned)(pl.nseg * pl.S), HT_THREADS, HT_SMEM_BYTES, s>>>(m0, m1, p);
+  return check_launch("hessian_umma");
+}
+
+}  // namespace jgq

@@ -121,10 +121,31 @@ def quant_matrix_shape(quantized_matrix, bits=4):
 # --------------------------------------------------------------------------
 # Hessian                                               reference gptq.py:57-103
 # --------------------------------------------------------------------------
-def _accumulate_raw(xs, H=None):
+def _merge_adjacent(xs):
+    """Batches that are consecutive row ranges of one contiguous device buffer (e.g. the
+    chunks of a captured activation) are handed to the kernel as one batch: same sum,
+    fewer and longer launches."""
+    out = []
+    for b in xs:
+        if (out and isinstance(b, torch.Tensor) and isinstance(out[-1], torch.Tensor)
+                and b.is_cuda and out[-1].is_cuda and b.dtype == out[-1].dtype
+                and b.is_contiguous() and out[-1].is_contiguous() and b.dim() >= 2 and out[-1].dim() >= 2
+                and b.shape[-1] == out[-1].shape[-1]
+                and b.untyped_storage().data_ptr() == out[-1].untyped_storage().data_ptr()
+                and b.data_ptr() == out[-1].data_ptr() + out[-1].numel() * out[-1].element_size()):
+            prev = out[-1]
+            K = prev.shape[-1]
+            rows = prev.numel() // K + b.numel() // K
+            out[-1] = torch.as_strided(prev, (rows, K), (K, 1))
+        else:
+            out.append(b)
+    return out
+
+
+def _accumulate_raw(xs, H=None, status=None):
     """H (K x K fp32, lower triangle) += sum over batches of X^T X; returns (H, n)."""
     n_total = 0
-    for batch in xs:
+    for batch in _merge_adjacent(list(xs)):
         b = _to_dev(batch)
         if b.dtype not in _DT:
             b = b.to(torch.float32)          # gptq.py:65: batch.astype(H.dtype)
@@ -144,7 +165,7 @@ def _accumulate_raw(xs, H=None):
             need = lib.jgq_hessian_workspace_bytes(m, K, _DT[chunk.dtype])
             ws = _workspace(need) if need else None
             check(lib.jgq_hessian_accum(chunk.data_ptr(), _DT[chunk.dtype], m, K, H.data_ptr(),
-                                        _ptr(ws), need, _stream()))
+                                        _ptr(ws), need, _ptr(status), _stream()))
         n_total += n
     return H, n_total
 
@@ -159,8 +180,12 @@ def accumulate_H(xs, use_fp64=False):
     if use_fp64:
         raise NotImplementedError('use_fp64=True is not available in the CUDA path')
     as_np = all(_is_np(x) for x in xs)
-    H, n = _accumulate_raw(xs)
-    return _out(_finalize_H(H, n), as_np)
+    status = torch.zeros(1, dtype=torch.int32, device=_dev())
+    H, n = _accumulate_raw(xs, status=status)
+    H = _finalize_H(H, n)
+    if int(status.item()) != 0:
+        raise RuntimeError('a device-side wait timed out while accumulating the Hessian')
+    return _out(H, as_np)
 
 
 # --------------------------------------------------------------------------
@@ -235,8 +260,9 @@ def gptq(W, xs, block_size=128, actorder=False, damping=0.01, use_fp64=False, *,
     if K % block_size != 0:
         raise ValueError(f'K={K} must be a multiple of block_size={block_size}')
     params = _col_params(Wf, bits)                           # gptq.py:185 (before any fix-up)
+    h_status = torch.zeros(1, dtype=torch.int32, device=Wf.device)
     if H is None:
-        Hd, n = _accumulate_raw(xs)
+        Hd, n = _accumulate_raw(xs, status=h_status)
         Hd = _finalize_H(Hd, n)                              # gptq.py:187
     else:
         Hd = _to_dev(H, torch.float32).clone().contiguous()
@@ -255,7 +281,10 @@ def gptq(W, xs, block_size=128, actorder=False, damping=0.01, use_fp64=False, *,
         Q = Q[invperm, :].contiguous()
         if codes is not None:
             codes = codes[invperm, :].contiguous()
-    if int(status.item()) != 0:                              # gptq.py:194-196 (one host sync per call)
+    st = int((status | (h_status << 8)).item())              # gptq.py:194-196 (one host sync per call)
+    if st >> 8:
+        raise RuntimeError('a device-side wait timed out while accumulating the Hessian')
+    if st != 0:
         raise ValueError('NaN when computing Hinv. Features NaN?')
     out_params = {'scale': _out(params['scale'], as_np), 'zero': _out(params['zero'], as_np),
                   'maxq': params['maxq']}

@@ -387,3 +387,30 @@ def test_config1_matmul_after_gptq(G):
     y = host(G.quantized_matmul(dev(x), qm))
     ref = x.astype(np.float64) @ host(G.unpack_matrix(qm)).astype(np.float64)
     assert np.linalg.norm(y - ref) / np.linalg.norm(ref) <= 1e-2
+
+
+# ------------------------------------------------- Hessian on the tensor path ----
+@pytest.mark.parametrize('n,K', [(1024, 256), (4096, 768), (2000, 320), (8192, 1024), (777, 512)])
+def test_hessian_tensor_path_fp32(G, n, K):
+    """fp32 batches go through the bf16-split tcgen05 kernel (K % 8 == 0, K >= 256, n >= 512)."""
+    rng = np.random.default_rng(90 + K)
+    X = (rng.standard_normal((n, K)) * rng.uniform(0.1, 3.0, size=K) + rng.uniform(-0.5, 0.5, size=K)).astype(np.float32)
+    ref = (X.astype(np.float64).T @ X.astype(np.float64)) / n
+    a = host(G.accumulate_H([dev(X)]))
+    b = host(G.accumulate_H([dev(X[: n // 2]), dev(X[n // 2:])]))
+    assert np.array_equal(a, a.T)
+    scale = np.sqrt(np.outer(np.diag(ref), np.diag(ref)))
+    assert np.abs(a - ref).max() <= 2e-5 * scale.max()
+    assert (np.abs(a - ref) / scale).max() <= 2e-5
+    assert (np.abs(b - ref) / scale).max() <= 2e-5
+    again = host(G.accumulate_H([dev(X)]))
+    assert np.array_equal(a, again), 'Hessian accumulation must be deterministic'
+
+
+@pytest.mark.parametrize('dtype', [torch.float16, torch.bfloat16])
+def test_hessian_tensor_path_half(G, dtype):
+    rng = np.random.default_rng(95)
+    X = torch.from_numpy(rng.standard_normal((2048, 512)).astype(np.float32)).to(dtype)
+    ref = (X.double().numpy().T @ X.double().numpy()) / 2048
+    got = host(G.accumulate_H([X.cuda()]))
+    assert np.allclose(got, ref, atol=5e-6, rtol=1e-5)
