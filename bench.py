@@ -349,16 +349,10 @@ def run_ours(args):
               for i in range(layers) for name, _, _ in LINEARS)
 
     def step_e2e():
-        for i in range(layers):
-            for name, _, _ in LINEARS:
-                xs = host_acts[i % distinct][name]
-                Q, params = gg.gptq(host_w[i][name], list(xs.chunk(CALIB_BATCHES)),
-                                   block_size=BLOCK_SIZE, damping=DAMP)
-                qm = G.pack_matrix(Q, params)
-                p, s, z = host_out[i][name]
-                p.copy_(qm.int_weight, non_blocking=True)
-                s.copy_(qm.scale, non_blocking=True)
-                z.copy_(qm.zero, non_blocking=True)
+        jobs = [(host_w[i][name], list(host_acts[i % distinct][name].chunk(CALIB_BATCHES)))
+                for i in range(layers) for name, _, _ in LINEARS]
+        outs = [host_out[i][name] for i in range(layers) for name, _, _ in LINEARS]
+        gg.gptq_many(jobs, block_size=BLOCK_SIZE, damping=DAMP, pack=True, out_host=outs)
         torch.cuda.synchronize()
 
     for _ in range(min(args.warmup, 3)):

@@ -73,126 +73,215 @@ __global__ void zero_dead_rows_kernel(float* __restrict__ W, int K, int64_t N,
     W[(int64_t)r * N + c] = 0.f;
 }
 
-// ---- (1) diagonal block: Cholesky in shared memory, then its inverse ----------
+// ---- one panel step: factor + invert the 64x64 diagonal block, then one tile of work ----
+// Every CTA of the step factors the (same) diagonal block itself - identical arithmetic,
+// identical bits - so that the panel tiles need no separate launch behind the factorization.
+// The 64x64 block is processed in 16-wide sub-blocks: a single warp factors and inverts a
+// 16x16 block with register rows and shuffles (no block-wide barrier inside), the rest is
+// small shared-memory products.
+
+// 16x16 Cholesky + inverse of the lower-triangular factor, one warp; lanes 16..31 mirror 0..15.
+__device__ __forceinline__ bool leaf16(float (*a)[CPAD], float (*inv)[CPAD], const int c0) {
+  const unsigned full = 0xffffffffu;
+  const int lane = threadIdx.x & 31, r = lane & 15;
+  float v[16], x[16];
+#pragma unroll
+  for (int j = 0; j < 16; ++j) v[j] = (j <= r) ? a[c0 + r][c0 + j] : 0.f;
+  bool notpd = false;
+#pragma unroll
+  for (int k = 0; k < 16; ++k) {
+    const float akk = __shfl_sync(full, v[k], k);
+    notpd |= !(akk > 0.f);
+    const float d = __fsqrt_rn(akk);
+    const float lk = (r == k) ? d : __fdiv_rn(v[k], d);      // l[r][k], meaningful for r >= k
+    v[k] = lk;
+#pragma unroll
+    for (int j = k + 1; j < 16; ++j) {
+      const float ljk = __shfl_sync(full, lk, j);             // l[j][k]
+      v[j] = fmaf(-lk, ljk, v[j]);                            // a[r][j] -= l[r][k] l[j][k]   (r >= j)
+    }
+  }
+  // column r of the inverse by forward substitution; row i of L lives in lane i
+#pragma unroll
+  for (int i = 0; i < 16; ++i) {
+    const float lii = __shfl_sync(full, v[i], i);
+    float sum = 0.f;
+#pragma unroll
+    for (int m = 0; m < i; ++m) {
+      const float lim = __shfl_sync(full, v[m], i);
+      sum = fmaf(lim, x[m], sum);
+    }
+    x[i] = (i == r) ? __fdiv_rn(1.f, lii) : ((i > r) ? __fdiv_rn(-sum, lii) : 0.f);
+  }
+  if (lane < 16) {
+#pragma unroll
+    for (int j = 0; j < 16; ++j) {
+      if (j <= r) a[c0 + r][c0 + j] = v[j];
+      inv[c0 + j][c0 + r] = x[j];
+    }
+  }
+  return __any_sync(full, notpd);
+}
+
 __global__ void __launch_bounds__(256)
-potrf_diag_kernel(float* __restrict__ A, float* __restrict__ X, int K, int kb,
-                  int32_t* __restrict__ status) {
+chol_step_kernel(float* __restrict__ A, float* __restrict__ X, int K, int kb, int tiles_below,
+                 int32_t* __restrict__ status) {
   __shared__ float a[CB][CPAD];
   __shared__ float inv[CB][CPAD];
   const int r0 = kb * CB;
   const int nb = min(CB, K - r0);
-  const int tid = threadIdx.x;
+  const int tid = threadIdx.x, warp = tid >> 5;
   for (int idx = tid; idx < CB * CB; idx += 256) {
     const int i = idx / CB, j = idx % CB;
-    a[i][j] = (i < nb && j <= i) ? A[(int64_t)(r0 + i) * K + r0 + j] : 0.f;
+    float v = 0.f;
+    if (i < nb && j <= i) v = A[(int64_t)(r0 + i) * K + r0 + j];
+    else if (i >= nb && i == j) v = 1.f;            // identity padding of a partial last block
+    a[i][j] = v;
     inv[i][j] = 0.f;
   }
   __syncthreads();
-  for (int k = 0; k < nb; ++k) {
-    if (tid == 0) {
-      const float piv = a[k][k];
-      if (!(piv > 0.f)) atomicOr(status, JGQ_STATUS_NOT_PD);
-      a[k][k] = __fsqrt_rn(piv);
+
+  // ---- blocked (16) right-looking Cholesky of the 64x64 block, diagonal sub-blocks inverted ----
+  for (int s = 0; s < 4; ++s) {
+    const int c0 = 16 * s;
+    if (warp == 0) {
+      const bool bad = leaf16(a, inv, c0);
+      if (bad && tid == 0 && blockIdx.x == 0) atomicOr(status, JGQ_STATUS_NOT_PD);
     }
     __syncthreads();
-    const float d = a[k][k];
-    for (int i = k + 1 + tid; i < nb; i += 256) a[i][k] = __fdiv_rn(a[i][k], d);
-    __syncthreads();
-    const int rem = nb - k - 1;
-    for (int idx = tid; idx < rem * rem; idx += 256) {
-      const int i = k + 1 + idx / rem, j = k + 1 + idx % rem;
-      if (j <= i) a[i][j] = fmaf(-a[i][k], a[j][k], a[i][j]);
-    }
-    __syncthreads();
-  }
-  // inverse of the lower-triangular block: column j is independent of the others
-  if (tid < nb) {
-    const int j = tid;
-    inv[j][j] = __fdiv_rn(1.f, a[j][j]);
-    for (int i = j + 1; i < nb; ++i) {
-      float s0 = 0.f, s1 = 0.f;
-      int m = j;
-      for (; m + 1 < i; m += 2) {
-        s0 = fmaf(a[i][m], inv[m][j], s0);
-        s1 = fmaf(a[i][m + 1], inv[m + 1][j], s1);
+    const int rows = CB - (c0 + 16);
+    if (rows > 0) {
+      float pv[3];
+#pragma unroll
+      for (int t = 0; t < 3; ++t) {
+        const int idx = tid + 256 * t;
+        pv[t] = 0.f;
+        if (idx < rows * 16) {
+          const int i = c0 + 16 + idx / 16, c = idx % 16;
+          float sum = 0.f;
+          for (int m = 0; m <= c; ++m) sum = fmaf(a[i][c0 + m], inv[c0 + c][c0 + m], sum);
+          pv[t] = sum;
+        }
       }
-      if (m < i) s0 = fmaf(a[i][m], inv[m][j], s0);
-      inv[i][j] = __fdiv_rn(-(s0 + s1), a[i][i]);
+      __syncthreads();
+#pragma unroll
+      for (int t = 0; t < 3; ++t) {
+        const int idx = tid + 256 * t;
+        if (idx < rows * 16) a[c0 + 16 + idx / 16][c0 + idx % 16] = pv[t];
+      }
+      __syncthreads();
+      for (int idx = tid; idx < rows * rows; idx += 256) {
+        const int i = c0 + 16 + idx / rows, j = c0 + 16 + idx % rows;
+        if (j <= i) {
+          float sum = 0.f;
+#pragma unroll
+          for (int m = 0; m < 16; ++m) sum = fmaf(a[i][c0 + m], a[j][c0 + m], sum);
+          a[i][j] -= sum;
+        }
+      }
+      __syncthreads();
     }
   }
-  __syncthreads();
-  for (int idx = tid; idx < nb * nb; idx += 256) {
-    const int i = idx / nb, j = idx % nb;
-    if (j <= i) A[(int64_t)(r0 + i) * K + r0 + j] = a[i][j];
-    X[(int64_t)(r0 + i) * K + r0 + j] = inv[i][j];
-  }
-}
 
-// 64x64x64 product helper: out[r][c] = sign * sum_m P[r][m] * Q(m, c) on shared tiles.
-// (2) panel:  tile <- tile * inv_k^T      (rows below the diagonal block)
-__global__ void __launch_bounds__(256)
-trsm_panel_kernel(float* __restrict__ A, const float* __restrict__ X, int K, int kb) {
-  __shared__ float p[CB][CPAD];
-  __shared__ float iv[CB][CPAD];
-  const int c0 = kb * CB;
-  const int nb = min(CB, K - c0);
-  const int r0 = (kb + 1) * CB + blockIdx.x * CB;
-  const int tid = threadIdx.x;
-  for (int idx = tid; idx < CB * CB; idx += 256) {
-    const int i = idx / CB, j = idx % CB;
-    p[i][j] = (r0 + i < K && j < nb) ? A[(int64_t)(r0 + i) * K + c0 + j] : 0.f;
-    iv[i][j] = (i < nb && j < nb) ? X[(int64_t)(c0 + i) * K + c0 + j] : 0.f;
+  // ---- assemble the inverse from its 16x16 diagonal blocks, one block diagonal at a time ----
+  {
+    const int rr = tid / 16, cc = tid % 16;
+    for (int d = 1; d < 4; ++d) {
+      float tv[3];
+#pragma unroll
+      for (int bi = 0; bi < 3; ++bi) {
+        const int i = d + bi, j = bi;           // block (i, j), i - j == d
+        tv[bi] = 0.f;
+        if (i < 4) {
+          float sum = 0.f;
+          for (int m = j; m < i; ++m)
+#pragma unroll
+            for (int q = 0; q < 16; ++q) sum = fmaf(a[16 * i + rr][16 * m + q], inv[16 * m + q][16 * j + cc], sum);
+          tv[bi] = sum;
+        }
+      }
+      __syncthreads();
+#pragma unroll
+      for (int bi = 0; bi < 3; ++bi)
+        if (d + bi < 4) inv[16 * (d + bi) + rr][16 * bi + cc] = tv[bi];
+      __syncthreads();
+#pragma unroll
+      for (int bi = 0; bi < 3; ++bi) {
+        const int i = d + bi, j = bi;
+        if (i < 4) {
+          float sum = 0.f;
+          for (int q = 0; q <= rr; ++q) sum = fmaf(inv[16 * i + rr][16 * i + q], inv[16 * i + q][16 * j + cc], sum);
+          tv[bi] = -sum;
+        }
+      }
+      __syncthreads();
+#pragma unroll
+      for (int bi = 0; bi < 3; ++bi)
+        if (d + bi < 4) inv[16 * (d + bi) + rr][16 * bi + cc] = tv[bi];
+      __syncthreads();
+    }
   }
-  __syncthreads();
+
+  const int bid = blockIdx.x;
+  if (bid == 0) {
+    // The inverse of the diagonal block is part of the result X.  The factor itself is not
+    // written back: nothing reads it after this step, and the other CTAs of this launch may
+    // still be loading the unfactored block from A.
+    for (int idx = tid; idx < nb * nb; idx += 256) {
+      const int i = idx / nb, j = idx % nb;
+      X[(int64_t)(r0 + i) * K + r0 + j] = inv[i][j];
+    }
+    return;
+  }
   const int tr = (tid >> 4) * 4, tc = (tid & 15) * 4;
   float acc[4][4] = {};
-  for (int m = 0; m < nb; ++m) {
-    float pv[4], qv[4];
+  if (bid <= tiles_below) {
+    // (2) panel tile below the diagonal block:  tile <- tile * inv^T
+    const int p0 = (kb + 1) * CB + (bid - 1) * CB;
+    __syncthreads();
+    for (int idx = tid; idx < CB * CB; idx += 256) {
+      const int i = idx / CB, j = idx % CB;
+      a[i][j] = (p0 + i < K && j < nb) ? A[(int64_t)(p0 + i) * K + r0 + j] : 0.f;
+    }
+    __syncthreads();
+    for (int m = 0; m < nb; ++m) {
+      float pv[4], qv[4];
 #pragma unroll
-    for (int i = 0; i < 4; ++i) { pv[i] = p[tr + i][m]; qv[i] = iv[tc + i][m]; }
+      for (int i = 0; i < 4; ++i) { pv[i] = a[tr + i][m]; qv[i] = inv[tc + i][m]; }
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(pv[i], qv[j], acc[i][j]);
+    }
 #pragma unroll
     for (int i = 0; i < 4; ++i)
 #pragma unroll
-      for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(pv[i], qv[j], acc[i][j]);
-  }
+      for (int j = 0; j < 4; ++j)
+        if (p0 + tr + i < K && tc + j < nb) A[(int64_t)(p0 + tr + i) * K + r0 + tc + j] = acc[i][j];
+  } else {
+    // (4) row block kb of the inverse:  X[kb, jt] <- -inv * S[kb, jt]
+    const int c0 = (bid - 1 - tiles_below) * CB;
+    __syncthreads();
+    for (int idx = tid; idx < CB * CB; idx += 256) {
+      const int i = idx / CB, j = idx % CB;
+      a[i][j] = (i < nb) ? X[(int64_t)(r0 + i) * K + c0 + j] : 0.f;
+    }
+    __syncthreads();
+    for (int m = 0; m < nb; ++m) {
+      float pv[4], qv[4];
 #pragma unroll
-  for (int i = 0; i < 4; ++i)
+      for (int i = 0; i < 4; ++i) { pv[i] = inv[tr + i][m]; qv[i] = a[m][tc + i]; }
 #pragma unroll
-    for (int j = 0; j < 4; ++j)
-      if (r0 + tr + i < K && tc + j < nb) A[(int64_t)(r0 + tr + i) * K + c0 + tc + j] = acc[i][j];
-}
-
-// (4) row block k of the inverse:  X[k, jt] <- -inv_k * S[k, jt]
-__global__ void __launch_bounds__(256)
-trtri_row_kernel(float* __restrict__ X, int K, int kb) {
-  __shared__ float st[CB][CPAD];
-  __shared__ float iv[CB][CPAD];
-  const int r0 = kb * CB;
-  const int nb = min(CB, K - r0);
-  const int c0 = blockIdx.x * CB;      // column tile, c0 < r0
-  const int tid = threadIdx.x;
-  for (int idx = tid; idx < CB * CB; idx += 256) {
-    const int i = idx / CB, j = idx % CB;
-    st[i][j] = (i < nb) ? X[(int64_t)(r0 + i) * K + c0 + j] : 0.f;
-    iv[i][j] = (i < nb && j < nb) ? X[(int64_t)(r0 + i) * K + r0 + j] : 0.f;
-  }
-  __syncthreads();
-  const int tr = (tid >> 4) * 4, tc = (tid & 15) * 4;
-  float acc[4][4] = {};
-  for (int m = 0; m < nb; ++m) {
-    float pv[4], qv[4];
+      for (int i = 0; i < 4; ++i)
 #pragma unroll
-    for (int i = 0; i < 4; ++i) { pv[i] = iv[tr + i][m]; qv[i] = st[m][tc + i]; }
+        for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(pv[i], qv[j], acc[i][j]);
+    }
 #pragma unroll
     for (int i = 0; i < 4; ++i)
 #pragma unroll
-      for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(pv[i], qv[j], acc[i][j]);
+      for (int j = 0; j < 4; ++j)
+        if (tr + i < nb) X[(int64_t)(r0 + tr + i) * K + c0 + tc + j] = -acc[i][j];
   }
-#pragma unroll
-  for (int i = 0; i < 4; ++i)
-#pragma unroll
-    for (int j = 0; j < 4; ++j)
-      if (tr + i < nb) X[(int64_t)(r0 + tr + i) * K + c0 + tc + j] = -acc[i][j];
 }
 
 // ---- final: L[i][j] = X[K-1-j][K-1-i] (i >= j), 0 above the diagonal -----------
@@ -266,17 +355,16 @@ extern "C" int jgq_damp_invert(float* W, int64_t N, float* H, int64_t K, float d
     const int r1 = (kb + 1) * CB;            // first row below the diagonal block
     const int below = Ki - r1;
     const int nb = std::min(CB, Ki - kb * CB);
-    potrf_diag_kernel<<<1, 256, 0, s>>>(A, X, Ki, kb, dev_status);
+    const int tiles_below = below > 0 ? (int)cdiv(below, CB) : 0;
+    chol_step_kernel<<<(unsigned)(1 + tiles_below + kb), 256, 0, s>>>(A, X, Ki, kb, tiles_below, dev_status);
     JGQ_LAUNCHED();
-    if (below > 0) { trsm_panel_kernel<<<(unsigned)cdiv(below, CB), 256, 0, s>>>(A, X, Ki, kb); JGQ_LAUNCHED(); }
-    if (kb > 0) { trtri_row_kernel<<<(unsigned)kb, 256, 0, s>>>(X, Ki, kb); JGQ_LAUNCHED(); }
     if (below > 0) {
+      // (3) trailing update of A (lower tiles) and (5) update of the pending part of X, one launch
       const float* P = A + (int64_t)r1 * K + (int64_t)kb * CB;
-      int rc = launch_sgemm(true, true, P, K, P, K, A + (int64_t)r1 * K + r1, K,
-                            below, below, nb, -1.f, 1.f, 1, s);
-      if (rc) return rc;
-      rc = launch_sgemm(true, false, P, K, X + (int64_t)kb * CB * K, K, X + (int64_t)r1 * K, K,
-                        below, r1, nb, 1.f, 1.f, 0, s);
+      const GemmParams g0 = make_gemm_params(P, K, P, K, A + (int64_t)r1 * K + r1, K, below, below, nb, -1.f, 1.f, 1);
+      const GemmParams g1 = make_gemm_params(P, K, X + (int64_t)kb * CB * K, K, X + (int64_t)r1 * K, K,
+                                             below, r1, nb, 1.f, 1.f, 0);
+      const int rc = launch_sgemm_dual(g0, true, g1, false, s);
       if (rc) return rc;
     }
   }

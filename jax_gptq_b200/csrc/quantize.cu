@@ -73,8 +73,36 @@ gptq_block_kernel(const float* __restrict__ W, const float* __restrict__ L,
           if (ii < sn) w[ii] = __fsub_rn(w[ii], __fmul_rn(Ld[(s0 + ii) * bs_pad + r], err));
       }
     }
-    // bring the later rows of this block up to date (only reached when sn == SUB)
-    for (int j = s0 + SUB; j < bs; ++j) {
+    // bring the later rows of this block up to date (only reached when sn == SUB).
+    // Four rows at a time: each row is its own dependent chain of 16 multiply/subtract pairs,
+    // so interleaving four of them hides the arithmetic latency of the single resident warp.
+    int j = s0 + SUB;
+    for (; j + 3 < bs; j += 4) {
+      float wj[4];
+      const float4* lrow[4];
+#pragma unroll
+      for (int r = 0; r < 4; ++r) {
+        wj[r] = Wb[(j + r) * TPB + tid];
+        lrow[r] = reinterpret_cast<const float4*>(&Ld[(j + r) * bs_pad + s0]);
+      }
+#pragma unroll
+      for (int i4 = 0; i4 < SUB / 4; ++i4) {
+        float4 l[4];
+#pragma unroll
+        for (int r = 0; r < 4; ++r) l[r] = lrow[r][i4];
+#pragma unroll
+        for (int r = 0; r < 4; ++r) wj[r] = __fsub_rn(wj[r], __fmul_rn(l[r].x, e[i4 * 4 + 0]));
+#pragma unroll
+        for (int r = 0; r < 4; ++r) wj[r] = __fsub_rn(wj[r], __fmul_rn(l[r].y, e[i4 * 4 + 1]));
+#pragma unroll
+        for (int r = 0; r < 4; ++r) wj[r] = __fsub_rn(wj[r], __fmul_rn(l[r].z, e[i4 * 4 + 2]));
+#pragma unroll
+        for (int r = 0; r < 4; ++r) wj[r] = __fsub_rn(wj[r], __fmul_rn(l[r].w, e[i4 * 4 + 3]));
+      }
+#pragma unroll
+      for (int r = 0; r < 4; ++r) Wb[(j + r) * TPB + tid] = wj[r];
+    }
+    for (; j < bs; ++j) {
       float wj = Wb[j * TPB + tid];
       const float4* lrow = reinterpret_cast<const float4*>(&Ld[j * bs_pad + s0]);
 #pragma unroll

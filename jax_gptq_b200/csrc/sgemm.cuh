@@ -10,6 +10,7 @@
 // threads, 8x8 register micro-tile, register-staged double buffering.
 #pragma once
 #include "common.cuh"
+#include <algorithm>
 
 namespace jgq {
 
@@ -67,13 +68,13 @@ __device__ __forceinline__ void gemm_store_tile(float (*S)[GBM + GPAD], const fl
 }
 
 template <bool A_KC, bool B_KC>
-__global__ void __launch_bounds__(GTHREADS)
-sgemm_kernel(const GemmParams p) {
+__device__ __forceinline__ void sgemm_body(const GemmParams& p, const int zsplit) {
   const int m0 = blockIdx.y * GBM, n0 = blockIdx.x * GBN;
+  if (m0 >= p.M || n0 >= p.N) return;
   if (p.tri && n0 > m0 + GBM - 1) return;
-  const int kbeg = blockIdx.z * p.k_chunk;
+  const int kbeg = zsplit * p.k_chunk;
   const int kend = min(p.Kd, kbeg + p.k_chunk);
-  float* __restrict__ C = p.C + (int64_t)blockIdx.z * p.c_split_stride;
+  float* __restrict__ C = p.C + (int64_t)zsplit * p.c_split_stride;
 
   __shared__ __align__(16) float As[2][GBK][GBM + GPAD];
   __shared__ __align__(16) float Bs[2][GBK][GBN + GPAD];
@@ -156,8 +157,48 @@ sgemm_kernel(const GemmParams p) {
   }
 }
 
+template <bool A_KC, bool B_KC>
+__global__ void __launch_bounds__(GTHREADS)
+sgemm_kernel(const GemmParams p) {
+  sgemm_body<A_KC, B_KC>(p, blockIdx.z);
+}
+
+// Two independent products in one launch (blockIdx.z selects the problem); A has the
+// contraction index contiguous in both, B's layout is a per-problem flag.
+struct GemmDualParams { GemmParams p[2]; int b_kc[2]; };
+
+__global__ void __launch_bounds__(GTHREADS)
+sgemm_dual_kernel(const GemmDualParams dp) {
+  const int z = blockIdx.z;
+  if (dp.b_kc[z]) sgemm_body<true, true>(dp.p[z], 0);
+  else            sgemm_body<true, false>(dp.p[z], 0);
+}
+
 // Host-side launcher.  `splits` > 1 slices the contraction range over blockIdx.z,
 // slice z writing C + z * c_split_stride (beta applies to each slice's own C).
+inline GemmParams make_gemm_params(const float* A, int64_t lda, const float* B, int64_t ldb, float* C, int64_t ldc,
+                                   int M, int N, int Kd, float alpha, float beta, int tri) {
+  GemmParams p;
+  p.A = A; p.lda = lda; p.B = B; p.ldb = ldb; p.C = C; p.ldc = ldc;
+  p.M = M; p.N = N; p.Kd = Kd; p.alpha = alpha; p.beta = beta; p.tri = tri;
+  p.a_vec = aligned(A, 16) && (lda % 4 == 0);
+  p.b_vec = aligned(B, 16) && (ldb % 4 == 0);
+  p.k_chunk = (int)cdiv(std::max(Kd, 1), GBK) * GBK;
+  p.c_split_stride = 0;
+  return p;
+}
+
+// Both problems use A with the contraction index contiguous.  Problems with M <= 0 or N <= 0 are skipped.
+inline int launch_sgemm_dual(const GemmParams& p0, bool b_kc0, const GemmParams& p1, bool b_kc1, cudaStream_t s) {
+  GemmDualParams dp;
+  dp.p[0] = p0; dp.p[1] = p1; dp.b_kc[0] = b_kc0; dp.b_kc[1] = b_kc1;
+  const int gx = (int)std::max(cdiv(std::max(p0.N, 0), GBN), cdiv(std::max(p1.N, 0), GBN));
+  const int gy = (int)std::max(cdiv(std::max(p0.M, 0), GBM), cdiv(std::max(p1.M, 0), GBM));
+  if (gx <= 0 || gy <= 0) return JGQ_OK;
+  sgemm_dual_kernel<<<dim3((unsigned)gx, (unsigned)gy, 2), GTHREADS, 0, s>>>(dp);
+  return check_launch("sgemm_dual");
+}
+
 inline int launch_sgemm(bool a_kc, bool b_kc, const float* A, int64_t lda, const float* B, int64_t ldb,
                         float* C, int64_t ldc, int M, int N, int Kd, float alpha, float beta, int tri,
                         cudaStream_t s, int splits = 1, int64_t c_split_stride = 0) {

@@ -388,3 +388,73 @@ def unpack_matrix(weight, dtype=None):
     check(lib.jgq_unpack_matrix(packed.data_ptr(), zero.data_ptr(), scale.data_ptr(), out.data_ptr(),
                                 _DT[out_dtype], outer, plen, inner, _stream()))
     return _out(out, as_np)
+
+
+# --------------------------------------------------------------------------
+# many layers with host-resident inputs: copies overlap the previous layer's compute
+# --------------------------------------------------------------------------
+def gptq_many(jobs, block_size=128, actorder=False, damping=0.01, bits=4, pack=True, out_host=None):
+    """Run ``gptq`` (and ``pack_matrix`` when `pack`) over a sequence of ``(W, xs)`` jobs.
+
+    This is the loop the reference's interpreter runs layer by layer
+    (quantize_interpreter.py:151-299) with its host<->device ``device_put`` traffic: while
+    job i is being quantized on the current stream, the weights and calibration batches of
+    job i+1 are copied from (pinned) host memory on a second stream.  Device-resident inputs
+    are used in place.  `out_host`, if given, is a list of ``(packed, scale, zero)`` pinned
+    host tensors that receive each packed result (device->host, asynchronously).
+    Returns the list of results (QuantizedMatrix when `pack`, else ``(Q, params)``).
+    """
+    jobs = list(jobs)
+    if not jobs:
+        return []
+    compute = torch.cuda.current_stream()
+    copier = torch.cuda.Stream()
+    device = _dev()
+
+    def stage(job):
+        W, xs = job
+        with torch.cuda.stream(copier):
+            Wd = W if (isinstance(W, torch.Tensor) and W.is_cuda) else _to_dev(W)
+            xs = list(xs)
+            host = [x for x in xs if not (isinstance(x, torch.Tensor) and x.is_cuda)]
+            if host and len(host) == len(xs):
+                ts = [x if isinstance(x, torch.Tensor) else torch.from_numpy(np.ascontiguousarray(x)) for x in xs]
+                K = ts[0].shape[-1]
+                same = all(t.dtype == ts[0].dtype and t.shape[-1] == K for t in ts)
+                if same:
+                    rows = [t.numel() // K for t in ts]
+                    buf = torch.empty((sum(rows), K), dtype=ts[0].dtype, device=device)
+                    views, r0 = [], 0
+                    for t, r in zip(ts, rows):
+                        v = buf[r0:r0 + r]
+                        v.copy_(t.reshape(r, K), non_blocking=True)
+                        views.append(v)
+                        r0 += r
+                    xd = views
+                    buf.record_stream(compute)
+                else:
+                    xd = [_to_dev(t) for t in ts]
+            else:
+                xd = [_to_dev(x) for x in xs]
+            for t in [Wd] + xd:
+                if isinstance(t, torch.Tensor) and t.is_cuda:
+                    t.record_stream(compute)
+            ev = copier.record_event()
+        return Wd, xd, ev
+
+    results = []
+    nxt = stage(jobs[0])
+    for i in range(len(jobs)):
+        Wd, xd, ev = nxt
+        if i + 1 < len(jobs):
+            nxt = stage(jobs[i + 1])
+        compute.wait_event(ev)
+        Q, params = gptq(Wd, xd, block_size=block_size, actorder=actorder, damping=damping, bits=bits)
+        res = pack_matrix(Q, params) if pack else (Q, params)
+        if out_host is not None and pack:
+            p, s, z = out_host[i]
+            p.copy_(res.int_weight, non_blocking=True)
+            s.copy_(res.scale, non_blocking=True)
+            z.copy_(res.zero, non_blocking=True)
+        results.append(res)
+    return results
