@@ -167,7 +167,7 @@ sgemm_kernel(const GemmParams p) {
 // contraction index contiguous in both, B's layout is a per-problem flag.
 struct GemmDualParams { GemmParams p[2]; int b_kc[2]; };
 
-__global__ void __launch_bounds__(GTHREADS)
+static __global__ void __launch_bounds__(GTHREADS)
 sgemm_dual_kernel(const GemmDualParams dp) {
   const int z = blockIdx.z;
   if (dp.b_kc[z]) sgemm_body<true, true>(dp.p[z], 0);
