@@ -36,11 +36,46 @@ gptq_block_kernel(const float* __restrict__ W, const float* __restrict__ L,
   const int64_t col = (int64_t)blockIdx.x * TPB + tid;
   const bool live = col < N;
 
-  for (int idx = tid; idx < bs * bs; idx += TPB) {
-    const int j = idx / bs, i = idx % bs;
-    Ld[j * bs_pad + i] = L[(int64_t)(start + j) * K + start + i];
+  // Stage the diagonal block of L and this CTA's columns of W.  The CTA is a single warp or
+  // two, so the loads are issued in batches of 8 independent 16-byte requests per thread:
+  // one request at a time would expose a full memory latency per row.
+  if ((bs & 3) == 0 && (K & 3) == 0 && ((reinterpret_cast<uintptr_t>(L) & 15) == 0)) {
+    const int q = bs >> 2;                       // float4 per row
+    const int total = bs * q;
+    for (int base = 0; base < total; base += 8 * TPB) {
+      float4 v[8];
+#pragma unroll
+      for (int u = 0; u < 8; ++u) {
+        const int idx = base + u * TPB + tid;
+        if (idx < total) {
+          const int j = idx / q, i4 = idx - j * q;
+          v[u] = __ldg(reinterpret_cast<const float4*>(L + (int64_t)(start + j) * K + start) + i4);
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < 8; ++u) {
+        const int idx = base + u * TPB + tid;
+        if (idx < total) {
+          const int j = idx / q, i4 = idx - j * q;
+          *reinterpret_cast<float4*>(&Ld[j * bs_pad + 4 * i4]) = v[u];
+        }
+      }
+    }
+  } else {
+    for (int idx = tid; idx < bs * bs; idx += TPB) {
+      const int j = idx / bs, i = idx % bs;
+      Ld[j * bs_pad + i] = L[(int64_t)(start + j) * K + start + i];
+    }
   }
-  for (int j = 0; j < bs; ++j) Wb[j * TPB + tid] = live ? W[(int64_t)(start + j) * N + col] : 0.f;
+  for (int j0 = 0; j0 < bs; j0 += 16) {
+    float v[16];
+#pragma unroll
+    for (int u = 0; u < 16; ++u)
+      v[u] = (live && j0 + u < bs) ? W[(int64_t)(start + j0 + u) * N + col] : 0.f;
+#pragma unroll
+    for (int u = 0; u < 16; ++u)
+      if (j0 + u < bs) Wb[(j0 + u) * TPB + tid] = v[u];
+  }
   const float sc = live ? scale[col] : 1.f;
   const float zr = live ? zero[col] : 0.f;
   __syncthreads();

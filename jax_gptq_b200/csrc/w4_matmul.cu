@@ -24,101 +24,86 @@
 // Slices of different CTAs (split-K, needed to occupy 148 SMs when N is small)
 // are written to the workspace; the CTA that takes the last ticket of a
 // channel group adds the slices in slice order and writes the result.
-#include "common.cuh"
-#include <type_traits>
+#include "w4_common.cuh"
+#include "umma.cuh"
 #include <algorithm>
+#include <cstring>
 #include <mutex>
 
 namespace jgq {
 
-constexpr int WCOLS = 128;          // channels per CTA
-constexpr int WWARPS = 4;
-constexpr int PSTRIDE = WCOLS + 4;  // floats per partial row: 128 sums + sum_k x (+pad)
-
-template <typename XT> struct MmaType;
-template <> struct MmaType<__half> {
-  static constexpr uint32_t kMagic = 0x64006400u;  // 1024 | code
-  __device__ static __forceinline__ uint32_t expand(uint32_t v) {
-    uint32_t r = (v & 0x000F000Fu) | kMagic;
-    __half2 h = __hsub2(*reinterpret_cast<__half2*>(&r), __half2half2(__float2half_rn(1024.f)));
-    return *reinterpret_cast<uint32_t*>(&h);
+// Activation fragments of one 16-step (rows m0.., contraction k0..k0+15) for lane (g, q).
+template <typename XT, int MT>
+__device__ __forceinline__ void load_afrags(const XT* __restrict__ x, int64_t m0, int64_t M, int64_t k0, int64_t K,
+                                            int g, int q, uint32_t (&a)[MT][4], uint32_t (&alo)[MT][4]) {
+  constexpr bool kSplitX = std::is_same<XT, float>::value;
+#pragma unroll
+  for (int t = 0; t < MT; ++t) {
+    const int64_t ma = m0 + 16 * t + g, mb = ma + 8;
+    if (kSplitX) {
+      load_x2_split((const float*)x, ma, M, k0 + 2 * q, K, a[t][0], alo[t][0]);
+      load_x2_split((const float*)x, mb, M, k0 + 2 * q, K, a[t][1], alo[t][1]);
+      load_x2_split((const float*)x, ma, M, k0 + 8 + 2 * q, K, a[t][2], alo[t][2]);
+      load_x2_split((const float*)x, mb, M, k0 + 8 + 2 * q, K, a[t][3], alo[t][3]);
+    } else {
+      a[t][0] = load_x2<XT>(x, ma, M, k0 + 2 * q, K);
+      a[t][1] = load_x2<XT>(x, mb, M, k0 + 2 * q, K);
+      a[t][2] = load_x2<XT>(x, ma, M, k0 + 8 + 2 * q, K);
+      a[t][3] = load_x2<XT>(x, mb, M, k0 + 8 + 2 * q, K);
+      alo[t][0] = alo[t][1] = alo[t][2] = alo[t][3] = 0u;
+    }
   }
-  __device__ static __forceinline__ uint32_t ones() { return 0x3C003C00u; }
-  __device__ static __forceinline__ void mma(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
-    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
-                 : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
-                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
-  }
-};
-template <> struct MmaType<__nv_bfloat16> {
-  static constexpr uint32_t kMagic = 0x43004300u;  // 128 | code
-  __device__ static __forceinline__ uint32_t expand(uint32_t v) {
-    uint32_t r = (v & 0x000F000Fu) | kMagic;
-    __nv_bfloat162 h = __hsub2(*reinterpret_cast<__nv_bfloat162*>(&r), __float2bfloat162_rn(128.f));
-    return *reinterpret_cast<uint32_t*>(&h);
-  }
-  __device__ static __forceinline__ uint32_t ones() { return 0x3F803F80u; }
-  __device__ static __forceinline__ void mma(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
-    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
-                 : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
-                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
-  }
-};
-
-// 16 packed bytes of byte row `row`, channels c0..c0+15 (zero outside the matrix).
-__device__ __forceinline__ uint4 load_codes16(const uint8_t* __restrict__ packed, int64_t row, int64_t KB,
-                                              int64_t c0, int64_t N, bool vec) {
-  uint4 r = make_uint4(0, 0, 0, 0);
-  if (row >= KB || c0 >= N) return r;
-  const uint8_t* p = packed + row * N + c0;
-  if (vec && c0 + 15 < N) {
-    r = __ldg(reinterpret_cast<const uint4*>(p));
-  } else {
-    uint32_t w[4] = {0, 0, 0, 0};
-    for (int b = 0; b < 16; ++b)
-      if (c0 + b < N) w[b >> 2] |= (uint32_t)p[b] << (8 * (b & 3));
-    r = make_uint4(w[0], w[1], w[2], w[3]);
-  }
-  return r;
 }
 
-// Two consecutive activations x[m, k], x[m, k+1] as one MMA operand register (zero outside).
-template <typename XT>
-__device__ __forceinline__ uint32_t load_x2(const XT* __restrict__ x, int64_t m, int64_t M, int64_t k, int64_t K) {
-  if (m >= M || k >= K) return 0u;      // K is even and k is even: k+1 < K as well
-  return *reinterpret_cast<const uint32_t*>(x + m * K + k);
+// One 16-step: 16 MMAs per row tile over the 2 x 16 bytes this lane holds, plus the MMA against ones.
+template <typename CT, int MT, bool kSplitX>
+__device__ __forceinline__ void w4_step(float (&acc)[MT][16][4], float (&accx)[MT][4], const uint4& r0, const uint4& r1,
+                                        const uint32_t (&a)[MT][4], const uint32_t (&alo)[MT][4]) {
+  const uint32_t w0[4] = {r0.x, r0.y, r0.z, r0.w};
+  const uint32_t w1[4] = {r1.x, r1.y, r1.z, r1.w};
+#pragma unroll
+  for (int wi = 0; wi < 4; ++wi) {
+    const uint32_t u0 = w0[wi], u0s = u0 >> 4, u1 = w1[wi], u1s = u1 >> 4;
+#pragma unroll
+    for (int bi = 0; bi < 4; ++bi) {
+      const uint32_t sel = (uint32_t)bi | ((uint32_t)bi << 4) | ((uint32_t)(4 + bi) << 8) | ((uint32_t)(4 + bi) << 12);
+      const uint32_t b0 = MmaType<CT>::expand(__byte_perm(u0, u0s, sel));
+      const uint32_t b1 = MmaType<CT>::expand(__byte_perm(u1, u1s, sel));
+#pragma unroll
+      for (int t = 0; t < MT; ++t) {
+        MmaType<CT>::mma(acc[t][wi * 4 + bi], a[t], b0, b1);
+        if (kSplitX) MmaType<CT>::mma(acc[t][wi * 4 + bi], alo[t], b0, b1);
+      }
+    }
+  }
+#pragma unroll
+  for (int t = 0; t < MT; ++t) {
+    MmaType<CT>::mma(accx[t], a[t], MmaType<CT>::ones(), MmaType<CT>::ones());
+    if (kSplitX) MmaType<CT>::mma(accx[t], alo[t], MmaType<CT>::ones(), MmaType<CT>::ones());
+  }
 }
 
-// fp32 activations: split into bf16 high and low parts (x = hi + lo + O(2^-17 |x|)).
-__device__ __forceinline__ void load_x2_split(const float* __restrict__ x, int64_t m, int64_t M, int64_t k, int64_t K,
-                                              uint32_t& hi, uint32_t& lo) {
-  hi = 0u; lo = 0u;
-  if (m >= M || k >= K) return;
-  const float2 v = *reinterpret_cast<const float2*>(x + m * K + k);
-  const __nv_bfloat16 h0 = __float2bfloat16_rn(v.x), h1 = __float2bfloat16_rn(v.y);
-  const __nv_bfloat16 l0 = __float2bfloat16_rn(v.x - __bfloat162float(h0));
-  const __nv_bfloat16 l1 = __float2bfloat16_rn(v.y - __bfloat162float(h1));
-  hi = (uint32_t)__bfloat16_as_ushort(h0) | ((uint32_t)__bfloat16_as_ushort(h1) << 16);
-  lo = (uint32_t)__bfloat16_as_ushort(l0) | ((uint32_t)__bfloat16_as_ushort(l1) << 16);
-}
-
-template <typename T> __device__ __forceinline__ float zs_to_f32(const void* p, int64_t i);
-template <> __device__ __forceinline__ float zs_to_f32<float>(const void* p, int64_t i) { return ((const float*)p)[i]; }
-template <> __device__ __forceinline__ float zs_to_f32<__half>(const void* p, int64_t i) { return __half2float(((const __half*)p)[i]); }
+constexpr int W4_NST = 16;                  // ring depth of the TMA-staged variant
+constexpr int W4_STAGE_ROWS = 32;           // byte rows per stage = 4 steps, one per consumer warp
+constexpr int W4_STAGE_BYTES = W4_STAGE_ROWS * WCOLS;
+constexpr int W4_RING_BYTES = W4_NST * W4_STAGE_BYTES + 1024;
 
 // XT: activation/output element type.  MT: 16-row tiles per CTA.
 // CT: MMA operand type (XT itself for f16/bf16, bf16 for fp32 activations).
-template <typename XT, typename CT, int MT, typename ZST>
-__global__ void __launch_bounds__(WWARPS * 32)
+// TMA: weights arrive through a 16-deep shared-memory ring filled by a producer warp with
+//      cp.async.bulk.tensor (needs N % 16 == 0); otherwise each lane loads its bytes directly.
+template <typename XT, typename CT, int MT, typename ZST, bool TMA>
+__global__ void __launch_bounds__(TMA ? (WWARPS + 1) * 32 : WWARPS * 32, (TMA && MT == 1) ? 3 : 1)
 w4_fwd_kernel(const XT* __restrict__ x, const uint8_t* __restrict__ packed,
               const void* __restrict__ zero, const void* __restrict__ scale,
               XT* __restrict__ out, int64_t M, int64_t N, int64_t K,
               int steps_per_split, int ksplit, float* __restrict__ partials, int* __restrict__ tickets,
-              int vec) {
+              int vec, const __grid_constant__ CUtensorMap wmap) {
   constexpr bool kSplitX = std::is_same<XT, float>::value;
   constexpr int ROWS = 16 * MT;
   __shared__ __align__(16) float red[ROWS][PSTRIDE];
   __shared__ int s_last;
+  __shared__ int s_abort;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, q = lane & 3;
@@ -142,52 +127,79 @@ w4_fwd_kernel(const XT* __restrict__ x, const uint8_t* __restrict__ packed,
 #pragma unroll
     for (int i = 0; i < 4; ++i) accx[t][i] = 0.f;
   }
+  if (threadIdx.x == 0) s_abort = 0;
 
-  const int64_t c0 = cbase + 16 * g;
-  for (int64_t step = step_begin + warp; step < step_end; step += WWARPS) {
-    const int64_t j0 = step * 8;
-    const uint4 r0 = load_codes16(packed, j0 + q, KB, c0, N, vec);
-    const uint4 r1 = load_codes16(packed, j0 + 4 + q, KB, c0, N, vec);
-    const int64_t k0 = 2 * j0;
-    uint32_t a[MT][4], alo[MT][4];
-#pragma unroll
-    for (int t = 0; t < MT; ++t) {
-      const int64_t ma = m0 + 16 * t + g, mb = ma + 8;
-      if (kSplitX) {
-        load_x2_split((const float*)x, ma, M, k0 + 2 * q, K, a[t][0], alo[t][0]);
-        load_x2_split((const float*)x, mb, M, k0 + 2 * q, K, a[t][1], alo[t][1]);
-        load_x2_split((const float*)x, ma, M, k0 + 8 + 2 * q, K, a[t][2], alo[t][2]);
-        load_x2_split((const float*)x, mb, M, k0 + 8 + 2 * q, K, a[t][3], alo[t][3]);
-      } else {
-        a[t][0] = load_x2<XT>(x, ma, M, k0 + 2 * q, K);
-        a[t][1] = load_x2<XT>(x, mb, M, k0 + 2 * q, K);
-        a[t][2] = load_x2<XT>(x, ma, M, k0 + 8 + 2 * q, K);
-        a[t][3] = load_x2<XT>(x, mb, M, k0 + 8 + 2 * q, K);
-      }
+  if constexpr (!TMA) {
+    const int64_t c0 = cbase + 16 * g;
+    for (int64_t step = step_begin + warp; step < step_end; step += WWARPS) {
+      const int64_t j0 = step * 8;
+      const uint4 r0 = load_codes16(packed, j0 + q, KB, c0, N, vec);
+      const uint4 r1 = load_codes16(packed, j0 + 4 + q, KB, c0, N, vec);
+      uint32_t a[MT][4], alo[MT][4];
+      load_afrags<XT, MT>(x, m0, M, 2 * j0, K, g, q, a, alo);
+      w4_step<CT, MT, kSplitX>(acc, accx, r0, r1, a, alo);
     }
-    const uint32_t w0[4] = {r0.x, r0.y, r0.z, r0.w};
-    const uint32_t w1[4] = {r1.x, r1.y, r1.z, r1.w};
-#pragma unroll
-    for (int wi = 0; wi < 4; ++wi) {
-      const uint32_t u0 = w0[wi], u0s = u0 >> 4, u1 = w1[wi], u1s = u1 >> 4;
-#pragma unroll
-      for (int bi = 0; bi < 4; ++bi) {
-        const uint32_t sel = (uint32_t)bi | ((uint32_t)bi << 4) | ((uint32_t)(4 + bi) << 8) | ((uint32_t)(4 + bi) << 12);
-        const uint32_t b0 = MmaType<CT>::expand(__byte_perm(u0, u0s, sel));
-        const uint32_t b1 = MmaType<CT>::expand(__byte_perm(u1, u1s, sel));
-#pragma unroll
-        for (int t = 0; t < MT; ++t) {
-          MmaType<CT>::mma(acc[t][wi * 4 + bi], a[t], b0, b1);
-          if (kSplitX) MmaType<CT>::mma(acc[t][wi * 4 + bi], alo[t], b0, b1);
+  } else {
+    using namespace umma;
+    extern __shared__ uint8_t ring_raw[];
+    uint8_t* ring = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(ring_raw) + 1023) & ~uintptr_t(1023));
+    __shared__ __align__(8) uint64_t full_bar[W4_NST];
+    __shared__ __align__(8) uint64_t empty_bar[W4_NST];
+    volatile int* abort_flag = &s_abort;
+    if (threadIdx.x == 0) {
+      for (int i = 0; i < W4_NST; ++i) { mbar_init(&full_bar[i], 1); mbar_init(&empty_bar[i], WWARPS); }
+      fence_barrier_init();
+      prefetch_tensormap(&wmap);
+    }
+    __syncthreads();
+    const int nstage = (int)((step_end - step_begin + 3) / 4);
+    if (warp == WWARPS) {
+      // ---- producer: one 32-row x 128-channel box per stage ----
+      if (lane == 0) {
+        int issued = 0;
+        for (int s = 0; s < nstage; ++s) {
+          const int slot = s % W4_NST;
+          if (s >= W4_NST && !mbar_wait(&empty_bar[slot], ((s / W4_NST) & 1) ^ 1, abort_flag)) break;
+          mbar_expect_tx(&full_bar[slot], W4_STAGE_BYTES);
+          tma_load_2d(ring + slot * W4_STAGE_BYTES, &wmap, (int)cbase, (int)((step_begin + 4 * s) * 8), &full_bar[slot]);
+          issued = s + 1;
+        }
+        if (*abort_flag) {
+          for (int s = max(0, issued - W4_NST); s < issued; ++s) {
+            const long long t0 = clock64();
+            while (!mbar_try_wait(&full_bar[s % W4_NST], (s / W4_NST) & 1) && clock64() - t0 < 20000000LL) {}
+          }
         }
       }
-    }
+    } else {
+      // ---- consumers: warp w takes step w of every stage ----
+      uint32_t a_n[MT][4], alo_n[MT][4];
+      load_afrags<XT, MT>(x, m0, M, 2 * 8 * (step_begin + warp), K, g, q, a_n, alo_n);
+      for (int s = 0; s < nstage; ++s) {
+        const int slot = s % W4_NST;
+        const int64_t step = step_begin + 4 * s + warp;
+        uint32_t a[MT][4], alo[MT][4];
 #pragma unroll
-    for (int t = 0; t < MT; ++t) {
-      MmaType<CT>::mma(accx[t], a[t], MmaType<CT>::ones(), MmaType<CT>::ones());
-      if (kSplitX) MmaType<CT>::mma(accx[t], alo[t], MmaType<CT>::ones(), MmaType<CT>::ones());
+        for (int t = 0; t < MT; ++t)
+#pragma unroll
+          for (int i = 0; i < 4; ++i) { a[t][i] = a_n[t][i]; alo[t][i] = alo_n[t][i]; }
+        if (s + 1 < nstage) load_afrags<XT, MT>(x, m0, M, 2 * 8 * (step + 4), K, g, q, a_n, alo_n);
+        const bool ok = __all_sync(0xffffffffu, mbar_wait(&full_bar[slot], (s / W4_NST) & 1, abort_flag));
+        if (!ok) break;
+        if (step < step_end) {
+          const uint8_t* tile = ring + slot * W4_STAGE_BYTES;
+          const uint4 r0 = *reinterpret_cast<const uint4*>(tile + (8 * warp + q) * WCOLS + 16 * g);
+          const uint4 r1 = *reinterpret_cast<const uint4*>(tile + (8 * warp + 4 + q) * WCOLS + 16 * g);
+          w4_step<CT, MT, kSplitX>(acc, accx, r0, r1, a, alo);
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&empty_bar[slot]);
+      }
     }
+    __syncthreads();
   }
+  const bool aborted = (*(volatile int*)&s_abort) != 0;
+  const float poison = aborted ? __int_as_float(0x7fc00000) : 0.f;   // a timed-out wait must not pass silently
 
   // ---- reduce the 4 warps into warp 0 through shared memory --------------------
   // fragment element (t, b, i): row 16t + g + 8*(i>>1), channel 32q + 16*(i&1) + b
@@ -295,7 +307,7 @@ w4_fwd_kernel(const XT* __restrict__ x, const uint8_t* __restrict__ packed,
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
           const int64_t m = m0 + 16 * t + g + 8 * h;
-          if (m < M) out[m * N + n] = from_f32<XT>(s * (acc[t][b][2 * h + i] - z * accx[t][2 * h]));
+          if (m < M) out[m * N + n] = from_f32<XT>(s * (acc[t][b][2 * h + i] - z * accx[t][2 * h]) + poison);
         }
     }
   }
@@ -368,31 +380,60 @@ static FwdPlan plan_fwd(int64_t M, int64_t N, int64_t K) {
   p.ncg = (int)cdiv(N, WCOLS);
   const int64_t total_steps = cdiv(K / 2, 8);
   const int64_t base = (int64_t)p.ncg * p.mtiles;
-  int64_t want = cdiv(4 * (int64_t)sm_count(), base);
+  const bool tma_shape = (N % 16 == 0);
+  // about 3 (ring variant, 64 KB of shared memory each) or 4 CTAs per SM
+  int64_t want = cdiv((tma_shape ? 3 : 4) * (int64_t)sm_count(), base);
   const int64_t max_split = std::max<int64_t>(1, total_steps / (2 * WWARPS));
   if (want > max_split) want = max_split;
   if (want < 1) want = 1;
   if (base > (int64_t)(kTicketBytes / sizeof(int))) want = 1;
-  p.steps_per_split = (int)cdiv(total_steps, want);
-  p.ksplit = (int)cdiv(total_steps, p.steps_per_split);
+  int64_t sps = cdiv(total_steps, want);
+  if (tma_shape) sps = cdiv(sps, 4) * 4;             // whole ring stages per split
+  p.steps_per_split = (int)sps;
+  p.ksplit = (int)cdiv(total_steps, sps);
   return p;
+}
+
+template <typename XT, typename CT, int MT, typename ZST, bool TMA>
+static int launch_fwd_inst(const FwdPlan& p, const void* x, const uint8_t* packed, const void* zero, const void* scale,
+                           void* out, int64_t M, int64_t N, int64_t K, void* ws, int vec, const CUtensorMap& wmap,
+                           cudaStream_t s) {
+  int* tickets = (int*)ws;                                   // kTicketBytes, zero between launches
+  float* partials = (float*)((char*)ws + kTicketBytes);
+  dim3 grid((unsigned)p.ncg, (unsigned)p.ksplit, (unsigned)p.mtiles);
+  auto kern = w4_fwd_kernel<XT, CT, MT, ZST, TMA>;
+  if (TMA) {
+    static bool attr_set[64] = {false};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev >= 0 && dev < 64 && !attr_set[dev]) {
+      cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, W4_RING_BYTES);
+      attr_set[dev] = true;
+    }
+  }
+  kern<<<grid, TMA ? (WWARPS + 1) * 32 : WWARPS * 32, TMA ? W4_RING_BYTES : 0, s>>>(
+      (const XT*)x, packed, zero, scale, (XT*)out, M, N, K, p.steps_per_split, p.ksplit, partials, tickets, vec, wmap);
+  return check_launch("w4_matmul");
 }
 
 template <typename XT, typename CT, typename ZST>
 static int launch_fwd(const void* x, const uint8_t* packed, const void* zero, const void* scale, void* out,
                       int64_t M, int64_t N, int64_t K, void* ws, cudaStream_t s) {
   const FwdPlan p = plan_fwd(M, N, K);
-  int* tickets = (int*)ws;                                   // kTicketBytes, zero between launches
-  float* partials = (float*)((char*)ws + kTicketBytes);
   const int vec = (N % 16 == 0) && aligned(packed, 16);
-  dim3 grid((unsigned)p.ncg, (unsigned)p.ksplit, (unsigned)p.mtiles);
-  if (p.mt == 1)
-    w4_fwd_kernel<XT, CT, 1, ZST><<<grid, WWARPS * 32, 0, s>>>((const XT*)x, packed, zero, scale, (XT*)out, M, N, K,
-                                                               p.steps_per_split, p.ksplit, partials, tickets, vec);
-  else
-    w4_fwd_kernel<XT, CT, 2, ZST><<<grid, WWARPS * 32, 0, s>>>((const XT*)x, packed, zero, scale, (XT*)out, M, N, K,
-                                                               p.steps_per_split, p.ksplit, partials, tickets, vec);
-  return check_launch("w4_matmul");
+  CUtensorMap wmap;
+  memset(&wmap, 0, sizeof(wmap));
+  bool tma = vec != 0;
+  if (tma) {
+    const int rc = encode_tmap_2d_u8(&wmap, packed, (uint64_t)N, (uint64_t)(K / 2), (uint64_t)N, WCOLS, W4_STAGE_ROWS, 0);
+    if (rc) return rc;
+  }
+  if (p.mt == 1) {
+    return tma ? launch_fwd_inst<XT, CT, 1, ZST, true>(p, x, packed, zero, scale, out, M, N, K, ws, vec, wmap, s)
+               : launch_fwd_inst<XT, CT, 1, ZST, false>(p, x, packed, zero, scale, out, M, N, K, ws, vec, wmap, s);
+  }
+  return tma ? launch_fwd_inst<XT, CT, 2, ZST, true>(p, x, packed, zero, scale, out, M, N, K, ws, vec, wmap, s)
+             : launch_fwd_inst<XT, CT, 2, ZST, false>(p, x, packed, zero, scale, out, M, N, K, ws, vec, wmap, s);
 }
 
 template <typename XT, typename ZST>
