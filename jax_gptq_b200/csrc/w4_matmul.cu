@@ -27,6 +27,7 @@
 #include "w4_common.cuh"
 #include "umma.cuh"
 #include <algorithm>
+#include <cstdlib>
 #include <cstring>
 #include <mutex>
 
@@ -444,6 +445,23 @@ static int launch_tb(const void* x, const uint8_t* packed, const void* zero, con
   return check_launch("w4_matmul_tb");
 }
 
+// tensor-path forward kernel (w4_umma.cu)
+struct UmmaPlan {
+  int use; int NT; int planes; int x_stages; int mtiles; int ncg; int ksplit; int stages_per_split; int tmem_cols;
+  size_t smem_bytes; size_t xsum_bytes; size_t plane_bytes; size_t part_bytes;
+};
+UmmaPlan plan_w4_umma(int64_t M, int64_t N, int64_t K, int x_dtype);
+size_t w4_umma_workspace_bytes(const UmmaPlan& pl);
+int launch_w4_umma(const UmmaPlan& pl, const void* x, int x_dtype, const uint8_t* packed, const void* zero,
+                   const void* scale, int zs_dtype, void* out, int64_t M, int64_t N, int64_t K, void* ws,
+                   cudaStream_t s);
+
+static bool w4_force_mma_sync() {      // JGQ_W4_PATH=mma keeps the mma.sync kernels (for comparisons)
+  static int v = -1;
+  if (v < 0) { const char* e = getenv("JGQ_W4_PATH"); v = (e && !strcmp(e, "mma")) ? 1 : 0; }
+  return v == 1;
+}
+
 }  // namespace jgq
 
 using namespace jgq;
@@ -457,6 +475,12 @@ extern "C" size_t jgq_w4_matmul_workspace_bytes(int64_t M, int64_t N, int64_t K,
   const FwdPlan p = plan_fwd(M, N, K);
   size_t bytes = kTicketBytes;
   if (p.ksplit > 1) bytes += align_up((size_t)p.ksplit * M * p.ncg * PSTRIDE * sizeof(float), 256);
+  // the tensor-path kernel is chosen at call time (it also needs aligned pointers); size for either.
+  // fp32 activations are the worst case for its staging planes.
+  const UmmaPlan up = plan_w4_umma(M, N, K, JGQ_F32);
+  if (up.use) bytes = std::max(bytes, w4_umma_workspace_bytes(up));
+  const UmmaPlan up16 = plan_w4_umma(M, N, K, JGQ_F16);
+  if (up16.use) bytes = std::max(bytes, w4_umma_workspace_bytes(up16));
   return bytes;
 }
 
@@ -487,6 +511,11 @@ extern "C" int jgq_w4_matmul(const void* x, int x_dtype, const uint8_t* packed,
   const size_t need = jgq_w4_matmul_workspace_bytes(M, N, K, 0);
   JGQ_REQUIRE(ws && ws_bytes >= need, JGQ_ERR_WORKSPACE, "w4_matmul: workspace %zu < %zu bytes", ws_bytes, need);
   JGQ_REQUIRE(aligned(ws, 256), JGQ_ERR_ALIGN, "w4_matmul: workspace must be 256-byte aligned");
+  if (!w4_force_mma_sync()) {
+    const UmmaPlan up = plan_w4_umma(M, N, K, x_dtype);
+    if (up.use && aligned(x, 16) && aligned(packed, 16) && aligned(out, 4))
+      return launch_w4_umma(up, x, x_dtype, packed, zero, scale, zs_dtype, out, M, N, K, ws, s);
+  }
 #define JGQ_FWD(XT, CT)                                                                                  \
   return zs_dtype == JGQ_F32 ? launch_fwd<XT, CT, float>(x, packed, zero, scale, out, M, N, K, ws, s)    \
                              : launch_fwd<XT, CT, __half>(x, packed, zero, scale, out, M, N, K, ws, s)

@@ -1,0 +1,430 @@
+// Packed-int4 forward matmul on the Blackwell tensor path (TMA + tcgen05 + TMEM).
+//
+//   out[m, n] = scale[n] * ( sum_k x[m,k] code[k,n]  -  zero[n] * sum_k x[m,k] )
+//
+// One kernel serves decode-sized and prefill-sized M.  A CTA owns 128 output channels,
+// up to 256 tokens and a slice of the contraction range:
+//
+//   warp 0      TMA producer: raw packed bytes (32 byte rows x 128 channels = 64 k per stage)
+//               and the matching activation tile (tokens x 64 k), two mbarrier rings
+//   warps 2-9   expand nibbles to bf16 / f16 with the magic-number trick and write them as
+//               the MMA's A operand: channels are the M dimension (128), stored M-major with
+//               128-byte swizzle, so a 16-byte load of raw bytes (16 channels of one byte row)
+//               becomes two 16-byte chunks for k = 2j and two for k = 2j+1 - no transposition
+//   warp 1      tcgen05.mma (M = 128 channels, N = tokens, K = 16) into a fp32 TMEM accumulator
+//   warps 2-5   epilogue: TMEM -> registers -> scale / zero -> global, or split-K slices
+//
+// The expansion pairs channels (c, c+2) of one byte-row word in a register, so MMA row r of
+// a CTA is channel (r & ~3) | {0,2,1,3}[r & 3]; the epilogue undoes that with index math.
+// At small M the kernel is HBM-bound (one pass over K*N/2 bytes, ~1.3 instructions per code
+// for the expansion, everything else on the tensor pipe); at large M it is tensor-bound.
+#include "umma.cuh"
+#include "w4_common.cuh"
+#include <algorithm>
+#include <cstring>
+
+namespace jgq {
+
+constexpr int U_COLS = 128;                    // channels per CTA (MMA M)
+constexpr int U_STAGE_K = 64;                  // contraction elements per stage
+constexpr int U_RAW_BYTES = 32 * U_COLS;       // 32 byte rows x 128 channels
+constexpr int U_A_BYTES = U_STAGE_K * U_COLS * 2;   // expanded A tile: 2 groups x 64 k x 128 B
+constexpr int U_RAW_ST = 8, U_A_ST = 4;
+constexpr int U_DQ_WARPS = 8;
+constexpr int U_THREADS = (2 + U_DQ_WARPS) * 32;
+constexpr size_t U_TICKET_BYTES = 4096;
+
+struct UmmaParams {
+  const uint8_t* packed;
+  const void* zero; const void* scale;
+  void* out;
+  const float* xsum;          // [M] sum over k of x[m, k]
+  float* partials; int* tickets;
+  int64_t M, N, K;
+  int NT;                     // tokens per CTA (MMA N), multiple of 16
+  int planes;                 // 1, or 2 for fp32 activations split into bf16 high / low
+  int fmt;                    // 0 = f16, 1 = bf16 operands
+  int x_stages;               // depth of the activation ring
+  int stages_per_split, ksplit, ncg, mtiles;
+  int tmem_cols;
+};
+
+template <typename T>
+__global__ void xsum_kernel(const T* __restrict__ x, float* __restrict__ xsum, int64_t K) {
+  __shared__ float part[8];
+  const int64_t m = blockIdx.x;
+  float s = 0.f;
+  for (int64_t k = threadIdx.x; k < K; k += blockDim.x) s += to_f32<T>(x[m * K + k]);
+  for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+  if ((threadIdx.x & 31) == 0) part[threadIdx.x >> 5] = s;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float t = 0.f;
+    for (int w = 0; w < (int)(blockDim.x >> 5); ++w) t += part[w];
+    xsum[m] = t;
+  }
+}
+
+__global__ void split_x_bf16_kernel(const float* __restrict__ X, __nv_bfloat16* __restrict__ P0,
+                                    __nv_bfloat16* __restrict__ P1, int64_t total) {
+  for (int64_t t = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; t < total;
+       t += (int64_t)gridDim.x * blockDim.x) {
+    const float v = X[t];
+    const __nv_bfloat16 h = __float2bfloat16_rn(v);
+    P0[t] = h;
+    P1[t] = __float2bfloat16_rn(v - __bfloat162float(h));
+  }
+}
+
+// 8 codes of one 32-bit word (4 channels x {k even, k odd}) -> four 2-channel registers.
+// e02 / e13: k even, channels (0,2) / (1,3);  o02 / o13: k odd.
+template <int FMT>
+__device__ __forceinline__ void expand_word(uint32_t w, uint32_t& e02, uint32_t& e13, uint32_t& o02, uint32_t& o13) {
+  if (FMT == 0) {   // f16: 0x6400 | c = 1024 + c ; 0x6400 | (c << 4) = 1024 + 16 c
+    const uint32_t w8 = w >> 8;
+    uint32_t a = (w & 0x000F000Fu) | 0x64006400u, b = (w8 & 0x000F000Fu) | 0x64006400u;
+    uint32_t c = (w & 0x00F000F0u) | 0x64006400u, d = (w8 & 0x00F000F0u) | 0x64006400u;
+    const __half2 k1024 = __half2half2(__float2half_rn(1024.f));
+    const __half2 k16th = __half2half2(__float2half_rn(0.0625f)), k64 = __half2half2(__float2half_rn(-64.f));
+    __half2 ra = __hsub2(*reinterpret_cast<__half2*>(&a), k1024), rb = __hsub2(*reinterpret_cast<__half2*>(&b), k1024);
+    __half2 rc = __hfma2(*reinterpret_cast<__half2*>(&c), k16th, k64), rd = __hfma2(*reinterpret_cast<__half2*>(&d), k16th, k64);
+    e02 = *reinterpret_cast<uint32_t*>(&ra); e13 = *reinterpret_cast<uint32_t*>(&rb);
+    o02 = *reinterpret_cast<uint32_t*>(&rc); o13 = *reinterpret_cast<uint32_t*>(&rd);
+  } else {          // bf16: 0x4300 | c = 128 + c
+    uint32_t a = (w & 0x000F000Fu) | 0x43004300u, b = ((w >> 8) & 0x000F000Fu) | 0x43004300u;
+    uint32_t c = ((w >> 4) & 0x000F000Fu) | 0x43004300u, d = ((w >> 12) & 0x000F000Fu) | 0x43004300u;
+    const __nv_bfloat162 k128 = __float2bfloat162_rn(128.f);
+    __nv_bfloat162 ra = __hsub2(*reinterpret_cast<__nv_bfloat162*>(&a), k128);
+    __nv_bfloat162 rb = __hsub2(*reinterpret_cast<__nv_bfloat162*>(&b), k128);
+    __nv_bfloat162 rc = __hsub2(*reinterpret_cast<__nv_bfloat162*>(&c), k128);
+    __nv_bfloat162 rd = __hsub2(*reinterpret_cast<__nv_bfloat162*>(&d), k128);
+    e02 = *reinterpret_cast<uint32_t*>(&ra); e13 = *reinterpret_cast<uint32_t*>(&rb);
+    o02 = *reinterpret_cast<uint32_t*>(&rc); o13 = *reinterpret_cast<uint32_t*>(&rd);
+  }
+}
+
+template <typename XT, typename ZST, int FMT>
+__global__ void __launch_bounds__(U_THREADS, 1)
+w4_umma_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__ CUtensorMap xmap0,
+               const __grid_constant__ CUtensorMap xmap1, const UmmaParams p) {
+  using namespace umma;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  const int x_plane_bytes = p.NT * 128;
+  const int x_stage_bytes = x_plane_bytes * p.planes;
+  uint8_t* raw_ring = smem;
+  uint8_t* a_ring = raw_ring + U_RAW_ST * U_RAW_BYTES;
+  uint8_t* x_ring = a_ring + U_A_ST * U_A_BYTES;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(x_ring + p.x_stages * x_stage_bytes);
+  uint64_t* raw_full = bars;                    // [U_RAW_ST]
+  uint64_t* raw_empty = raw_full + U_RAW_ST;    // [U_RAW_ST]
+  uint64_t* a_full = raw_empty + U_RAW_ST;      // [U_A_ST]
+  uint64_t* a_empty = a_full + U_A_ST;          // [U_A_ST]
+  uint64_t* x_full = a_empty + U_A_ST;          // [4]
+  uint64_t* x_empty = x_full + 4;               // [4]
+  uint64_t* acc_bar = x_empty + 4;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_bar + 1);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  int* s_last = const_cast<int*>(reinterpret_cast<volatile int*>(tmem_slot + 2));
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int cg = blockIdx.x, split = blockIdx.y, mtile = blockIdx.z;
+  const int64_t cbase = (int64_t)cg * U_COLS;
+  const int64_t m0 = (int64_t)mtile * p.NT;
+  const int64_t total_stages = (p.K + U_STAGE_K - 1) / U_STAGE_K;
+  const int64_t st_begin = (int64_t)split * p.stages_per_split;
+  const int nst = (int)(min(total_stages, st_begin + p.stages_per_split) - st_begin);
+
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < U_RAW_ST; ++i) { mbar_init(&raw_full[i], 1); mbar_init(&raw_empty[i], U_DQ_WARPS); }
+    for (int i = 0; i < U_A_ST; ++i) { mbar_init(&a_full[i], U_DQ_WARPS); mbar_init(&a_empty[i], 1); }
+    for (int i = 0; i < 4; ++i) { mbar_init(&x_full[i], 1); mbar_init(&x_empty[i], 1); }
+    mbar_init(acc_bar, 1);
+    *abort_flag = 0;
+    *s_last = 0;
+    fence_barrier_init();
+    prefetch_tensormap(&wmap);
+    prefetch_tensormap(&xmap0);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, (uint32_t)p.tmem_cols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_acc = *tmem_slot;
+
+  if (warp == 0) {
+    // ===================== TMA producer =====================
+    if (lane == 0) {
+      int issued = 0;
+      for (int i = 0; i < nst; ++i) {
+        const int rs = i % U_RAW_ST, xs = i % p.x_stages;
+        const int64_t stage = st_begin + i;
+        if (i >= U_RAW_ST && !mbar_wait(&raw_empty[rs], ((i / U_RAW_ST) & 1) ^ 1, abort_flag)) break;
+        mbar_expect_tx(&raw_full[rs], U_RAW_BYTES);
+        tma_load_2d(raw_ring + rs * U_RAW_BYTES, &wmap, (int)cbase, (int)(stage * 32), &raw_full[rs]);
+        if (i >= p.x_stages && !mbar_wait(&x_empty[xs], ((i / p.x_stages) & 1) ^ 1, abort_flag)) break;
+        mbar_expect_tx(&x_full[xs], (uint32_t)x_stage_bytes);
+        tma_load_2d(x_ring + xs * x_stage_bytes, &xmap0, (int)(stage * U_STAGE_K), (int)m0, &x_full[xs]);
+        if (p.planes > 1)
+          tma_load_2d(x_ring + xs * x_stage_bytes + x_plane_bytes, &xmap1, (int)(stage * U_STAGE_K), (int)m0, &x_full[xs]);
+        issued = i + 1;
+      }
+      if (*abort_flag) {
+        for (int i = max(0, issued - U_RAW_ST); i < issued; ++i) {
+          const long long t0 = clock64();
+          while (!mbar_try_wait(&raw_full[i % U_RAW_ST], (i / U_RAW_ST) & 1) && clock64() - t0 < 20000000LL) {}
+        }
+        for (int i = max(0, issued - p.x_stages); i < issued; ++i) {
+          const long long t0 = clock64();
+          while (!mbar_try_wait(&x_full[i % p.x_stages], (i / p.x_stages) & 1) && clock64() - t0 < 20000000LL) {}
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ===================== MMA issuer =====================
+    if (lane == 0) {
+      const uint32_t idesc = make_idesc_f16(p.fmt, /*a M-major*/ 1, /*b K-major*/ 0, U_COLS, p.NT);
+      bool ok = true;
+      for (int i = 0; i < nst && ok; ++i) {
+        const int as = i % U_A_ST, xs = i % p.x_stages;
+        ok = mbar_wait(&a_full[as], (i / U_A_ST) & 1, abort_flag) &&
+             mbar_wait(&x_full[xs], (i / p.x_stages) & 1, abort_flag);
+        if (!ok) break;
+        tc_fence_after();
+        const uint32_t a_base = smem_u32(a_ring + as * U_A_BYTES);
+        const uint32_t x_base = smem_u32(x_ring + xs * x_stage_bytes);
+#pragma unroll
+        for (int k16 = 0; k16 < U_STAGE_K / 16; ++k16) {
+          const uint64_t da = make_desc_sw128(a_base + k16 * 2048, 8192, 1024);
+          for (int pl = 0; pl < p.planes; ++pl) {
+            const uint64_t db = make_desc_sw128(x_base + pl * x_plane_bytes + k16 * 32, 16, 1024);
+            mma_f16_ss(tmem_acc, da, db, idesc, (i > 0 || k16 > 0 || pl > 0) ? 1u : 0u);
+          }
+        }
+        mma_commit(&a_empty[as]);
+        mma_commit(&x_empty[xs]);
+      }
+      if (ok) mma_commit(acc_bar);
+    }
+  } else {
+    // ===================== nibble expansion (warps 2..9) =====================
+    const int dt = threadIdx.x - 64;            // 0..255: one 16-byte load per stage
+    const int row = dt >> 3, cgp = dt & 7;      // byte row 0..31, 16-channel group 0..7
+    const int ngroup = cgp >> 2, ch0 = (cgp & 3) * 2;
+    bool ok = true;
+    for (int i = 0; i < nst; ++i) {
+      const int rs = i % U_RAW_ST, as = i % U_A_ST;
+      ok = __all_sync(0xffffffffu, mbar_wait(&raw_full[rs], (i / U_RAW_ST) & 1, abort_flag));
+      if (!ok) break;
+      const uint4 v = *reinterpret_cast<const uint4*>(raw_ring + rs * U_RAW_BYTES + row * U_COLS + cgp * 16);
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&raw_empty[rs]);
+      if (i >= U_A_ST) {
+        ok = __all_sync(0xffffffffu, mbar_wait(&a_empty[as], ((i / U_A_ST) & 1) ^ 1, abort_flag));
+        if (!ok) break;
+        tc_fence_after();
+      }
+      uint32_t e[8], o[8];     // k even / k odd: 16 channels each, in expanded order
+      expand_word<FMT>(v.x, e[0], e[1], o[0], o[1]);
+      expand_word<FMT>(v.y, e[2], e[3], o[2], o[3]);
+      expand_word<FMT>(v.z, e[4], e[5], o[4], o[5]);
+      expand_word<FMT>(v.w, e[6], e[7], o[6], o[7]);
+      uint8_t* grp = a_ring + as * U_A_BYTES + ngroup * 8192;
+      const int ke = 2 * row, ko = 2 * row + 1;
+      *reinterpret_cast<uint4*>(grp + ke * 128 + (((ch0 + 0) ^ (ke & 7)) << 4)) = make_uint4(e[0], e[1], e[2], e[3]);
+      *reinterpret_cast<uint4*>(grp + ke * 128 + (((ch0 + 1) ^ (ke & 7)) << 4)) = make_uint4(e[4], e[5], e[6], e[7]);
+      *reinterpret_cast<uint4*>(grp + ko * 128 + (((ch0 + 0) ^ (ko & 7)) << 4)) = make_uint4(o[0], o[1], o[2], o[3]);
+      *reinterpret_cast<uint4*>(grp + ko * 128 + (((ch0 + 1) ^ (ko & 7)) << 4)) = make_uint4(o[4], o[5], o[6], o[7]);
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&a_full[as]);
+    }
+
+    // ===================== epilogue (warps 2..5) =====================
+    if (warp < 6) {
+      const bool done = __all_sync(0xffffffffu, mbar_wait(acc_bar, 0, abort_flag));
+      tc_fence_after();
+      const int q = warp & 3;
+      const int r = 32 * q + lane;                                   // MMA row = TMEM lane
+      const int chan = (r & ~3) | ((r & 1) << 1) | ((r >> 1) & 1);   // {0,2,1,3}[r & 3]
+      const int64_t n = cbase + chan;
+      const bool aborted = !done;
+      float sc = 0.f, zr = 0.f;
+      if (n < p.N) { sc = zs_to_f32<ZST>(p.scale, n); zr = zs_to_f32<ZST>(p.zero, n); }
+      const int ntok = (int)((p.M - m0 < (int64_t)p.NT) ? (p.M - m0) : (int64_t)p.NT);
+      XT* outp = reinterpret_cast<XT*>(p.out);
+      for (int c = 0; c < p.NT && !aborted; c += 32) {
+        uint32_t v[32];
+        tmem_ld_32x32(tmem_acc + ((uint32_t)(32 * q) << 16) + (uint32_t)c, v);
+        tmem_ld_wait();
+        if (p.ksplit == 1) {
+          if (n < p.N) {
+#pragma unroll
+            for (int t = 0; t < 32; ++t) {
+              const int tok = c + t;
+              if (tok < ntok)
+                outp[(m0 + tok) * p.N + n] = from_f32<XT>(sc * (__uint_as_float(v[t]) - zr * p.xsum[m0 + tok]));
+            }
+          }
+        } else {
+#pragma unroll
+          for (int t = 0; t < 32; ++t) {
+            const int tok = c + t;
+            if (tok < ntok)
+              p.partials[(((int64_t)split * p.M + m0 + tok) * p.ncg + cg) * U_COLS + r] = __uint_as_float(v[t]);
+          }
+        }
+      }
+      if (p.ksplit > 1) {
+        // publish the slice; the CTA that draws the last ticket of this (channel group, token tile)
+        // adds all slices in slice order and writes the result
+        __threadfence();
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        if (warp == 2 && lane == 0) {
+          const int old = atomicAdd(&p.tickets[mtile * p.ncg + cg], 1);
+          *s_last = (old == p.ksplit - 1);
+          if (old == p.ksplit - 1) p.tickets[mtile * p.ncg + cg] = 0;
+        }
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        if (*reinterpret_cast<volatile int*>(s_last) && n < p.N) {
+          __threadfence();
+          for (int tok = 0; tok < ntok; ++tok) {
+            float acc = 0.f;
+            for (int z = 0; z < p.ksplit; ++z)
+              acc += __ldcg(&p.partials[(((int64_t)z * p.M + m0 + tok) * p.ncg + cg) * U_COLS + r]);
+            const float poison = aborted ? __int_as_float(0x7fc00000) : 0.f;
+            outp[(m0 + tok) * p.N + n] = from_f32<XT>(sc * (acc - zr * p.xsum[m0 + tok]) + poison);
+          }
+        }
+      } else if (aborted && n < p.N) {
+        for (int tok = 0; tok < ntok; ++tok) outp[(m0 + tok) * p.N + n] = from_f32<XT>(__int_as_float(0x7fc00000));
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_acc, (uint32_t)p.tmem_cols);
+  }
+}
+
+// ------------------------------------------------------------------ host ----
+struct UmmaPlan {
+  int use; int NT; int planes; int x_stages; int mtiles; int ncg; int ksplit; int stages_per_split; int tmem_cols;
+  size_t smem_bytes; size_t xsum_bytes; size_t plane_bytes; size_t part_bytes;
+};
+
+UmmaPlan plan_w4_umma(int64_t M, int64_t N, int64_t K, int x_dtype) {
+  UmmaPlan pl;
+  memset(&pl, 0, sizeof(pl));
+  if (M < 1 || N % 16 != 0 || K % 8 != 0) return pl;
+  pl.use = 1;
+  pl.planes = (x_dtype == JGQ_F32) ? 2 : 1;
+  const int64_t max_nt = pl.planes == 2 ? 128 : 256;
+  const int64_t per_tile = std::min<int64_t>(M, max_nt);
+  pl.NT = (int)(cdiv(per_tile, 16) * 16);
+  pl.mtiles = (int)cdiv(M, pl.NT);
+  pl.ncg = (int)cdiv(N, U_COLS);
+  pl.tmem_cols = pl.NT <= 32 ? 32 : pl.NT <= 64 ? 64 : pl.NT <= 128 ? 128 : 256;
+  const size_t x_stage = (size_t)pl.NT * 128 * pl.planes;
+  const size_t fixed = (size_t)U_RAW_ST * U_RAW_BYTES + (size_t)U_A_ST * U_A_BYTES;
+  int xs = (int)std::min<size_t>(4, (((size_t)220 << 10) - fixed) / x_stage);
+  pl.x_stages = std::max(2, xs);
+  pl.smem_bytes = fixed + pl.x_stages * x_stage + 1024 + 512;
+  const int64_t total_stages = cdiv(K, U_STAGE_K);
+  const int64_t base = (int64_t)pl.ncg * pl.mtiles;
+  const int sms = sm_count();
+  int64_t kmax = std::max<int64_t>(1, total_stages / 8);          // at least 8 stages per CTA
+  if (base > (int64_t)(U_TICKET_BYTES / sizeof(int))) kmax = 1;
+  kmax = std::min<int64_t>(kmax, 64);
+  int64_t best = 1;
+  double best_eff = 0.0;
+  for (int64_t s = 1; s <= kmax; ++s) {
+    const int64_t sps = cdiv(total_stages, s);
+    const int64_t ks = cdiv(total_stages, sps);
+    const int64_t ctas = base * ks;
+    const double eff = (double)ctas / (double)(cdiv(ctas, sms) * sms);
+    if (eff > best_eff + 1e-9) { best_eff = eff; best = s; }
+    if (eff >= 0.92) { best = s; break; }
+  }
+  pl.stages_per_split = (int)cdiv(total_stages, best);
+  pl.ksplit = (int)cdiv(total_stages, pl.stages_per_split);
+  pl.xsum_bytes = align_up((size_t)M * sizeof(float), 256);
+  pl.plane_bytes = pl.planes == 2 ? align_up((size_t)M * K * 2, 256) : 0;
+  pl.part_bytes = pl.ksplit > 1 ? align_up((size_t)pl.ksplit * M * pl.ncg * U_COLS * sizeof(float), 256) : 0;
+  return pl;
+}
+
+size_t w4_umma_workspace_bytes(const UmmaPlan& pl) {
+  return U_TICKET_BYTES + pl.xsum_bytes + 2 * pl.plane_bytes + pl.part_bytes;
+}
+
+template <typename XT, typename ZST, int FMT>
+static int launch_inst(const UmmaPlan& pl, const UmmaParams& p, const CUtensorMap& wmap, const CUtensorMap& x0,
+                       const CUtensorMap& x1, cudaStream_t s) {
+  auto kern = w4_umma_kernel<XT, ZST, FMT>;
+  static size_t attr_bytes[64] = {0};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev >= 0 && dev < 64 && attr_bytes[dev] < pl.smem_bytes) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(227 << 10) - 1024) != cudaSuccess)
+      return fail(JGQ_ERR_CUDA, "w4_matmul: cannot raise the dynamic shared memory limit");
+    attr_bytes[dev] = (size_t)(227 << 10);
+  }
+  dim3 grid((unsigned)pl.ncg, (unsigned)pl.ksplit, (unsigned)pl.mtiles);
+  kern<<<grid, U_THREADS, pl.smem_bytes, s>>>(wmap, x0, x1, p);
+  return check_launch("w4_umma");
+}
+
+int launch_w4_umma(const UmmaPlan& pl, const void* x, int x_dtype, const uint8_t* packed, const void* zero,
+                   const void* scale, int zs_dtype, void* out, int64_t M, int64_t N, int64_t K, void* ws,
+                   cudaStream_t s) {
+  uint8_t* w = (uint8_t*)ws;
+  UmmaParams p;
+  memset(&p, 0, sizeof(p));
+  p.tickets = (int*)w; w += U_TICKET_BYTES;
+  float* xsum = (float*)w; w += pl.xsum_bytes;
+  const void* plane0 = x;
+  const void* plane1 = x;
+  if (pl.planes == 2) {
+    __nv_bfloat16* P0 = (__nv_bfloat16*)w;
+    __nv_bfloat16* P1 = (__nv_bfloat16*)(w + pl.plane_bytes);
+    w += 2 * pl.plane_bytes;
+    const int64_t total = M * K;
+    const int blocks = (int)std::min<int64_t>(cdiv(total, 256), (int64_t)sm_count() * 8);
+    split_x_bf16_kernel<<<blocks, 256, 0, s>>>((const float*)x, P0, P1, total);
+    JGQ_LAUNCHED();
+    plane0 = P0; plane1 = P1;
+  }
+  p.partials = (float*)w;
+  if (x_dtype == JGQ_F32)      xsum_kernel<float><<<(unsigned)M, 256, 0, s>>>((const float*)x, xsum, K);
+  else if (x_dtype == JGQ_F16) xsum_kernel<__half><<<(unsigned)M, 256, 0, s>>>((const __half*)x, xsum, K);
+  else                         xsum_kernel<__nv_bfloat16><<<(unsigned)M, 256, 0, s>>>((const __nv_bfloat16*)x, xsum, K);
+  JGQ_LAUNCHED();
+  CUtensorMap wmap, x0, x1;
+  int rc = encode_tmap_2d_u8(&wmap, packed, (uint64_t)N, (uint64_t)(K / 2), (uint64_t)N, U_COLS, 32, 0);
+  if (rc) return rc;
+  rc = encode_tmap_2d_b16(&x0, plane0, (uint64_t)K, (uint64_t)M, (uint64_t)K * 2, 64, (uint32_t)pl.NT);
+  if (rc) return rc;
+  rc = encode_tmap_2d_b16(&x1, plane1, (uint64_t)K, (uint64_t)M, (uint64_t)K * 2, 64, (uint32_t)pl.NT);
+  if (rc) return rc;
+  p.packed = packed; p.zero = zero; p.scale = scale; p.out = out; p.xsum = xsum;
+  p.M = M; p.N = N; p.K = K; p.NT = pl.NT; p.planes = pl.planes;
+  p.fmt = (x_dtype == JGQ_F16) ? 0 : 1;
+  p.x_stages = pl.x_stages; p.stages_per_split = pl.stages_per_split; p.ksplit = pl.ksplit;
+  p.ncg = pl.ncg; p.mtiles = pl.mtiles; p.tmem_cols = pl.tmem_cols;
+  const bool zf32 = zs_dtype == JGQ_F32;
+  if (x_dtype == JGQ_F16)
+    return zf32 ? launch_inst<__half, float, 0>(pl, p, wmap, x0, x1, s) : launch_inst<__half, __half, 0>(pl, p, wmap, x0, x1, s);
+  if (x_dtype == JGQ_BF16)
+    return zf32 ? launch_inst<__nv_bfloat16, float, 1>(pl, p, wmap, x0, x1, s)
+                : launch_inst<__nv_bfloat16, __half, 1>(pl, p, wmap, x0, x1, s);
+  return zf32 ? launch_inst<float, float, 1>(pl, p, wmap, x0, x1, s) : launch_inst<float, __half, 1>(pl, p, wmap, x0, x1, s);
+}
+
+}  // namespace jgq
