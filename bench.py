@@ -402,7 +402,7 @@ def run_ours(args):
         dist.destroy_process_group()
 
 
-def bench_w4(torch, G, dev, peaks):
+def bench_w4(torch, G, dev, peaks, cases=None):
     """Config-3 sweep on one GPU: fp16 activations, fp16 scale/zero; weights rotated over
     enough distinct buffers to exceed L2 between launches."""
     hbm = float(peaks.get('hbm_gbs', 6650.0))
@@ -410,14 +410,17 @@ def bench_w4(torch, G, dev, peaks):
     rows = []
     gen = torch.Generator(device=dev).manual_seed(3003)
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    for K, N in ((4096, 4096), (4096, 11008), (11008, 4096), (8192, 28672)):
+    shapes = ((4096, 4096), (4096, 11008), (11008, 4096), (8192, 28672))
+    if cases:
+        shapes = tuple(dict.fromkeys((k, n) for k, n, _ in cases))
+    for K, N in shapes:
         wbytes = K * N // 2
         nbuf = max(2, -(-(300 << 20) // wbytes))
         packed = [torch.randint(0, 256, (K // 2, N), generator=gen, device=dev, dtype=torch.uint8) for _ in range(nbuf)]
         scale = (0.001 + 0.019 * torch.rand(N, generator=gen, device=dev)).half()
         zero = torch.randint(0, 16, (N,), generator=gen, device=dev).half()
         qms = [G.QuantizedMatrix(p, zero, scale) for p in packed]
-        for M in (1, 16, 128, 2048):
+        for M in ((1, 16, 128, 2048) if not cases else tuple(m for k, n, m in cases if (k, n) == (K, N))):
             x = torch.randn((M, K), generator=gen, device=dev).half()
             iters = 20 if M <= 128 else 3
             # launched straight through the C ABI so that host-side Python time does not
@@ -459,9 +462,22 @@ def main():
     ap.add_argument('--impl', default='ours', choices=['ours', 'reference'])
     ap.add_argument('--layers', type=int, default=N_LAYERS, help='blocks to quantize (12 = the full workload)')
     ap.add_argument('--skip-matmul', action='store_true')
+    ap.add_argument('--only-matmul', action='store_true', help='run only the packed-int4 matmul sweep')
+    ap.add_argument('--matmul-shapes', default='', help='comma list of KxNxM cases for --only-matmul')
     ap.add_argument('--skip-cpu', action='store_true')
     args = ap.parse_args()
-    if args.impl == 'reference':
+    if args.only_matmul:
+        import torch
+        import jax_gptq_b200 as G
+        torch.cuda.set_device(0)
+        peaks = {}
+        try:
+            peaks = json.load(open(os.path.join(ROOT, 'MEASURED_PEAKS.json')))
+        except (OSError, ValueError):
+            pass
+        cases = [tuple(int(v) for v in c.split('x')) for c in args.matmul_shapes.split(',') if c]
+        print(json.dumps({'w4_matmul': bench_w4(torch, G, torch.device('cuda', 0), peaks, cases or None)}), flush=True)
+    elif args.impl == 'reference':
         run_reference(args)
     else:
         run_ours(args)
