@@ -45,10 +45,12 @@ constexpr long long kWaitBudgetCycles = 4000000000LL;   // ~2 s at 2 GHz
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort) {
   if (mbar_try_wait(bar, parity)) return true;
   const long long t0 = clock64();
-  while (true) {
+  for (unsigned spin = 1;; ++spin) {
     if (mbar_try_wait(bar, parity)) return true;
-    if (*abort) return false;
-    if (clock64() - t0 > kWaitBudgetCycles) { *abort = 1; return false; }
+    if ((spin & 31u) == 0) {           // the abort flag and the clock are looked at once per 32 polls
+      if (*abort) return false;
+      if (clock64() - t0 > kWaitBudgetCycles) { *abort = 1; return false; }
+    }
   }
 }
 

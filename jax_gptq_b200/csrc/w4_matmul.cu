@@ -447,7 +447,7 @@ static int launch_tb(const void* x, const uint8_t* packed, const void* zero, con
 
 // tensor-path forward kernel (w4_umma.cu)
 struct UmmaPlan {
-  int use; int NT; int planes; int x_stages; int mtiles; int ncg; int ksplit; int stages_per_split; int tmem_cols;
+  int use; int NT; int planes; int raw_stages; int a_stages; int x_stages; int mtiles; int ncg; int ksplit; int stages_per_split; int tmem_cols;
   size_t smem_bytes; size_t xsum_bytes; size_t plane_bytes; size_t part_bytes;
 };
 UmmaPlan plan_w4_umma(int64_t M, int64_t N, int64_t K, int x_dtype);

@@ -29,7 +29,7 @@ constexpr int U_COLS = 128;                    // channels per CTA (MMA M)
 constexpr int U_STAGE_K = 64;                  // contraction elements per stage
 constexpr int U_RAW_BYTES = 32 * U_COLS;       // 32 byte rows x 128 channels
 constexpr int U_A_BYTES = U_STAGE_K * U_COLS * 2;   // expanded A tile: 2 groups x 64 k x 128 B
-constexpr int U_RAW_ST = 8, U_A_ST = 4;
+constexpr int U_MAX_ST = 8;                    // upper bound of every ring depth
 constexpr int U_DQ_WARPS = 8;
 constexpr int U_THREADS = (2 + U_DQ_WARPS) * 32;
 constexpr size_t U_TICKET_BYTES = 4096;
@@ -44,7 +44,7 @@ struct UmmaParams {
   int NT;                     // tokens per CTA (MMA N), multiple of 16
   int planes;                 // 1, or 2 for fp32 activations split into bf16 high / low
   int fmt;                    // 0 = f16, 1 = bf16 operands
-  int x_stages;               // depth of the activation ring
+  int raw_stages, a_stages, x_stages;   // ring depths: raw bytes, expanded A tiles, activation tiles
   int stages_per_split, ksplit, ncg, mtiles;
   int tmem_cols;
 };
@@ -113,16 +113,17 @@ w4_umma_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__
   const int x_plane_bytes = p.NT * 128;
   const int x_stage_bytes = x_plane_bytes * p.planes;
   uint8_t* raw_ring = smem;
-  uint8_t* a_ring = raw_ring + U_RAW_ST * U_RAW_BYTES;
-  uint8_t* x_ring = a_ring + U_A_ST * U_A_BYTES;
+  const int RAW_ST = p.raw_stages, A_ST = p.a_stages;
+  uint8_t* a_ring = raw_ring + RAW_ST * U_RAW_BYTES;
+  uint8_t* x_ring = a_ring + A_ST * U_A_BYTES;
   uint64_t* bars = reinterpret_cast<uint64_t*>(x_ring + p.x_stages * x_stage_bytes);
-  uint64_t* raw_full = bars;                    // [U_RAW_ST]
-  uint64_t* raw_empty = raw_full + U_RAW_ST;    // [U_RAW_ST]
-  uint64_t* a_full = raw_empty + U_RAW_ST;      // [U_A_ST]
-  uint64_t* a_empty = a_full + U_A_ST;          // [U_A_ST]
-  uint64_t* x_full = a_empty + U_A_ST;          // [4]
-  uint64_t* x_empty = x_full + 4;               // [4]
-  uint64_t* acc_bar = x_empty + 4;
+  uint64_t* raw_full = bars;                    // each ring has room for U_MAX_ST barriers
+  uint64_t* raw_empty = raw_full + U_MAX_ST;
+  uint64_t* a_full = raw_empty + U_MAX_ST;
+  uint64_t* a_empty = a_full + U_MAX_ST;
+  uint64_t* x_full = a_empty + U_MAX_ST;
+  uint64_t* x_empty = x_full + U_MAX_ST;
+  uint64_t* acc_bar = x_empty + U_MAX_ST;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_bar + 1);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   int* s_last = const_cast<int*>(reinterpret_cast<volatile int*>(tmem_slot + 2));
@@ -136,9 +137,11 @@ w4_umma_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__
   const int nst = (int)(min(total_stages, st_begin + p.stages_per_split) - st_begin);
 
   if (threadIdx.x == 0) {
-    for (int i = 0; i < U_RAW_ST; ++i) { mbar_init(&raw_full[i], 1); mbar_init(&raw_empty[i], U_DQ_WARPS); }
-    for (int i = 0; i < U_A_ST; ++i) { mbar_init(&a_full[i], U_DQ_WARPS); mbar_init(&a_empty[i], 1); }
-    for (int i = 0; i < 4; ++i) { mbar_init(&x_full[i], 1); mbar_init(&x_empty[i], 1); }
+    for (int i = 0; i < U_MAX_ST; ++i) {
+      mbar_init(&raw_full[i], 1); mbar_init(&raw_empty[i], 1);     // a stage belongs to one expansion warp
+      mbar_init(&a_full[i], 1); mbar_init(&a_empty[i], 1);
+      mbar_init(&x_full[i], 1); mbar_init(&x_empty[i], 1);
+    }
     mbar_init(acc_bar, 1);
     *abort_flag = 0;
     *s_last = 0;
@@ -160,9 +163,9 @@ w4_umma_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__
     if (lane == 0) {
       int issued = 0;
       for (int i = 0; i < nst; ++i) {
-        const int rs = i % U_RAW_ST, xs = i % p.x_stages;
+        const int rs = i % RAW_ST, xs = i % p.x_stages;
         const int64_t stage = st_begin + i;
-        if (i >= U_RAW_ST && !mbar_wait(&raw_empty[rs], ((i / U_RAW_ST) & 1) ^ 1, abort_flag)) break;
+        if (i >= RAW_ST && !mbar_wait(&raw_empty[rs], ((i / RAW_ST) & 1) ^ 1, abort_flag)) break;
         mbar_expect_tx(&raw_full[rs], U_RAW_BYTES);
         tma_load_2d(raw_ring + rs * U_RAW_BYTES, &wmap, (int)cbase, (int)(stage * 32), &raw_full[rs]);
         if (i >= p.x_stages && !mbar_wait(&x_empty[xs], ((i / p.x_stages) & 1) ^ 1, abort_flag)) break;
@@ -173,9 +176,9 @@ w4_umma_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__
         issued = i + 1;
       }
       if (*abort_flag) {
-        for (int i = max(0, issued - U_RAW_ST); i < issued; ++i) {
+        for (int i = max(0, issued - RAW_ST); i < issued; ++i) {
           const long long t0 = clock64();
-          while (!mbar_try_wait(&raw_full[i % U_RAW_ST], (i / U_RAW_ST) & 1) && clock64() - t0 < 20000000LL) {}
+          while (!mbar_try_wait(&raw_full[i % RAW_ST], (i / RAW_ST) & 1) && clock64() - t0 < 20000000LL) {}
         }
         for (int i = max(0, issued - p.x_stages); i < issued; ++i) {
           const long long t0 = clock64();
@@ -189,8 +192,8 @@ w4_umma_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__
       const uint32_t idesc = make_idesc_f16(p.fmt, /*a M-major*/ 1, /*b K-major*/ 0, U_COLS, p.NT);
       bool ok = true;
       for (int i = 0; i < nst && ok; ++i) {
-        const int as = i % U_A_ST, xs = i % p.x_stages;
-        ok = mbar_wait(&a_full[as], (i / U_A_ST) & 1, abort_flag) &&
+        const int as = i % A_ST, xs = i % p.x_stages;
+        ok = mbar_wait(&a_full[as], (i / A_ST) & 1, abort_flag) &&
              mbar_wait(&x_full[xs], (i / p.x_stages) & 1, abort_flag);
         if (!ok) break;
         tc_fence_after();
@@ -211,33 +214,42 @@ w4_umma_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__
     }
   } else {
     // ===================== nibble expansion (warps 2..9) =====================
-    const int dt = threadIdx.x - 64;            // 0..255: one 16-byte load per stage
-    const int row = dt >> 3, cgp = dt & 7;      // byte row 0..31, 16-channel group 0..7
+    // Stage i belongs to expansion warp i % 8: the warp expands the whole 32 x 128-byte stage
+    // (8 x 16 bytes per lane), so the barrier round trips and the proxy fence are paid once per
+    // 4 KB and the eight warps sit at different points of their pipelines.
+    const int dw = warp - 2;
+    const int cgp = lane & 7, rsub = lane >> 3;   // 16-channel group 0..7, byte row within a group of 4
     const int ngroup = cgp >> 2, ch0 = (cgp & 3) * 2;
     bool ok = true;
-    for (int i = 0; i < nst; ++i) {
-      const int rs = i % U_RAW_ST, as = i % U_A_ST;
-      ok = __all_sync(0xffffffffu, mbar_wait(&raw_full[rs], (i / U_RAW_ST) & 1, abort_flag));
+    for (int i = dw; i < nst; i += U_DQ_WARPS) {
+      const int rs = i % RAW_ST, as = i % A_ST;
+      ok = __all_sync(0xffffffffu, mbar_wait(&raw_full[rs], (i / RAW_ST) & 1, abort_flag));
       if (!ok) break;
-      const uint4 v = *reinterpret_cast<const uint4*>(raw_ring + rs * U_RAW_BYTES + row * U_COLS + cgp * 16);
+      uint4 v[8];
+      const uint8_t* rawp = raw_ring + rs * U_RAW_BYTES + cgp * 16;
+#pragma unroll
+      for (int u = 0; u < 8; ++u) v[u] = *reinterpret_cast<const uint4*>(rawp + (4 * u + rsub) * U_COLS);
       __syncwarp();
       if (lane == 0) mbar_arrive(&raw_empty[rs]);
-      if (i >= U_A_ST) {
-        ok = __all_sync(0xffffffffu, mbar_wait(&a_empty[as], ((i / U_A_ST) & 1) ^ 1, abort_flag));
+      if (i >= A_ST) {
+        ok = __all_sync(0xffffffffu, mbar_wait(&a_empty[as], ((i / A_ST) & 1) ^ 1, abort_flag));
         if (!ok) break;
         tc_fence_after();
       }
-      uint32_t e[8], o[8];     // k even / k odd: 16 channels each, in expanded order
-      expand_word<FMT>(v.x, e[0], e[1], o[0], o[1]);
-      expand_word<FMT>(v.y, e[2], e[3], o[2], o[3]);
-      expand_word<FMT>(v.z, e[4], e[5], o[4], o[5]);
-      expand_word<FMT>(v.w, e[6], e[7], o[6], o[7]);
       uint8_t* grp = a_ring + as * U_A_BYTES + ngroup * 8192;
-      const int ke = 2 * row, ko = 2 * row + 1;
-      *reinterpret_cast<uint4*>(grp + ke * 128 + (((ch0 + 0) ^ (ke & 7)) << 4)) = make_uint4(e[0], e[1], e[2], e[3]);
-      *reinterpret_cast<uint4*>(grp + ke * 128 + (((ch0 + 1) ^ (ke & 7)) << 4)) = make_uint4(e[4], e[5], e[6], e[7]);
-      *reinterpret_cast<uint4*>(grp + ko * 128 + (((ch0 + 0) ^ (ko & 7)) << 4)) = make_uint4(o[0], o[1], o[2], o[3]);
-      *reinterpret_cast<uint4*>(grp + ko * 128 + (((ch0 + 1) ^ (ko & 7)) << 4)) = make_uint4(o[4], o[5], o[6], o[7]);
+#pragma unroll
+      for (int u = 0; u < 8; ++u) {
+        uint32_t e[8], o[8];     // k even / k odd: 16 channels each, in expanded order
+        expand_word<FMT>(v[u].x, e[0], e[1], o[0], o[1]);
+        expand_word<FMT>(v[u].y, e[2], e[3], o[2], o[3]);
+        expand_word<FMT>(v[u].z, e[4], e[5], o[4], o[5]);
+        expand_word<FMT>(v[u].w, e[6], e[7], o[6], o[7]);
+        const int ke = 2 * (4 * u + rsub), ko = ke + 1;
+        *reinterpret_cast<uint4*>(grp + ke * 128 + (((ch0 + 0) ^ (ke & 7)) << 4)) = make_uint4(e[0], e[1], e[2], e[3]);
+        *reinterpret_cast<uint4*>(grp + ke * 128 + (((ch0 + 1) ^ (ke & 7)) << 4)) = make_uint4(e[4], e[5], e[6], e[7]);
+        *reinterpret_cast<uint4*>(grp + ko * 128 + (((ch0 + 0) ^ (ko & 7)) << 4)) = make_uint4(o[0], o[1], o[2], o[3]);
+        *reinterpret_cast<uint4*>(grp + ko * 128 + (((ch0 + 1) ^ (ko & 7)) << 4)) = make_uint4(o[4], o[5], o[6], o[7]);
+      }
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
       __syncwarp();
       if (lane == 0) mbar_arrive(&a_full[as]);
@@ -315,7 +327,7 @@ w4_umma_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__
 
 // ------------------------------------------------------------------ host ----
 struct UmmaPlan {
-  int use; int NT; int planes; int x_stages; int mtiles; int ncg; int ksplit; int stages_per_split; int tmem_cols;
+  int use; int NT; int planes; int raw_stages; int a_stages; int x_stages; int mtiles; int ncg; int ksplit; int stages_per_split; int tmem_cols;
   size_t smem_bytes; size_t xsum_bytes; size_t plane_bytes; size_t part_bytes;
 };
 
@@ -332,10 +344,13 @@ UmmaPlan plan_w4_umma(int64_t M, int64_t N, int64_t K, int x_dtype) {
   pl.ncg = (int)cdiv(N, U_COLS);
   pl.tmem_cols = pl.NT <= 32 ? 32 : pl.NT <= 64 ? 64 : pl.NT <= 128 ? 128 : 256;
   const size_t x_stage = (size_t)pl.NT * 128 * pl.planes;
-  const size_t fixed = (size_t)U_RAW_ST * U_RAW_BYTES + (size_t)U_A_ST * U_A_BYTES;
-  int xs = (int)std::min<size_t>(4, (((size_t)220 << 10) - fixed) / x_stage);
-  pl.x_stages = std::max(2, xs);
-  pl.smem_bytes = fixed + pl.x_stages * x_stage + 1024 + 512;
+  // ring depths under ~208 KB: the expanded-A ring should hold one stage per expansion warp
+  if (x_stage <= (8u << 10))       { pl.raw_stages = 8; pl.a_stages = 8; pl.x_stages = 4; }
+  else if (x_stage <= (16u << 10)) { pl.raw_stages = 8; pl.a_stages = 8; pl.x_stages = 3; }
+  else if (x_stage <= (32u << 10)) { pl.raw_stages = 4; pl.a_stages = 6; pl.x_stages = 3; }
+  else                             { pl.raw_stages = 4; pl.a_stages = 4; pl.x_stages = 2; }
+  pl.smem_bytes = (size_t)pl.raw_stages * U_RAW_BYTES + (size_t)pl.a_stages * U_A_BYTES + pl.x_stages * x_stage +
+                  1024 + 512;
   const int64_t total_stages = cdiv(K, U_STAGE_K);
   const int64_t base = (int64_t)pl.ncg * pl.mtiles;
   const int sms = sm_count();
@@ -416,7 +431,7 @@ int launch_w4_umma(const UmmaPlan& pl, const void* x, int x_dtype, const uint8_t
   p.packed = packed; p.zero = zero; p.scale = scale; p.out = out; p.xsum = xsum;
   p.M = M; p.N = N; p.K = K; p.NT = pl.NT; p.planes = pl.planes;
   p.fmt = (x_dtype == JGQ_F16) ? 0 : 1;
-  p.x_stages = pl.x_stages; p.stages_per_split = pl.stages_per_split; p.ksplit = pl.ksplit;
+  p.raw_stages = pl.raw_stages; p.a_stages = pl.a_stages; p.x_stages = pl.x_stages; p.stages_per_split = pl.stages_per_split; p.ksplit = pl.ksplit;
   p.ncg = pl.ncg; p.mtiles = pl.mtiles; p.tmem_cols = pl.tmem_cols;
   const bool zf32 = zs_dtype == JGQ_F32;
   if (x_dtype == JGQ_F16)
