@@ -221,7 +221,10 @@ w4_umma_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__
     const int cgp = lane & 7, rsub = lane >> 3;   // 16-channel group 0..7, byte row within a group of 4
     const int ngroup = cgp >> 2, ch0 = (cgp & 3) * 2;
     bool ok = true;
-    for (int i = dw; i < nst; i += U_DQ_WARPS) {
+    // A warp always works on the same ring slot (slot = warp index), so it sees every phase of
+    // that slot's barriers in order; the ring depths equal the number of active expansion warps.
+    const int ndq = A_ST;
+    for (int i = dw; i < nst && dw < ndq; i += ndq) {
       const int rs = i % RAW_ST, as = i % A_ST;
       ok = __all_sync(0xffffffffu, mbar_wait(&raw_full[rs], (i / RAW_ST) & 1, abort_flag));
       if (!ok) break;
@@ -344,11 +347,11 @@ UmmaPlan plan_w4_umma(int64_t M, int64_t N, int64_t K, int x_dtype) {
   pl.ncg = (int)cdiv(N, U_COLS);
   pl.tmem_cols = pl.NT <= 32 ? 32 : pl.NT <= 64 ? 64 : pl.NT <= 128 ? 128 : 256;
   const size_t x_stage = (size_t)pl.NT * 128 * pl.planes;
-  // ring depths under ~208 KB: the expanded-A ring should hold one stage per expansion warp
-  if (x_stage <= (8u << 10))       { pl.raw_stages = 8; pl.a_stages = 8; pl.x_stages = 4; }
-  else if (x_stage <= (16u << 10)) { pl.raw_stages = 8; pl.a_stages = 8; pl.x_stages = 3; }
-  else if (x_stage <= (32u << 10)) { pl.raw_stages = 4; pl.a_stages = 6; pl.x_stages = 3; }
-  else                             { pl.raw_stages = 4; pl.a_stages = 4; pl.x_stages = 2; }
+  // ring depths (<= 224 KB in all): raw and expanded-A rings hold one stage per active expansion warp
+  // (8, or 4 when the activation tiles are large and the tensor pipe is the bound anyway)
+  if (x_stage <= (8u << 10))       { pl.raw_stages = 8; pl.a_stages = 8; pl.x_stages = 8; }
+  else if (x_stage <= (16u << 10)) { pl.raw_stages = 8; pl.a_stages = 8; pl.x_stages = 4; }
+  else                             { pl.raw_stages = 4; pl.a_stages = 4; pl.x_stages = 4; }
   pl.smem_bytes = (size_t)pl.raw_stages * U_RAW_BYTES + (size_t)pl.a_stages * U_A_BYTES + pl.x_stages * x_stage +
                   1024 + 512;
   const int64_t total_stages = cdiv(K, U_STAGE_K);
