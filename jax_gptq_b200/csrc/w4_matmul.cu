@@ -4,20 +4,22 @@
 //   transpose_b:  out[M, K] = x[M, N] @ ((code[K, N] - zero[N]) * scale[N])^T
 //
 // packed[K/2, N] holds code[2j, n] in the low and code[2j+1, n] in the high
-// nibble of byte (j, n).
-//
-// Forward kernel.  Scale and zero depend on the output channel only, so they
-// leave the contraction loop:
+// nibble of byte (j, n).  Scale and zero depend on the output channel only, so
+// they leave the contraction loop:
 //     out[m, n] = scale[n] * ( sum_k x[m,k] code[k,n]  -  zero[n] * sum_k x[m,k] ).
-// The loop therefore streams raw codes.  At decode-sized M the kernel is
-// HBM-bound (one pass over K*N/2 bytes); the multiply-adds are handed to the
-// tensor pipe (mma.sync m16n8k16, fp32 accumulate) so that the issue slots go
-// to the loads and the nibble expansion.  A byte already holds the two
-// consecutive-k codes an MMA B-fragment register wants, so a thread's 16-byte
-// load (16 channels of one byte row) feeds 16 MMAs without any shuffle:
-// lane (g, q) loads byte rows j0+q and j0+4+q of channels 16g..16g+15, and MMA
-// number b uses byte b of both, which makes n-slot g of MMA b channel 16g+b.
-// sum_k x[m,k] comes from one more MMA against a fragment of ones.
+//
+// This file holds the decode-sized forward kernel (M <= 16 per CTA pass; larger M
+// goes to the tcgen05 kernel in w4_umma.cu) and the transposed kernel.
+//
+// Decode kernel: HBM-bound, one pass over K*N/2 bytes.  Codes go from global
+// memory straight to registers (16-byte loads, a register ring keeps several
+// steps of loads in flight per lane) and the multiply-adds are handed to the
+// tensor pipe with the WEIGHTS as the 16-row MMA operand: a byte already holds
+// the two consecutive-k codes one A-fragment register wants.  Lane (g, q) loads
+// byte rows j0+q and j0+4+q of channels 16g..16g+15; MMA number b (0..7) takes
+// bytes b and b+8 of both loads, i.e. MMA row g is channel 16g+b and row g+8 is
+// channel 16g+8+b, the 8 MMA columns are tokens.  sum_k x[m,k] comes from one
+// more MMA whose A operand is all ones.
 //
 // A CTA is 4 warps on one 128-channel group; the warps interleave over the
 // CTA's slice of the contraction range and are reduced through shared memory.
@@ -25,7 +27,6 @@
 // are written to the workspace; the CTA that takes the last ticket of a
 // channel group adds the slices in slice order and writes the result.
 #include "w4_common.cuh"
-#include "umma.cuh"
 #include <algorithm>
 #include <cstdlib>
 #include <cstring>
@@ -33,78 +34,82 @@
 
 namespace jgq {
 
-// Activation fragments of one 16-step (rows m0.., contraction k0..k0+15) for lane (g, q).
-template <typename XT, int MT>
-__device__ __forceinline__ void load_afrags(const XT* __restrict__ x, int64_t m0, int64_t M, int64_t k0, int64_t K,
-                                            int g, int q, uint32_t (&a)[MT][4], uint32_t (&alo)[MT][4]) {
+constexpr int W4_RING = 4;      // steps of weight loads in flight per lane (2 x 16 B each)
+
+// Activation fragment (MMA B operand, 16 k x 8 tokens) of one 16-step for lane (g, q):
+// token m0 + 8*t + g, contraction k0 + 2q.. and k0 + 8 + 2q..
+template <typename XT, int NTOK>
+__device__ __forceinline__ void load_xfrags(const XT* __restrict__ x, int64_t m0, int64_t M, int64_t k0, int64_t K,
+                                            int g, int q, uint32_t (&b)[NTOK][2], uint32_t (&blo)[NTOK][2]) {
   constexpr bool kSplitX = std::is_same<XT, float>::value;
 #pragma unroll
-  for (int t = 0; t < MT; ++t) {
-    const int64_t ma = m0 + 16 * t + g, mb = ma + 8;
+  for (int t = 0; t < NTOK; ++t) {
+    const int64_t m = m0 + 8 * t + g;
     if (kSplitX) {
-      load_x2_split((const float*)x, ma, M, k0 + 2 * q, K, a[t][0], alo[t][0]);
-      load_x2_split((const float*)x, mb, M, k0 + 2 * q, K, a[t][1], alo[t][1]);
-      load_x2_split((const float*)x, ma, M, k0 + 8 + 2 * q, K, a[t][2], alo[t][2]);
-      load_x2_split((const float*)x, mb, M, k0 + 8 + 2 * q, K, a[t][3], alo[t][3]);
+      load_x2_split((const float*)x, m, M, k0 + 2 * q, K, b[t][0], blo[t][0]);
+      load_x2_split((const float*)x, m, M, k0 + 8 + 2 * q, K, b[t][1], blo[t][1]);
     } else {
-      a[t][0] = load_x2<XT>(x, ma, M, k0 + 2 * q, K);
-      a[t][1] = load_x2<XT>(x, mb, M, k0 + 2 * q, K);
-      a[t][2] = load_x2<XT>(x, ma, M, k0 + 8 + 2 * q, K);
-      a[t][3] = load_x2<XT>(x, mb, M, k0 + 8 + 2 * q, K);
-      alo[t][0] = alo[t][1] = alo[t][2] = alo[t][3] = 0u;
+      b[t][0] = load_x2<XT>(x, m, M, k0 + 2 * q, K);
+      b[t][1] = load_x2<XT>(x, m, M, k0 + 8 + 2 * q, K);
+      blo[t][0] = blo[t][1] = 0u;
     }
   }
 }
 
-// One 16-step: 16 MMAs per row tile over the 2 x 16 bytes this lane holds, plus the MMA against ones.
-template <typename CT, int MT, bool kSplitX>
-__device__ __forceinline__ void w4_step(float (&acc)[MT][16][4], float (&accx)[MT][4], const uint4& r0, const uint4& r1,
-                                        const uint32_t (&a)[MT][4], const uint32_t (&alo)[MT][4]) {
+// mma with the fragment roles of this kernel: D[16 ch x 8 tok] += A[16 ch x 16 k] * B[16 k x 8 tok]
+template <typename CT>
+__device__ __forceinline__ void mma_wx(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                       const uint32_t (&b)[2]) {
+  const uint32_t a[4] = {a0, a1, a2, a3};
+  MmaType<CT>::mma(d, a, b[0], b[1]);
+}
+
+// One 16-step: 8 MMAs per token octet over the 2 x 16 bytes this lane holds, plus the MMA with ones.
+template <typename CT, int NTOK, bool kSplitX>
+__device__ __forceinline__ void w4_step(float (&acc)[NTOK][8][4], float (&accx)[NTOK][4], const uint4& r0, const uint4& r1,
+                                        const uint32_t (&xb)[NTOK][2], const uint32_t (&xlo)[NTOK][2]) {
   const uint32_t w0[4] = {r0.x, r0.y, r0.z, r0.w};
   const uint32_t w1[4] = {r1.x, r1.y, r1.z, r1.w};
 #pragma unroll
-  for (int wi = 0; wi < 4; ++wi) {
-    const uint32_t u0 = w0[wi], u0s = u0 >> 4, u1 = w1[wi], u1s = u1 >> 4;
+  for (int wi = 0; wi < 2; ++wi) {
+    // words wi (channels 4wi..4wi+3) and wi + 2 (channels 8 + 4wi ..) of both byte rows
+    const uint32_t u0 = w0[wi], u0s = u0 >> 4, v0 = w0[wi + 2], v0s = v0 >> 4;
+    const uint32_t u1 = w1[wi], u1s = u1 >> 4, v1 = w1[wi + 2], v1s = v1 >> 4;
 #pragma unroll
     for (int bi = 0; bi < 4; ++bi) {
       const uint32_t sel = (uint32_t)bi | ((uint32_t)bi << 4) | ((uint32_t)(4 + bi) << 8) | ((uint32_t)(4 + bi) << 12);
-      const uint32_t b0 = MmaType<CT>::expand(__byte_perm(u0, u0s, sel));
-      const uint32_t b1 = MmaType<CT>::expand(__byte_perm(u1, u1s, sel));
+      const uint32_t a0 = MmaType<CT>::expand(__byte_perm(u0, u0s, sel));   // channel 4wi+bi,     k 2q..
+      const uint32_t a1 = MmaType<CT>::expand(__byte_perm(v0, v0s, sel));   // channel 8+4wi+bi,   k 2q..
+      const uint32_t a2 = MmaType<CT>::expand(__byte_perm(u1, u1s, sel));   // channel 4wi+bi,     k 8+2q..
+      const uint32_t a3 = MmaType<CT>::expand(__byte_perm(v1, v1s, sel));   // channel 8+4wi+bi,   k 8+2q..
 #pragma unroll
-      for (int t = 0; t < MT; ++t) {
-        MmaType<CT>::mma(acc[t][wi * 4 + bi], a[t], b0, b1);
-        if (kSplitX) MmaType<CT>::mma(acc[t][wi * 4 + bi], alo[t], b0, b1);
+      for (int t = 0; t < NTOK; ++t) {
+        mma_wx<CT>(acc[t][wi * 4 + bi], a0, a1, a2, a3, xb[t]);
+        if (kSplitX) mma_wx<CT>(acc[t][wi * 4 + bi], a0, a1, a2, a3, xlo[t]);
       }
     }
   }
+  const uint32_t one = MmaType<CT>::ones();
 #pragma unroll
-  for (int t = 0; t < MT; ++t) {
-    MmaType<CT>::mma(accx[t], a[t], MmaType<CT>::ones(), MmaType<CT>::ones());
-    if (kSplitX) MmaType<CT>::mma(accx[t], alo[t], MmaType<CT>::ones(), MmaType<CT>::ones());
+  for (int t = 0; t < NTOK; ++t) {
+    mma_wx<CT>(accx[t], one, one, one, one, xb[t]);
+    if (kSplitX) mma_wx<CT>(accx[t], one, one, one, one, xlo[t]);
   }
 }
 
-constexpr int W4_NST = 16;                  // ring depth of the TMA-staged variant
-constexpr int W4_STAGE_ROWS = 32;           // byte rows per stage = 4 steps, one per consumer warp
-constexpr int W4_STAGE_BYTES = W4_STAGE_ROWS * WCOLS;
-constexpr int W4_RING_BYTES = W4_NST * W4_STAGE_BYTES + 1024;
-
-// XT: activation/output element type.  MT: 16-row tiles per CTA.
+// XT: activation/output element type.  NTOK: token octets per CTA pass (1: M <= 8, 2: M <= 16).
 // CT: MMA operand type (XT itself for f16/bf16, bf16 for fp32 activations).
-// TMA: weights arrive through a 16-deep shared-memory ring filled by a producer warp with
-//      cp.async.bulk.tensor (needs N % 16 == 0); otherwise each lane loads its bytes directly.
-template <typename XT, typename CT, int MT, typename ZST, bool TMA>
-__global__ void __launch_bounds__(TMA ? (WWARPS + 1) * 32 : WWARPS * 32, (TMA && MT == 1) ? 3 : 1)
-w4_fwd_kernel(const XT* __restrict__ x, const uint8_t* __restrict__ packed,
-              const void* __restrict__ zero, const void* __restrict__ scale,
-              XT* __restrict__ out, int64_t M, int64_t N, int64_t K,
-              int steps_per_split, int ksplit, float* __restrict__ partials, int* __restrict__ tickets,
-              int vec, const __grid_constant__ CUtensorMap wmap) {
+template <typename XT, typename CT, int NTOK, typename ZST>
+__global__ void __launch_bounds__(WWARPS * 32, NTOK == 1 ? 4 : 2)
+w4_decode_kernel(const XT* __restrict__ x, const uint8_t* __restrict__ packed,
+                 const void* __restrict__ zero, const void* __restrict__ scale,
+                 XT* __restrict__ out, int64_t M, int64_t N, int64_t K,
+                 int steps_per_split, int ksplit, float* __restrict__ partials, int* __restrict__ tickets,
+                 int vec) {
   constexpr bool kSplitX = std::is_same<XT, float>::value;
-  constexpr int ROWS = 16 * MT;
+  constexpr int ROWS = 8 * NTOK;            // tokens per CTA pass
   __shared__ __align__(16) float red[ROWS][PSTRIDE];
   __shared__ int s_last;
-  __shared__ int s_abort;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, q = lane & 3;
@@ -117,139 +122,103 @@ w4_fwd_kernel(const XT* __restrict__ x, const uint8_t* __restrict__ packed,
   const int64_t step_begin = (int64_t)split * steps_per_split;
   const int64_t step_end = min(total_steps, step_begin + steps_per_split);
 
-  float acc[MT][16][4];
-  float accx[MT][4];
+  float acc[NTOK][8][4];
+  float accx[NTOK][4];
 #pragma unroll
-  for (int t = 0; t < MT; ++t) {
+  for (int t = 0; t < NTOK; ++t) {
 #pragma unroll
-    for (int b = 0; b < 16; ++b)
+    for (int b = 0; b < 8; ++b)
 #pragma unroll
       for (int i = 0; i < 4; ++i) acc[t][b][i] = 0.f;
 #pragma unroll
     for (int i = 0; i < 4; ++i) accx[t][i] = 0.f;
   }
-  if (threadIdx.x == 0) s_abort = 0;
 
-  if constexpr (!TMA) {
+  // ---- main loop: warp w takes steps step_begin + w, + 4, ...; W4_RING of them in flight ----
+  {
     const int64_t c0 = cbase + 16 * g;
-    for (int64_t step = step_begin + warp; step < step_end; step += WWARPS) {
-      const int64_t j0 = step * 8;
-      const uint4 r0 = load_codes16(packed, j0 + q, KB, c0, N, vec);
-      const uint4 r1 = load_codes16(packed, j0 + 4 + q, KB, c0, N, vec);
-      uint32_t a[MT][4], alo[MT][4];
-      load_afrags<XT, MT>(x, m0, M, 2 * j0, K, g, q, a, alo);
-      w4_step<CT, MT, kSplitX>(acc, accx, r0, r1, a, alo);
+    const int64_t first = step_begin + warp;
+    const int nmine = first < step_end ? (int)((step_end - first + WWARPS - 1) / WWARPS) : 0;
+    uint4 ring0[W4_RING], ring1[W4_RING];
+#pragma unroll
+    for (int d = 0; d < W4_RING; ++d) {
+      const int64_t j0 = (first + (int64_t)d * WWARPS) * 8;
+      ring0[d] = (d < nmine) ? load_codes16(packed, j0 + q, KB, c0, N, vec) : make_uint4(0, 0, 0, 0);
+      ring1[d] = (d < nmine) ? load_codes16(packed, j0 + 4 + q, KB, c0, N, vec) : make_uint4(0, 0, 0, 0);
     }
-  } else {
-    using namespace umma;
-    extern __shared__ uint8_t ring_raw[];
-    uint8_t* ring = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(ring_raw) + 1023) & ~uintptr_t(1023));
-    __shared__ __align__(8) uint64_t full_bar[W4_NST];
-    __shared__ __align__(8) uint64_t empty_bar[W4_NST];
-    volatile int* abort_flag = &s_abort;
-    if (threadIdx.x == 0) {
-      for (int i = 0; i < W4_NST; ++i) { mbar_init(&full_bar[i], 1); mbar_init(&empty_bar[i], WWARPS); }
-      fence_barrier_init();
-      prefetch_tensormap(&wmap);
-    }
-    __syncthreads();
-    const int nstage = (int)((step_end - step_begin + 3) / 4);
-    if (warp == WWARPS) {
-      // ---- producer: one 32-row x 128-channel box per stage ----
-      if (lane == 0) {
-        int issued = 0;
-        for (int s = 0; s < nstage; ++s) {
-          const int slot = s % W4_NST;
-          if (s >= W4_NST && !mbar_wait(&empty_bar[slot], ((s / W4_NST) & 1) ^ 1, abort_flag)) break;
-          mbar_expect_tx(&full_bar[slot], W4_STAGE_BYTES);
-          tma_load_2d(ring + slot * W4_STAGE_BYTES, &wmap, (int)cbase, (int)((step_begin + 4 * s) * 8), &full_bar[slot]);
-          issued = s + 1;
-        }
-        if (*abort_flag) {
-          for (int s = max(0, issued - W4_NST); s < issued; ++s) {
-            const long long t0 = clock64();
-            while (!mbar_try_wait(&full_bar[s % W4_NST], (s / W4_NST) & 1) && clock64() - t0 < 20000000LL) {}
+    uint32_t xb[NTOK][2], xlo[NTOK][2];
+    if (nmine > 0) load_xfrags<XT, NTOK>(x, m0, M, 16 * first, K, g, q, xb, xlo);
+    for (int base = 0; base < nmine; base += W4_RING) {
+#pragma unroll
+      for (int d = 0; d < W4_RING; ++d) {
+        const int idx = base + d;
+        if (idx < nmine) {
+          const uint4 r0 = ring0[d], r1 = ring1[d];
+          const int nxt = idx + W4_RING;
+          if (nxt < nmine) {
+            const int64_t j0 = (first + (int64_t)nxt * WWARPS) * 8;
+            ring0[d] = load_codes16(packed, j0 + q, KB, c0, N, vec);
+            ring1[d] = load_codes16(packed, j0 + 4 + q, KB, c0, N, vec);
           }
-        }
-      }
-    } else {
-      // ---- consumers: warp w takes step w of every stage ----
-      uint32_t a_n[MT][4], alo_n[MT][4];
-      load_afrags<XT, MT>(x, m0, M, 2 * 8 * (step_begin + warp), K, g, q, a_n, alo_n);
-      for (int s = 0; s < nstage; ++s) {
-        const int slot = s % W4_NST;
-        const int64_t step = step_begin + 4 * s + warp;
-        uint32_t a[MT][4], alo[MT][4];
+          uint32_t cb[NTOK][2], clo[NTOK][2];
 #pragma unroll
-        for (int t = 0; t < MT; ++t)
-#pragma unroll
-          for (int i = 0; i < 4; ++i) { a[t][i] = a_n[t][i]; alo[t][i] = alo_n[t][i]; }
-        if (s + 1 < nstage) load_afrags<XT, MT>(x, m0, M, 2 * 8 * (step + 4), K, g, q, a_n, alo_n);
-        const bool ok = __all_sync(0xffffffffu, mbar_wait(&full_bar[slot], (s / W4_NST) & 1, abort_flag));
-        if (!ok) break;
-        if (step < step_end) {
-          const uint8_t* tile = ring + slot * W4_STAGE_BYTES;
-          const uint4 r0 = *reinterpret_cast<const uint4*>(tile + (8 * warp + q) * WCOLS + 16 * g);
-          const uint4 r1 = *reinterpret_cast<const uint4*>(tile + (8 * warp + 4 + q) * WCOLS + 16 * g);
-          w4_step<CT, MT, kSplitX>(acc, accx, r0, r1, a, alo);
+          for (int t = 0; t < NTOK; ++t) { cb[t][0] = xb[t][0]; cb[t][1] = xb[t][1]; clo[t][0] = xlo[t][0]; clo[t][1] = xlo[t][1]; }
+          if (idx + 1 < nmine) load_xfrags<XT, NTOK>(x, m0, M, 16 * (first + (int64_t)(idx + 1) * WWARPS), K, g, q, xb, xlo);
+          w4_step<CT, NTOK, kSplitX>(acc, accx, r0, r1, cb, clo);
         }
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&empty_bar[slot]);
       }
     }
-    __syncthreads();
   }
-  const bool aborted = (*(volatile int*)&s_abort) != 0;
-  const float poison = aborted ? __int_as_float(0x7fc00000) : 0.f;   // a timed-out wait must not pass silently
 
   // ---- reduce the 4 warps into warp 0 through shared memory --------------------
-  // fragment element (t, b, i): row 16t + g + 8*(i>>1), channel 32q + 16*(i&1) + b
+  // fragment element (t, b, i): token 8t + 2q + (i & 1), channel 16g + b + 8 * (i >> 1)
   for (int w = 1; w < WWARPS; ++w) {
     if (warp == w) {
 #pragma unroll
-      for (int t = 0; t < MT; ++t) {
+      for (int t = 0; t < NTOK; ++t) {
 #pragma unroll
-        for (int b = 0; b < 16; ++b)
+        for (int b = 0; b < 8; ++b)
 #pragma unroll
           for (int i = 0; i < 4; ++i)
-            red[16 * t + g + 8 * (i >> 1)][32 * q + 16 * (i & 1) + b] = acc[t][b][i];
-        if (q == 0) { red[16 * t + g][WCOLS] = accx[t][0]; red[16 * t + g + 8][WCOLS] = accx[t][2]; }
+            red[8 * t + 2 * q + (i & 1)][16 * g + b + 8 * (i >> 1)] = acc[t][b][i];
+        if (g == 0) { red[8 * t + 2 * q][WCOLS] = accx[t][0]; red[8 * t + 2 * q + 1][WCOLS] = accx[t][1]; }
       }
     }
     __syncthreads();
     if (warp == 0) {
 #pragma unroll
-      for (int t = 0; t < MT; ++t) {
+      for (int t = 0; t < NTOK; ++t) {
 #pragma unroll
-        for (int b = 0; b < 16; ++b)
+        for (int b = 0; b < 8; ++b)
 #pragma unroll
           for (int i = 0; i < 4; ++i)
-            acc[t][b][i] += red[16 * t + g + 8 * (i >> 1)][32 * q + 16 * (i & 1) + b];
-        accx[t][0] += red[16 * t + g][WCOLS];
-        accx[t][2] += red[16 * t + g + 8][WCOLS];
+            acc[t][b][i] += red[8 * t + 2 * q + (i & 1)][16 * g + b + 8 * (i >> 1)];
+        accx[t][0] += red[8 * t + 2 * q][WCOLS];
+        accx[t][1] += red[8 * t + 2 * q + 1][WCOLS];
       }
     }
     __syncthreads();
   }
 
   // ---- split-K: publish this CTA's slice, last ticket holder sums all slices ----
+  // slice layout: [split][token][channel group][132]: 128 channel sums, then sum_k x
   if (ksplit > 1) {
     if (warp == 0) {
 #pragma unroll
-      for (int t = 0; t < MT; ++t)
+      for (int t = 0; t < NTOK; ++t)
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
-          const int64_t m = m0 + 16 * t + g + 8 * h;
+          const int64_t m = m0 + 8 * t + 2 * q + h;
           if (m < M) {
-            float* dst = partials + (((int64_t)split * M + m) * ncg + cg) * PSTRIDE;
+            float* dst = partials + (((int64_t)split * M + m) * ncg + cg) * PSTRIDE + 16 * g;
 #pragma unroll
             for (int i = 0; i < 2; ++i)
 #pragma unroll
-              for (int b4 = 0; b4 < 4; ++b4)
-                *reinterpret_cast<float4*>(dst + 32 * q + 16 * i + 4 * b4) =
-                    make_float4(acc[t][4 * b4 + 0][2 * h + i], acc[t][4 * b4 + 1][2 * h + i],
-                                acc[t][4 * b4 + 2][2 * h + i], acc[t][4 * b4 + 3][2 * h + i]);
-            if (q == 0) dst[WCOLS] = accx[t][2 * h];
+              for (int b4 = 0; b4 < 2; ++b4)
+                *reinterpret_cast<float4*>(dst + 8 * i + 4 * b4) =
+                    make_float4(acc[t][4 * b4 + 0][2 * i + h], acc[t][4 * b4 + 1][2 * i + h],
+                                acc[t][4 * b4 + 2][2 * i + h], acc[t][4 * b4 + 3][2 * i + h]);
+            if (g == 0) dst[WCOLS] = accx[t][h];
           }
         }
       __threadfence();
@@ -264,12 +233,12 @@ w4_fwd_kernel(const XT* __restrict__ x, const uint8_t* __restrict__ packed,
     if (warp != 0) return;
     __threadfence();
 #pragma unroll
-    for (int t = 0; t < MT; ++t)
+    for (int t = 0; t < NTOK; ++t)
 #pragma unroll
       for (int h = 0; h < 2; ++h) {
-        const int64_t m = m0 + 16 * t + g + 8 * h;
+        const int64_t m = m0 + 8 * t + 2 * q + h;
 #pragma unroll
-        for (int b = 0; b < 16; ++b) { acc[t][b][2 * h] = 0.f; acc[t][b][2 * h + 1] = 0.f; }
+        for (int b = 0; b < 8; ++b) { acc[t][b][h] = 0.f; acc[t][b][2 + h] = 0.f; }
         float xs = 0.f;
         if (m < M) {
           for (int z = 0; z < ksplit; ++z) {
@@ -277,41 +246,38 @@ w4_fwd_kernel(const XT* __restrict__ x, const uint8_t* __restrict__ packed,
 #pragma unroll
             for (int i = 0; i < 2; ++i)
 #pragma unroll
-              for (int b4 = 0; b4 < 4; ++b4) {
-                const float4 v = __ldcg(reinterpret_cast<const float4*>(src + 32 * q + 16 * i + 4 * b4));
-                acc[t][4 * b4 + 0][2 * h + i] += v.x; acc[t][4 * b4 + 1][2 * h + i] += v.y;
-                acc[t][4 * b4 + 2][2 * h + i] += v.z; acc[t][4 * b4 + 3][2 * h + i] += v.w;
+              for (int b4 = 0; b4 < 2; ++b4) {
+                const float4 v = __ldcg(reinterpret_cast<const float4*>(src + 16 * g + 8 * i + 4 * b4));
+                acc[t][4 * b4 + 0][2 * i + h] += v.x; acc[t][4 * b4 + 1][2 * i + h] += v.y;
+                acc[t][4 * b4 + 2][2 * i + h] += v.z; acc[t][4 * b4 + 3][2 * i + h] += v.w;
               }
             xs += __ldcg(src + WCOLS);
           }
         }
-        accx[t][2 * h] = xs;
+        accx[t][h] = xs;
       }
     if (lane == 0) tickets[mtile * ncg + cg] = 0;   // ready for the next launch
   } else {
     if (warp != 0) return;
-    // sum_k x is identical in every n-slot; take it from this lane's own fragment
   }
 
   // ---- epilogue (warp 0): out = scale * (acc - zero * sum_k x) -------------------
-  // all lanes of a quad hold the same rows; accx[t][0] / [2] are rows g / g+8 (valid in every lane)
+  // lane (g, q): channels cbase + 16g .. +15, tokens 8t + 2q and 8t + 2q + 1
 #pragma unroll
-  for (int i = 0; i < 2; ++i) {
-    const int64_t ccol = cbase + 32 * q + 16 * i;
+  for (int i = 0; i < 2; ++i)
 #pragma unroll
-    for (int b = 0; b < 16; ++b) {
-      const int64_t n = ccol + b;
+    for (int b = 0; b < 8; ++b) {
+      const int64_t n = cbase + 16 * g + 8 * i + b;
       if (n >= N) continue;
       const float s = zs_to_f32<ZST>(scale, n), z = zs_to_f32<ZST>(zero, n);
 #pragma unroll
-      for (int t = 0; t < MT; ++t)
+      for (int t = 0; t < NTOK; ++t)
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
-          const int64_t m = m0 + 16 * t + g + 8 * h;
-          if (m < M) out[m * N + n] = from_f32<XT>(s * (acc[t][b][2 * h + i] - z * accx[t][2 * h]) + poison);
+          const int64_t m = m0 + 8 * t + 2 * q + h;
+          if (m < M) out[m * N + n] = from_f32<XT>(s * (acc[t][b][2 * i + h] - z * accx[t][h]));
         }
     }
-  }
 }
 
 // ---- transpose_b: out[m, kk] = sum_n x[m, n] * (code[kk, n] - zero[n]) * scale[n] ------
@@ -372,69 +338,41 @@ w4_tb_kernel(const XT* __restrict__ x, const uint8_t* __restrict__ packed,
 
 constexpr size_t kTicketBytes = 4096;   // 1024 tickets; split-K is only planned below 4 * #SM CTAs
 
-struct FwdPlan { int mt; int mtiles; int ncg; int ksplit; int steps_per_split; };
+struct FwdPlan { int ntok; int mtiles; int ncg; int ksplit; int steps_per_split; };
 
 static FwdPlan plan_fwd(int64_t M, int64_t N, int64_t K) {
   FwdPlan p;
-  p.mt = (M <= 16) ? 1 : 2;
-  p.mtiles = (int)cdiv(M, 16 * p.mt);
+  p.ntok = (M <= 8) ? 1 : 2;
+  p.mtiles = (int)cdiv(M, 8 * p.ntok);
   p.ncg = (int)cdiv(N, WCOLS);
   const int64_t total_steps = cdiv(K / 2, 8);
   const int64_t base = (int64_t)p.ncg * p.mtiles;
-  const bool tma_shape = (N % 16 == 0);
-  // about 3 (ring variant, 64 KB of shared memory each) or 4 CTAs per SM
-  int64_t want = cdiv((tma_shape ? 3 : 4) * (int64_t)sm_count(), base);
+  // one resident wave: 4 CTAs of 4 warps per SM
+  const int64_t slots = 4 * (int64_t)sm_count();
+  int64_t want = std::max<int64_t>(1, slots / base);
   const int64_t max_split = std::max<int64_t>(1, total_steps / (2 * WWARPS));
   if (want > max_split) want = max_split;
-  if (want < 1) want = 1;
   if (base > (int64_t)(kTicketBytes / sizeof(int))) want = 1;
-  int64_t sps = cdiv(total_steps, want);
-  if (tma_shape) sps = cdiv(sps, 4) * 4;             // whole ring stages per split
-  p.steps_per_split = (int)sps;
-  p.ksplit = (int)cdiv(total_steps, sps);
+  p.steps_per_split = (int)cdiv(total_steps, want);
+  p.ksplit = (int)cdiv(total_steps, p.steps_per_split);
   return p;
-}
-
-template <typename XT, typename CT, int MT, typename ZST, bool TMA>
-static int launch_fwd_inst(const FwdPlan& p, const void* x, const uint8_t* packed, const void* zero, const void* scale,
-                           void* out, int64_t M, int64_t N, int64_t K, void* ws, int vec, const CUtensorMap& wmap,
-                           cudaStream_t s) {
-  int* tickets = (int*)ws;                                   // kTicketBytes, zero between launches
-  float* partials = (float*)((char*)ws + kTicketBytes);
-  dim3 grid((unsigned)p.ncg, (unsigned)p.ksplit, (unsigned)p.mtiles);
-  auto kern = w4_fwd_kernel<XT, CT, MT, ZST, TMA>;
-  if (TMA) {
-    static bool attr_set[64] = {false};
-    int dev = 0;
-    cudaGetDevice(&dev);
-    if (dev >= 0 && dev < 64 && !attr_set[dev]) {
-      cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, W4_RING_BYTES);
-      attr_set[dev] = true;
-    }
-  }
-  kern<<<grid, TMA ? (WWARPS + 1) * 32 : WWARPS * 32, TMA ? W4_RING_BYTES : 0, s>>>(
-      (const XT*)x, packed, zero, scale, (XT*)out, M, N, K, p.steps_per_split, p.ksplit, partials, tickets, vec, wmap);
-  return check_launch("w4_matmul");
 }
 
 template <typename XT, typename CT, typename ZST>
 static int launch_fwd(const void* x, const uint8_t* packed, const void* zero, const void* scale, void* out,
                       int64_t M, int64_t N, int64_t K, void* ws, cudaStream_t s) {
   const FwdPlan p = plan_fwd(M, N, K);
+  int* tickets = (int*)ws;                                   // kTicketBytes, zero between launches
+  float* partials = (float*)((char*)ws + kTicketBytes);
   const int vec = (N % 16 == 0) && aligned(packed, 16);
-  CUtensorMap wmap;
-  memset(&wmap, 0, sizeof(wmap));
-  bool tma = vec != 0;
-  if (tma) {
-    const int rc = encode_tmap_2d_u8(&wmap, packed, (uint64_t)N, (uint64_t)(K / 2), (uint64_t)N, WCOLS, W4_STAGE_ROWS, 0);
-    if (rc) return rc;
-  }
-  if (p.mt == 1) {
-    return tma ? launch_fwd_inst<XT, CT, 1, ZST, true>(p, x, packed, zero, scale, out, M, N, K, ws, vec, wmap, s)
-               : launch_fwd_inst<XT, CT, 1, ZST, false>(p, x, packed, zero, scale, out, M, N, K, ws, vec, wmap, s);
-  }
-  return tma ? launch_fwd_inst<XT, CT, 2, ZST, true>(p, x, packed, zero, scale, out, M, N, K, ws, vec, wmap, s)
-             : launch_fwd_inst<XT, CT, 2, ZST, false>(p, x, packed, zero, scale, out, M, N, K, ws, vec, wmap, s);
+  dim3 grid((unsigned)p.ncg, (unsigned)p.ksplit, (unsigned)p.mtiles);
+  if (p.ntok == 1)
+    w4_decode_kernel<XT, CT, 1, ZST><<<grid, WWARPS * 32, 0, s>>>((const XT*)x, packed, zero, scale, (XT*)out, M, N, K,
+                                                                  p.steps_per_split, p.ksplit, partials, tickets, vec);
+  else
+    w4_decode_kernel<XT, CT, 2, ZST><<<grid, WWARPS * 32, 0, s>>>((const XT*)x, packed, zero, scale, (XT*)out, M, N, K,
+                                                                  p.steps_per_split, p.ksplit, partials, tickets, vec);
+  return check_launch("w4_matmul");
 }
 
 template <typename XT, typename ZST>
@@ -456,7 +394,7 @@ int launch_w4_umma(const UmmaPlan& pl, const void* x, int x_dtype, const uint8_t
                    const void* scale, int zs_dtype, void* out, int64_t M, int64_t N, int64_t K, void* ws,
                    cudaStream_t s);
 
-static bool w4_force_mma_sync() {      // JGQ_W4_PATH=mma keeps the mma.sync kernels (for comparisons)
+static bool w4_force_mma_sync() {      // JGQ_W4_PATH=mma sends every M to the mma.sync kernel (for comparisons)
   static int v = -1;
   if (v < 0) { const char* e = getenv("JGQ_W4_PATH"); v = (e && !strcmp(e, "mma")) ? 1 : 0; }
   return v == 1;
@@ -513,7 +451,7 @@ extern "C" int jgq_w4_matmul(const void* x, int x_dtype, const uint8_t* packed,
   JGQ_REQUIRE(aligned(ws, 256), JGQ_ERR_ALIGN, "w4_matmul: workspace must be 256-byte aligned");
   if (!w4_force_mma_sync()) {
     const UmmaPlan up = plan_w4_umma(M, N, K, x_dtype);
-    if (up.use && aligned(x, 16) && aligned(packed, 16) && aligned(out, 4))
+    if (M > 16 && up.use && aligned(x, 16) && aligned(packed, 16) && aligned(out, 4))
       return launch_w4_umma(up, x, x_dtype, packed, zero, scale, zs_dtype, out, M, N, K, ws, s);
   }
 #define JGQ_FWD(XT, CT)                                                                                  \
