@@ -81,4 +81,65 @@ template <typename T> __device__ __forceinline__ float zs_to_f32(const void* p, 
 template <> __device__ __forceinline__ float zs_to_f32<float>(const void* p, int64_t i) { return ((const float*)p)[i]; }
 template <> __device__ __forceinline__ float zs_to_f32<__half>(const void* p, int64_t i) { return __half2float(((const __half*)p)[i]); }
 
+// Activation fragment (MMA B operand, 16 k x 8 tokens) of one 16-step for lane (g, q):
+// token m0 + 8*t + g, contraction k0 + 2q.. and k0 + 8 + 2q..
+template <typename XT, int NTOK>
+__device__ __forceinline__ void load_xfrags(const XT* __restrict__ x, int64_t m0, int64_t M, int64_t k0, int64_t K,
+                                            int g, int q, uint32_t (&b)[NTOK][2], uint32_t (&blo)[NTOK][2]) {
+  constexpr bool kSplitX = std::is_same<XT, float>::value;
+#pragma unroll
+  for (int t = 0; t < NTOK; ++t) {
+    const int64_t m = m0 + 8 * t + g;
+    if (kSplitX) {
+      load_x2_split((const float*)x, m, M, k0 + 2 * q, K, b[t][0], blo[t][0]);
+      load_x2_split((const float*)x, m, M, k0 + 8 + 2 * q, K, b[t][1], blo[t][1]);
+    } else {
+      b[t][0] = load_x2<XT>(x, m, M, k0 + 2 * q, K);
+      b[t][1] = load_x2<XT>(x, m, M, k0 + 8 + 2 * q, K);
+      blo[t][0] = blo[t][1] = 0u;
+    }
+  }
+}
+
+// mma with the fragment roles of this kernel: D[16 ch x 8 tok] += A[16 ch x 16 k] * B[16 k x 8 tok]
+template <typename CT>
+__device__ __forceinline__ void mma_wx(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                       const uint32_t (&b)[2]) {
+  const uint32_t a[4] = {a0, a1, a2, a3};
+  MmaType<CT>::mma(d, a, b[0], b[1]);
+}
+
+// One 16-step: 8 MMAs per token octet over the 2 x 16 bytes this lane holds, plus the MMA with ones.
+template <typename CT, int NTOK, bool kSplitX>
+__device__ __forceinline__ void w4_step(float (&acc)[NTOK][8][4], float (&accx)[NTOK][4], const uint4& r0, const uint4& r1,
+                                        const uint32_t (&xb)[NTOK][2], const uint32_t (&xlo)[NTOK][2]) {
+  const uint32_t w0[4] = {r0.x, r0.y, r0.z, r0.w};
+  const uint32_t w1[4] = {r1.x, r1.y, r1.z, r1.w};
+#pragma unroll
+  for (int wi = 0; wi < 2; ++wi) {
+    // words wi (channels 4wi..4wi+3) and wi + 2 (channels 8 + 4wi ..) of both byte rows
+    const uint32_t u0 = w0[wi], u0s = u0 >> 4, v0 = w0[wi + 2], v0s = v0 >> 4;
+    const uint32_t u1 = w1[wi], u1s = u1 >> 4, v1 = w1[wi + 2], v1s = v1 >> 4;
+#pragma unroll
+    for (int bi = 0; bi < 4; ++bi) {
+      const uint32_t sel = (uint32_t)bi | ((uint32_t)bi << 4) | ((uint32_t)(4 + bi) << 8) | ((uint32_t)(4 + bi) << 12);
+      const uint32_t a0 = MmaType<CT>::expand(__byte_perm(u0, u0s, sel));   // channel 4wi+bi,     k 2q..
+      const uint32_t a1 = MmaType<CT>::expand(__byte_perm(v0, v0s, sel));   // channel 8+4wi+bi,   k 2q..
+      const uint32_t a2 = MmaType<CT>::expand(__byte_perm(u1, u1s, sel));   // channel 4wi+bi,     k 8+2q..
+      const uint32_t a3 = MmaType<CT>::expand(__byte_perm(v1, v1s, sel));   // channel 8+4wi+bi,   k 8+2q..
+#pragma unroll
+      for (int t = 0; t < NTOK; ++t) {
+        mma_wx<CT>(acc[t][wi * 4 + bi], a0, a1, a2, a3, xb[t]);
+        if (kSplitX) mma_wx<CT>(acc[t][wi * 4 + bi], a0, a1, a2, a3, xlo[t]);
+      }
+    }
+  }
+  const uint32_t one = MmaType<CT>::ones();
+#pragma unroll
+  for (int t = 0; t < NTOK; ++t) {
+    mma_wx<CT>(accx[t], one, one, one, one, xb[t]);
+    if (kSplitX) mma_wx<CT>(accx[t], one, one, one, one, xlo[t]);
+  }
+}
+
 }  // namespace jgq

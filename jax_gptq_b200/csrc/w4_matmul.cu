@@ -36,67 +36,6 @@ namespace jgq {
 
 constexpr int W4_RING = 4;      // steps of weight loads in flight per lane (2 x 16 B each)
 
-// Activation fragment (MMA B operand, 16 k x 8 tokens) of one 16-step for lane (g, q):
-// token m0 + 8*t + g, contraction k0 + 2q.. and k0 + 8 + 2q..
-template <typename XT, int NTOK>
-__device__ __forceinline__ void load_xfrags(const XT* __restrict__ x, int64_t m0, int64_t M, int64_t k0, int64_t K,
-                                            int g, int q, uint32_t (&b)[NTOK][2], uint32_t (&blo)[NTOK][2]) {
-  constexpr bool kSplitX = std::is_same<XT, float>::value;
-#pragma unroll
-  for (int t = 0; t < NTOK; ++t) {
-    const int64_t m = m0 + 8 * t + g;
-    if (kSplitX) {
-      load_x2_split((const float*)x, m, M, k0 + 2 * q, K, b[t][0], blo[t][0]);
-      load_x2_split((const float*)x, m, M, k0 + 8 + 2 * q, K, b[t][1], blo[t][1]);
-    } else {
-      b[t][0] = load_x2<XT>(x, m, M, k0 + 2 * q, K);
-      b[t][1] = load_x2<XT>(x, m, M, k0 + 8 + 2 * q, K);
-      blo[t][0] = blo[t][1] = 0u;
-    }
-  }
-}
-
-// mma with the fragment roles of this kernel: D[16 ch x 8 tok] += A[16 ch x 16 k] * B[16 k x 8 tok]
-template <typename CT>
-__device__ __forceinline__ void mma_wx(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
-                                       const uint32_t (&b)[2]) {
-  const uint32_t a[4] = {a0, a1, a2, a3};
-  MmaType<CT>::mma(d, a, b[0], b[1]);
-}
-
-// One 16-step: 8 MMAs per token octet over the 2 x 16 bytes this lane holds, plus the MMA with ones.
-template <typename CT, int NTOK, bool kSplitX>
-__device__ __forceinline__ void w4_step(float (&acc)[NTOK][8][4], float (&accx)[NTOK][4], const uint4& r0, const uint4& r1,
-                                        const uint32_t (&xb)[NTOK][2], const uint32_t (&xlo)[NTOK][2]) {
-  const uint32_t w0[4] = {r0.x, r0.y, r0.z, r0.w};
-  const uint32_t w1[4] = {r1.x, r1.y, r1.z, r1.w};
-#pragma unroll
-  for (int wi = 0; wi < 2; ++wi) {
-    // words wi (channels 4wi..4wi+3) and wi + 2 (channels 8 + 4wi ..) of both byte rows
-    const uint32_t u0 = w0[wi], u0s = u0 >> 4, v0 = w0[wi + 2], v0s = v0 >> 4;
-    const uint32_t u1 = w1[wi], u1s = u1 >> 4, v1 = w1[wi + 2], v1s = v1 >> 4;
-#pragma unroll
-    for (int bi = 0; bi < 4; ++bi) {
-      const uint32_t sel = (uint32_t)bi | ((uint32_t)bi << 4) | ((uint32_t)(4 + bi) << 8) | ((uint32_t)(4 + bi) << 12);
-      const uint32_t a0 = MmaType<CT>::expand(__byte_perm(u0, u0s, sel));   // channel 4wi+bi,     k 2q..
-      const uint32_t a1 = MmaType<CT>::expand(__byte_perm(v0, v0s, sel));   // channel 8+4wi+bi,   k 2q..
-      const uint32_t a2 = MmaType<CT>::expand(__byte_perm(u1, u1s, sel));   // channel 4wi+bi,     k 8+2q..
-      const uint32_t a3 = MmaType<CT>::expand(__byte_perm(v1, v1s, sel));   // channel 8+4wi+bi,   k 8+2q..
-#pragma unroll
-      for (int t = 0; t < NTOK; ++t) {
-        mma_wx<CT>(acc[t][wi * 4 + bi], a0, a1, a2, a3, xb[t]);
-        if (kSplitX) mma_wx<CT>(acc[t][wi * 4 + bi], a0, a1, a2, a3, xlo[t]);
-      }
-    }
-  }
-  const uint32_t one = MmaType<CT>::ones();
-#pragma unroll
-  for (int t = 0; t < NTOK; ++t) {
-    mma_wx<CT>(accx[t], one, one, one, one, xb[t]);
-    if (kSplitX) mma_wx<CT>(accx[t], one, one, one, one, xlo[t]);
-  }
-}
-
 // XT: activation/output element type.  NTOK: token octets per CTA pass (1: M <= 8, 2: M <= 16).
 // CT: MMA operand type (XT itself for f16/bf16, bf16 for fp32 activations).
 template <typename XT, typename CT, int NTOK, typename ZST>
@@ -394,10 +333,22 @@ int launch_w4_umma(const UmmaPlan& pl, const void* x, int x_dtype, const uint8_t
                    const void* scale, int zs_dtype, void* out, int64_t M, int64_t N, int64_t K, void* ws,
                    cudaStream_t s);
 
+// persistent TMA-streamed decode kernel (w4_stream.cu)
+struct StreamPlan { int use; int ntok; int ncg; int spc; int64_t S; int G; int maxc; size_t part_bytes; };
+StreamPlan plan_w4_stream(int64_t M, int64_t N, int64_t K);
+int launch_w4_stream(const StreamPlan& pl, const void* x, int x_dtype, const uint8_t* packed, const void* zero,
+                     const void* scale, int zs_dtype, void* out, int64_t M, int64_t N, int64_t K, void* ws,
+                     cudaStream_t s);
+
+static int w4_path_override() {        // JGQ_W4_PATH=direct: direct-load decode kernel; =mma: no tcgen05 either
+  static int v = -1;
+  if (v < 0) { const char* e = getenv("JGQ_W4_PATH"); v = !e ? 0 : !strcmp(e, "direct") ? 1 : !strcmp(e, "mma") ? 2 : 0; }
+  return v;
+}
+
 static bool w4_force_mma_sync() {      // JGQ_W4_PATH=mma sends every M to the mma.sync kernel (for comparisons)
   static int v = -1;
-  if (v < 0) { const char* e = getenv("JGQ_W4_PATH"); v = (e && !strcmp(e, "mma")) ? 1 : 0; }
-  return v == 1;
+  return w4_path_override() == 2;
 }
 
 }  // namespace jgq
@@ -419,6 +370,8 @@ extern "C" size_t jgq_w4_matmul_workspace_bytes(int64_t M, int64_t N, int64_t K,
   if (up.use) bytes = std::max(bytes, w4_umma_workspace_bytes(up));
   const UmmaPlan up16 = plan_w4_umma(M, N, K, JGQ_F16);
   if (up16.use) bytes = std::max(bytes, w4_umma_workspace_bytes(up16));
+  const StreamPlan sp = plan_w4_stream(M, N, K);
+  if (sp.use) bytes = std::max(bytes, kTicketBytes + sp.part_bytes);
   return bytes;
 }
 
@@ -449,6 +402,10 @@ extern "C" int jgq_w4_matmul(const void* x, int x_dtype, const uint8_t* packed,
   const size_t need = jgq_w4_matmul_workspace_bytes(M, N, K, 0);
   JGQ_REQUIRE(ws && ws_bytes >= need, JGQ_ERR_WORKSPACE, "w4_matmul: workspace %zu < %zu bytes", ws_bytes, need);
   JGQ_REQUIRE(aligned(ws, 256), JGQ_ERR_ALIGN, "w4_matmul: workspace must be 256-byte aligned");
+  if (w4_path_override() == 0) {
+    const StreamPlan sp = plan_w4_stream(M, N, K);
+    if (sp.use && aligned(packed, 16)) return launch_w4_stream(sp, x, x_dtype, packed, zero, scale, zs_dtype, out, M, N, K, ws, s);
+  }
   if (!w4_force_mma_sync()) {
     const UmmaPlan up = plan_w4_umma(M, N, K, x_dtype);
     if (M > 16 && up.use && aligned(x, 16) && aligned(packed, 16) && aligned(out, 4))

@@ -1,0 +1,336 @@
+// Decode-sized packed-int4 forward matmul, TMA-streamed and persistent.
+//
+// HBM-bound: what matters is the number of bytes in flight per SM.  Measured on B200, a
+// producer lane streaming 4 KB TMA boxes reaches about 3 TB/s, 16 KB boxes about 5 TB/s, so
+// the weights move in 128-byte-row x 128-channel boxes (16 KB = 16 contraction steps),
+// four of them in flight per CTA, three CTAs per SM.
+//
+// The grid is one resident wave.  Work is the list of all stages, ordered by (token tile,
+// channel group, contraction position); CTA c owns the contiguous range
+// [c*S/G, (c+1)*S/G) of it, so every CTA streams the same number of bytes whatever N and K
+// are.  A CTA accumulates while it stays inside one channel group and flushes when the
+// group changes or its range ends: the four consumer warps are reduced through shared
+// memory, the slice goes to the workspace, and the CTA that draws the group's last ticket
+// adds the group's slices in CTA order and applies scale / zero.  No floating-point atomics.
+//
+// Consumers use the same fragment mapping as the direct-load kernel (w4_matmul.cu): weights
+// are the 16-row MMA operand, lane (g, q) owns channels 16g..16g+15 and byte rows q, q+4 of
+// a step.  The boxes are written with the 128-byte swizzle, so the four byte rows a quarter
+// warp reads land in different banks.
+#include "w4_common.cuh"
+#include "umma.cuh"
+#include <algorithm>
+#include <cstring>
+
+namespace jgq {
+
+constexpr int S_NST = 4;                      // stages in flight per CTA
+constexpr int S_STEPS = 16;                   // contraction steps (8 byte rows each) per stage
+constexpr int S_ROWS = 8 * S_STEPS;           // byte rows per stage
+constexpr int S_STAGE_BYTES = S_ROWS * WCOLS; // 16 KB
+constexpr int S_RING_BYTES = S_NST * S_STAGE_BYTES + 1024;
+constexpr int S_THREADS = (WWARPS + 1) * 32;
+
+struct StreamParams {
+  const void* x; const void* zero; const void* scale; void* out;
+  float* partials; int* tickets;
+  int64_t M, N, K;
+  int ncg, mtiles, spc;        // channel groups, token tiles, stages per (tile, group)
+  int64_t S;                   // total stages = mtiles * ncg * spc
+  int G;                       // CTAs (<= S)
+  int maxc;                    // slice slots per group
+};
+
+__device__ __forceinline__ int stream_cta_of(int64_t idx, int64_t S, int G) {
+  return (int)(((idx + 1) * G + S - 1) / S) - 1;     // the c with c*S/G <= idx < (c+1)*S/G
+}
+
+template <typename XT, typename CT, int NTOK, typename ZST>
+__global__ void __launch_bounds__(S_THREADS, NTOK == 1 ? 3 : 2)
+w4_stream_kernel(const __grid_constant__ CUtensorMap wmap, const StreamParams p) {
+  using namespace umma;
+  constexpr bool kSplitX = std::is_same<XT, float>::value;
+  constexpr int ROWS = 8 * NTOK;
+  extern __shared__ uint8_t ring_raw[];
+  uint8_t* ring = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(ring_raw) + 1023) & ~uintptr_t(1023));
+  __shared__ __align__(16) float red[ROWS][PSTRIDE];
+  __shared__ __align__(8) uint64_t full_bar[S_NST];
+  __shared__ __align__(8) uint64_t empty_bar[S_NST];
+  __shared__ int s_abort;
+  __shared__ int s_last;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int g = lane >> 2, q = lane & 3;
+  const XT* __restrict__ x = reinterpret_cast<const XT*>(p.x);
+  XT* __restrict__ out = reinterpret_cast<XT*>(p.out);
+  const int64_t KB = p.K / 2;
+  const int64_t total_steps = (KB + 7) / 8;
+  const int64_t idx_begin = ((int64_t)blockIdx.x * p.S) / p.G;
+  const int64_t idx_end = ((int64_t)(blockIdx.x + 1) * p.S) / p.G;
+  const int nstage = (int)(idx_end - idx_begin);
+  volatile int* abort_flag = &s_abort;
+
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < S_NST; ++i) { mbar_init(&full_bar[i], 1); mbar_init(&empty_bar[i], WWARPS); }
+    s_abort = 0;
+    s_last = 0;
+    fence_barrier_init();
+    prefetch_tensormap(&wmap);
+  }
+  __syncthreads();
+
+  if (warp == WWARPS) {
+    // ===================== producer: one 16 KB box per stage =====================
+    if (lane == 0) {
+      int issued = 0;
+      for (int s = 0; s < nstage; ++s) {
+        const int slot = s % S_NST;
+        if (s >= S_NST && !mbar_wait(&empty_bar[slot], ((s / S_NST) & 1) ^ 1, abort_flag)) break;
+        const int64_t idx = idx_begin + s;
+        const int64_t gid = idx / p.spc;
+        const int st = (int)(idx - gid * p.spc);
+        const int cg = (int)(gid % p.ncg);
+        mbar_expect_tx(&full_bar[slot], S_STAGE_BYTES);
+        tma_load_2d(ring + slot * S_STAGE_BYTES, &wmap, cg * WCOLS, st * S_ROWS, &full_bar[slot]);
+        issued = s + 1;
+      }
+      if (*abort_flag) {
+        for (int s = max(0, issued - S_NST); s < issued; ++s) {
+          const long long t0 = clock64();
+          while (!mbar_try_wait(&full_bar[s % S_NST], (s / S_NST) & 1) && clock64() - t0 < 20000000LL) {}
+        }
+      }
+    }
+  }
+
+  if (warp == WWARPS) return;      // consumers synchronise among themselves with a named barrier
+
+  float acc[NTOK][8][4];
+  float accx[NTOK][4];
+  auto clear_acc = [&]() {
+#pragma unroll
+    for (int t = 0; t < NTOK; ++t) {
+#pragma unroll
+      for (int b = 0; b < 8; ++b)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) acc[t][b][i] = 0.f;
+#pragma unroll
+      for (int i = 0; i < 4; ++i) accx[t][i] = 0.f;
+    }
+  };
+  clear_acc();
+
+  bool alive = true;      // false after a timed-out wait: keep walking the barriers, skip the work
+  for (int s = 0; s < nstage; ++s) {
+    const int64_t idx = idx_begin + s;
+    const int64_t gid = idx / p.spc;
+    const int st = (int)(idx - gid * p.spc);
+    const int cg = (int)(gid % p.ncg), mtile = (int)(gid / p.ncg);
+    const int64_t m0 = (int64_t)mtile * ROWS;
+
+    if (alive) {
+      const int slot = s % S_NST;
+      alive = __all_sync(0xffffffffu, mbar_wait(&full_bar[slot], (s / S_NST) & 1, abort_flag));
+      if (alive) {
+        const uint8_t* tile = ring + slot * S_STAGE_BYTES;
+        const int64_t step0 = (int64_t)st * S_STEPS;
+        uint32_t xb[NTOK][2], xlo[NTOK][2];
+        load_xfrags<XT, NTOK>(x, m0, p.M, 16 * (step0 + warp), p.K, g, q, xb, xlo);
+#pragma unroll
+        for (int u = 0; u < S_STEPS / WWARPS; ++u) {
+          const int sl = WWARPS * u + warp;                 // step inside the stage
+          uint32_t cb[NTOK][2], clo[NTOK][2];
+#pragma unroll
+          for (int t = 0; t < NTOK; ++t) { cb[t][0] = xb[t][0]; cb[t][1] = xb[t][1]; clo[t][0] = xlo[t][0]; clo[t][1] = xlo[t][1]; }
+          if (u + 1 < S_STEPS / WWARPS)
+            load_xfrags<XT, NTOK>(x, m0, p.M, 16 * (step0 + sl + WWARPS), p.K, g, q, xb, xlo);
+          if (step0 + sl < total_steps) {
+            const int ra = 8 * sl + q, rb = ra + 4;         // byte rows; 16-byte chunk g, swizzled by row & 7
+            const uint4 r0 = *reinterpret_cast<const uint4*>(tile + ra * WCOLS + ((g ^ (ra & 7)) << 4));
+            const uint4 r1 = *reinterpret_cast<const uint4*>(tile + rb * WCOLS + ((g ^ (rb & 7)) << 4));
+            w4_step<CT, NTOK, kSplitX>(acc, accx, r0, r1, cb, clo);
+          }
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&empty_bar[slot]);
+      }
+    }
+
+    // ---- flush when the (token tile, channel group) ends here ----
+    const bool last_of_group = (st == p.spc - 1) || (s == nstage - 1);
+    if (!last_of_group) continue;
+
+    // reduce the 4 consumer warps into warp 0
+    // fragment element (t, b, i): token 8t + 2q + (i & 1), channel 16g + b + 8 * (i >> 1)
+    for (int w = 1; w < WWARPS; ++w) {
+      if (warp == w) {
+#pragma unroll
+        for (int t = 0; t < NTOK; ++t) {
+#pragma unroll
+          for (int b = 0; b < 8; ++b)
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+              red[8 * t + 2 * q + (i & 1)][16 * g + b + 8 * (i >> 1)] = acc[t][b][i];
+          if (g == 0) { red[8 * t + 2 * q][WCOLS] = accx[t][0]; red[8 * t + 2 * q + 1][WCOLS] = accx[t][1]; }
+        }
+      }
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      if (warp == 0) {
+#pragma unroll
+        for (int t = 0; t < NTOK; ++t) {
+#pragma unroll
+          for (int b = 0; b < 8; ++b)
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+              acc[t][b][i] += red[8 * t + 2 * q + (i & 1)][16 * g + b + 8 * (i >> 1)];
+          accx[t][0] += red[8 * t + 2 * q][WCOLS];
+          accx[t][1] += red[8 * t + 2 * q + 1][WCOLS];
+        }
+      }
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+    }
+
+    if (warp == 0) {
+      const int first_c = stream_cta_of(gid * p.spc, p.S, p.G);
+      const int last_c = stream_cta_of((gid + 1) * p.spc - 1, p.S, p.G);
+      const int ncontrib = last_c - first_c + 1;
+      bool write_out = true;
+      if (ncontrib > 1) {
+        // publish this CTA's slice: [group][slot][token row][132]
+        float* slice = p.partials + (((int64_t)gid * p.maxc + (blockIdx.x - first_c)) * ROWS) * PSTRIDE;
+#pragma unroll
+        for (int t = 0; t < NTOK; ++t)
+#pragma unroll
+          for (int h = 0; h < 2; ++h) {
+            float* dst = slice + (8 * t + 2 * q + h) * PSTRIDE + 16 * g;
+#pragma unroll
+            for (int i = 0; i < 2; ++i)
+#pragma unroll
+              for (int b4 = 0; b4 < 2; ++b4)
+                *reinterpret_cast<float4*>(dst + 8 * i + 4 * b4) =
+                    make_float4(acc[t][4 * b4 + 0][2 * i + h], acc[t][4 * b4 + 1][2 * i + h],
+                                acc[t][4 * b4 + 2][2 * i + h], acc[t][4 * b4 + 3][2 * i + h]);
+            if (g == 0) dst[WCOLS - 16 * g] = accx[t][h];
+          }
+        __threadfence();
+        __syncwarp();
+        int last = 0;
+        if (lane == 0) {
+          const int old = atomicAdd(&p.tickets[gid], 1);
+          last = (old == ncontrib - 1);
+          if (last) p.tickets[gid] = 0;             // ready for the next launch
+        }
+        last = __shfl_sync(0xffffffffu, last, 0);
+        write_out = last != 0;
+        if (write_out) {
+          __threadfence();
+          const float* base = p.partials + ((int64_t)gid * p.maxc * ROWS) * PSTRIDE;
+#pragma unroll
+          for (int t = 0; t < NTOK; ++t)
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+#pragma unroll
+              for (int b = 0; b < 8; ++b) { acc[t][b][h] = 0.f; acc[t][b][2 + h] = 0.f; }
+              float xs = 0.f;
+              for (int z = 0; z < ncontrib; ++z) {
+                const float* src = base + ((int64_t)z * ROWS + 8 * t + 2 * q + h) * PSTRIDE;
+#pragma unroll
+                for (int i = 0; i < 2; ++i)
+#pragma unroll
+                  for (int b4 = 0; b4 < 2; ++b4) {
+                    const float4 v = __ldcg(reinterpret_cast<const float4*>(src + 16 * g + 8 * i + 4 * b4));
+                    acc[t][4 * b4 + 0][2 * i + h] += v.x; acc[t][4 * b4 + 1][2 * i + h] += v.y;
+                    acc[t][4 * b4 + 2][2 * i + h] += v.z; acc[t][4 * b4 + 3][2 * i + h] += v.w;
+                  }
+                xs += __ldcg(src + WCOLS);
+              }
+              accx[t][h] = xs;
+            }
+        }
+      }
+      if (write_out) {
+        // out = scale * (acc - zero * sum_k x); lane (g, q): channels 16g..16g+15, tokens 8t + 2q, + 1
+        const float poison = (alive && !*abort_flag) ? 0.f : __int_as_float(0x7fc00000);
+        const int64_t cbase = (int64_t)cg * WCOLS;
+#pragma unroll
+        for (int i = 0; i < 2; ++i)
+#pragma unroll
+          for (int b = 0; b < 8; ++b) {
+            const int64_t n = cbase + 16 * g + 8 * i + b;
+            if (n >= p.N) continue;
+            const float sc = zs_to_f32<ZST>(p.scale, n), z = zs_to_f32<ZST>(p.zero, n);
+#pragma unroll
+            for (int t = 0; t < NTOK; ++t)
+#pragma unroll
+              for (int h = 0; h < 2; ++h) {
+                const int64_t m = m0 + 8 * t + 2 * q + h;
+                if (m < p.M) out[m * p.N + n] = from_f32<XT>(sc * (acc[t][b][2 * i + h] - z * accx[t][h]) + poison);
+              }
+          }
+      }
+    }
+    clear_acc();
+  }
+}
+
+// ------------------------------------------------------------------ host ----
+struct StreamPlan { int use; int ntok; int ncg; int spc; int64_t S; int G; int maxc; size_t part_bytes; };
+
+StreamPlan plan_w4_stream(int64_t M, int64_t N, int64_t K) {
+  StreamPlan pl;
+  memset(&pl, 0, sizeof(pl));
+  if (M < 1 || M > 16 || N % 16 != 0 || K % 2 != 0) return pl;
+  pl.ncg = (int)cdiv(N, WCOLS);
+  if (pl.ncg > 1024) return pl;                       // one ticket per channel group in 4 KB
+  pl.use = 1;
+  pl.ntok = M <= 8 ? 1 : 2;
+  const int64_t total_steps = cdiv(K / 2, 8);
+  pl.spc = (int)cdiv(total_steps, S_STEPS);
+  pl.S = (int64_t)pl.ncg * pl.spc;
+  pl.G = (int)std::min<int64_t>((pl.ntok == 1 ? 3 : 2) * (int64_t)sm_count(), pl.S);   // one resident wave
+  const int64_t per = pl.S / pl.G;                    // every CTA streams per or per + 1 stages
+  pl.maxc = (int)cdiv(pl.spc, per) + 1;
+  pl.part_bytes = align_up((size_t)pl.ncg * pl.maxc * 8 * pl.ntok * PSTRIDE * sizeof(float), 256);
+  return pl;
+}
+
+template <typename XT, typename CT, int NTOK, typename ZST>
+static int launch_stream_inst(const StreamPlan& pl, const StreamParams& p, const CUtensorMap& wmap, cudaStream_t s) {
+  auto kern = w4_stream_kernel<XT, CT, NTOK, ZST>;
+  static bool attr_set[64] = {false};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev >= 0 && dev < 64 && !attr_set[dev]) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, S_RING_BYTES) != cudaSuccess)
+      return fail(JGQ_ERR_CUDA, "w4_matmul: cannot raise the dynamic shared memory limit");
+    attr_set[dev] = true;
+  }
+  kern<<<(unsigned)pl.G, S_THREADS, S_RING_BYTES, s>>>(wmap, p);
+  return check_launch("w4_stream");
+}
+
+int launch_w4_stream(const StreamPlan& pl, const void* x, int x_dtype, const uint8_t* packed, const void* zero,
+                     const void* scale, int zs_dtype, void* out, int64_t M, int64_t N, int64_t K, void* ws,
+                     cudaStream_t s) {
+  CUtensorMap wmap;
+  const int rc = encode_tmap_2d_u8(&wmap, packed, (uint64_t)N, (uint64_t)(K / 2), (uint64_t)N, WCOLS, S_ROWS, 1);
+  if (rc) return rc;
+  StreamParams p;
+  memset(&p, 0, sizeof(p));
+  p.x = x; p.zero = zero; p.scale = scale; p.out = out;
+  p.tickets = (int*)ws;
+  p.partials = (float*)((char*)ws + 4096);
+  p.M = M; p.N = N; p.K = K;
+  p.ncg = pl.ncg; p.mtiles = 1; p.spc = pl.spc; p.S = pl.S; p.G = pl.G; p.maxc = pl.maxc;
+  const bool zf = zs_dtype == JGQ_F32;
+#define JGQ_STREAM(XT, CT)                                                                        \
+  if (pl.ntok == 1)                                                                               \
+    return zf ? launch_stream_inst<XT, CT, 1, float>(pl, p, wmap, s) : launch_stream_inst<XT, CT, 1, __half>(pl, p, wmap, s); \
+  return zf ? launch_stream_inst<XT, CT, 2, float>(pl, p, wmap, s) : launch_stream_inst<XT, CT, 2, __half>(pl, p, wmap, s)
+  if (x_dtype == JGQ_F32) { JGQ_STREAM(float, __nv_bfloat16); }
+  if (x_dtype == JGQ_F16) { JGQ_STREAM(__half, __half); }
+  JGQ_STREAM(__nv_bfloat16, __nv_bfloat16);
+#undef JGQ_STREAM
+}
+
+}  // namespace jgq
