@@ -429,25 +429,43 @@ def bench_w4(torch, G, dev, peaks, cases=None):
             need = _lib.lib.jgq_w4_matmul_workspace_bytes(M, N, K, 0)
             ws = torch.zeros(max(need, 1), dtype=torch.uint8, device=dev)
             out = torch.empty((M, N), dtype=torch.float16, device=dev)
-            st = torch.cuda.current_stream().cuda_stream
-
-            def launch(i):
+            def launch(i, st):
                 _lib.check(_lib.lib.jgq_w4_matmul(x.data_ptr(), _lib.F16, packed[i % nbuf].data_ptr(), zero.data_ptr(),
                                                   scale.data_ptr(), _lib.F16, out.data_ptr(), M, N, K, 0,
                                                   ws.data_ptr(), need, st))
+            st = torch.cuda.current_stream().cuda_stream
             for i in range(3):
-                launch(i)
+                launch(i, st)
             torch.cuda.synchronize()
             e0.record()
             for i in range(iters):
-                launch(i)
+                launch(i, st)
             e1.record()
             torch.cuda.synchronize()
-            ms = e0.elapsed_time(e1) / iters
+            ms_loop = e0.elapsed_time(e1) / iters
+            # the same launches recorded once into a CUDA graph and replayed: at a few microseconds per
+            # kernel the Python call per launch would otherwise leave the GPU idle between kernels
+            ms = ms_loop
+            try:
+                graph = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(graph):
+                    cst = torch.cuda.current_stream().cuda_stream
+                    for i in range(iters):
+                        launch(i, cst)
+                graph.replay()
+                torch.cuda.synchronize()
+                e0.record()
+                graph.replay()
+                e1.record()
+                torch.cuda.synchronize()
+                ms = e0.elapsed_time(e1) / iters
+                del graph
+            except Exception:      # capture not possible: keep the host-loop figure
+                pass
             bytes_alg = wbytes + 4 * N + 2 * M * K + 2 * M * N
             gbs = bytes_alg / (ms * 1e-3) / 1e9
             tflops = 2.0 * M * K * N / (ms * 1e-3) / 1e12
-            rows.append({'K': K, 'N': N, 'M': M, 'us': ms * 1e3, 'GBps': gbs, 'hbm_frac': gbs / hbm,
+            rows.append({'K': K, 'N': N, 'M': M, 'us': ms * 1e3, 'us_host_loop': ms_loop * 1e3, 'GBps': gbs, 'hbm_frac': gbs / hbm,
                         'TFLOPs': tflops, 'tensor_frac': tflops / tf})
         del packed, qms
         torch.cuda.empty_cache()
