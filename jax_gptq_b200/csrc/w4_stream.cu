@@ -134,22 +134,41 @@ w4_stream_kernel(const __grid_constant__ CUtensorMap wmap, const StreamParams p)
       if (alive) {
         const uint8_t* tile = ring + slot * S_STAGE_BYTES;
         const int64_t step0 = (int64_t)st * S_STEPS;
+        // activation fragments: lane (g, q) needs x[m0 + 8t + g][16*step + 2q .. +1] and [.. + 8 + 2q .. +1]
         uint32_t xb[NTOK][2], xlo[NTOK][2];
-        load_xfrags<XT, NTOK>(x, m0, p.M, 16 * (step0 + warp), p.K, g, q, xb, xlo);
+        const uint32_t* xrow[NTOK];            // 16-bit activations: row pointer in 32-bit words, or null
+#pragma unroll
+        for (int t = 0; t < NTOK; ++t) {
+          const int64_t m = m0 + 8 * t + g;
+          xrow[t] = (!kSplitX && m < p.M) ? reinterpret_cast<const uint32_t*>(x) + (m * p.K) / 2 + q : nullptr;
+        }
+        const int kwords = (int)(p.K / 2);     // 32-bit words per activation row
+        auto fetch_x = [&](int64_t step) {
+          if (kSplitX) {
+            load_xfrags<XT, NTOK>(x, m0, p.M, 16 * step, p.K, g, q, xb, xlo);
+          } else {
+            const int w0 = (int)(8 * step);
+#pragma unroll
+            for (int t = 0; t < NTOK; ++t) {
+              xb[t][0] = (xrow[t] && w0 + q < kwords) ? __ldg(xrow[t] + w0) : 0u;
+              xb[t][1] = (xrow[t] && w0 + 4 + q < kwords) ? __ldg(xrow[t] + w0 + 4) : 0u;
+              xlo[t][0] = xlo[t][1] = 0u;
+            }
+          }
+        };
+        fetch_x(step0 + warp);
 #pragma unroll
         for (int u = 0; u < S_STEPS / WWARPS; ++u) {
           const int sl = WWARPS * u + warp;                 // step inside the stage
           uint32_t cb[NTOK][2], clo[NTOK][2];
 #pragma unroll
           for (int t = 0; t < NTOK; ++t) { cb[t][0] = xb[t][0]; cb[t][1] = xb[t][1]; clo[t][0] = xlo[t][0]; clo[t][1] = xlo[t][1]; }
-          if (u + 1 < S_STEPS / WWARPS)
-            load_xfrags<XT, NTOK>(x, m0, p.M, 16 * (step0 + sl + WWARPS), p.K, g, q, xb, xlo);
-          if (step0 + sl < total_steps) {
-            const int ra = 8 * sl + q, rb = ra + 4;         // byte rows; 16-byte chunk g, swizzled by row & 7
-            const uint4 r0 = *reinterpret_cast<const uint4*>(tile + ra * WCOLS + ((g ^ (ra & 7)) << 4));
-            const uint4 r1 = *reinterpret_cast<const uint4*>(tile + rb * WCOLS + ((g ^ (rb & 7)) << 4));
-            w4_step<CT, NTOK, kSplitX>(acc, accx, r0, r1, cb, clo);
-          }
+          if (u + 1 < S_STEPS / WWARPS) fetch_x(step0 + sl + WWARPS);
+          // rows past the end of the matrix arrive as zeros (TMA fill) and their activations are zero too
+          const int ra = 8 * sl + q, rb = ra + 4;           // byte rows; 16-byte chunk g, swizzled by row & 7
+          const uint4 r0 = *reinterpret_cast<const uint4*>(tile + ra * WCOLS + ((g ^ (ra & 7)) << 4));
+          const uint4 r1 = *reinterpret_cast<const uint4*>(tile + rb * WCOLS + ((g ^ (rb & 7)) << 4));
+          w4_step<CT, NTOK, kSplitX>(acc, accx, r0, r1, cb, clo);
         }
         __syncwarp();
         if (lane == 0) mbar_arrive(&empty_bar[slot]);
