@@ -157,17 +157,27 @@ w4_stream_kernel(const __grid_constant__ CUtensorMap wmap, const StreamParams p)
           }
         };
         fetch_x(step0 + warp);
+        // byte rows 8*sl + q and + 4 of step sl; 16-byte chunk g, swizzled by row & 7.  The next step's
+        // two shared-memory loads are issued before the current step's arithmetic.
+        auto tile_load = [&](int sl, uint4& a, uint4& b) {
+          const int ra = 8 * sl + q, rb = ra + 4;
+          a = *reinterpret_cast<const uint4*>(tile + ra * WCOLS + ((g ^ (ra & 7)) << 4));
+          b = *reinterpret_cast<const uint4*>(tile + rb * WCOLS + ((g ^ (rb & 7)) << 4));
+        };
+        uint4 n0, n1;
+        tile_load(warp, n0, n1);
 #pragma unroll
         for (int u = 0; u < S_STEPS / WWARPS; ++u) {
           const int sl = WWARPS * u + warp;                 // step inside the stage
           uint32_t cb[NTOK][2], clo[NTOK][2];
 #pragma unroll
           for (int t = 0; t < NTOK; ++t) { cb[t][0] = xb[t][0]; cb[t][1] = xb[t][1]; clo[t][0] = xlo[t][0]; clo[t][1] = xlo[t][1]; }
-          if (u + 1 < S_STEPS / WWARPS) fetch_x(step0 + sl + WWARPS);
+          const uint4 r0 = n0, r1 = n1;
+          if (u + 1 < S_STEPS / WWARPS) {
+            fetch_x(step0 + sl + WWARPS);
+            tile_load(sl + WWARPS, n0, n1);
+          }
           // rows past the end of the matrix arrive as zeros (TMA fill) and their activations are zero too
-          const int ra = 8 * sl + q, rb = ra + 4;           // byte rows; 16-byte chunk g, swizzled by row & 7
-          const uint4 r0 = *reinterpret_cast<const uint4*>(tile + ra * WCOLS + ((g ^ (ra & 7)) << 4));
-          const uint4 r1 = *reinterpret_cast<const uint4*>(tile + rb * WCOLS + ((g ^ (rb & 7)) << 4));
           w4_step<CT, NTOK, kSplitX>(acc, accx, r0, r1, cb, clo);
         }
         __syncwarp();
@@ -251,17 +261,32 @@ w4_stream_kernel(const __grid_constant__ CUtensorMap wmap, const StreamParams p)
 #pragma unroll
               for (int b = 0; b < 8; ++b) { acc[t][b][h] = 0.f; acc[t][b][2 + h] = 0.f; }
               float xs = 0.f;
-              for (int z = 0; z < ncontrib; ++z) {
-                const float* src = base + ((int64_t)z * ROWS + 8 * t + 2 * q + h) * PSTRIDE;
+              for (int z0 = 0; z0 < ncontrib; z0 += 2) {
+                float4 v[2][4];
+                float xv[2];
 #pragma unroll
-                for (int i = 0; i < 2; ++i)
+                for (int zz = 0; zz < 2; ++zz) {
+                  if (z0 + zz < ncontrib) {
+                    const float* src = base + ((int64_t)(z0 + zz) * ROWS + 8 * t + 2 * q + h) * PSTRIDE;
 #pragma unroll
-                  for (int b4 = 0; b4 < 2; ++b4) {
-                    const float4 v = __ldcg(reinterpret_cast<const float4*>(src + 16 * g + 8 * i + 4 * b4));
-                    acc[t][4 * b4 + 0][2 * i + h] += v.x; acc[t][4 * b4 + 1][2 * i + h] += v.y;
-                    acc[t][4 * b4 + 2][2 * i + h] += v.z; acc[t][4 * b4 + 3][2 * i + h] += v.w;
+                    for (int j = 0; j < 4; ++j) v[zz][j] = __ldcg(reinterpret_cast<const float4*>(src + 16 * g + 4 * j));
+                    xv[zz] = __ldcg(src + WCOLS);
                   }
-                xs += __ldcg(src + WCOLS);
+                }
+#pragma unroll
+                for (int zz = 0; zz < 2; ++zz) {
+                  if (z0 + zz < ncontrib) {
+#pragma unroll
+                    for (int i = 0; i < 2; ++i)
+#pragma unroll
+                      for (int b4 = 0; b4 < 2; ++b4) {
+                        const float4 w = v[zz][2 * i + b4];
+                        acc[t][4 * b4 + 0][2 * i + h] += w.x; acc[t][4 * b4 + 1][2 * i + h] += w.y;
+                        acc[t][4 * b4 + 2][2 * i + h] += w.z; acc[t][4 * b4 + 3][2 * i + h] += w.w;
+                      }
+                    xs += xv[zz];
+                  }
+                }
               }
               accx[t][h] = xs;
             }
@@ -306,7 +331,7 @@ StreamPlan plan_w4_stream(int64_t M, int64_t N, int64_t K) {
   const int64_t total_steps = cdiv(K / 2, 8);
   pl.spc = (int)cdiv(total_steps, S_STEPS);
   pl.S = (int64_t)pl.ncg * pl.spc;
-  pl.G = (int)std::min<int64_t>((pl.ntok == 1 ? 3 : 2) * (int64_t)sm_count(), pl.S);   // one resident wave
+  pl.G = (int)std::min<int64_t>((pl.ntok == 1 ? 3 : 2) * (int64_t)sm_count(), std::max<int64_t>(1, pl.S / 2));   // one resident wave, >= 2 stages each
   const int64_t per = pl.S / pl.G;                    // every CTA streams per or per + 1 stages
   pl.maxc = (int)cdiv(pl.spc, per) + 1;
   pl.part_bytes = align_up((size_t)pl.ncg * pl.maxc * 8 * pl.ntok * PSTRIDE * sizeof(float), 256);
