@@ -1,0 +1,72 @@
+"""Two-GPU check of the sharded forms (skipped on boxes with one GPU): token-sharded Hessian +
+NCCL all-reduce + column-sharded quantization against the single-GPU result, and the
+column-sharded packed matmul against the unsharded one."""
+import os
+import socket
+
+import numpy as np
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(('127.0.0.1', 0))
+        return s.getsockname()[1]
+
+
+def _worker(rank, world, port, q):
+    import torch.distributed as dist
+    import importlib
+    os.environ['MASTER_ADDR'] = '127.0.0.1'
+    os.environ['MASTER_PORT'] = str(port)
+    torch.cuda.set_device(rank)
+    dist.init_process_group('nccl', rank=rank, world_size=world, device_id=torch.device('cuda', rank))
+    try:
+        G = importlib.import_module('jax_gptq_b200.gptq')
+        D = importlib.import_module('jax_gptq_b200.dist')
+        op = importlib.import_module('jax_gptq_b200.op')
+        rng = np.random.default_rng(77)
+        K, N, n = 512, 640, 4096
+        W = torch.from_numpy((0.02 * rng.standard_normal((K, N))).astype(np.float32)).cuda()
+        X = torch.from_numpy(rng.standard_normal((n, K)).astype(np.float32)).cuda()
+        b, e = D.shard_range(n, rank, world)
+        Q, params, (c0, c1) = D.gptq_token_sharded(W, [X[b:e]], block_size=128)
+        Q_full, p_full = G.gptq(W, [X], block_size=128)
+        same = float((Q == Q_full[:, c0:c1]).float().mean().item())
+        ok_scale = bool(torch.equal(params['scale'], p_full['scale'][c0:c1]))
+        # column-sharded matmul
+        qm_full = G.pack_matrix(Q_full, p_full)
+        qm_shard = G.pack_matrix(Q_full[:, c0:c1].contiguous(),
+                                 {'scale': p_full['scale'][c0:c1].contiguous(), 'zero': p_full['zero'][c0:c1].contiguous(),
+                                  'maxq': 15})
+        x = X[:16].half()
+        y_full = op.quantized_matmul(x, qm_full)
+        y = D.quantized_matmul_column_sharded(x, qm_shard, gather=True, N=N)
+        err = float((y.float() - y_full.float()).abs().max().item())
+        q.put((rank, same, ok_scale, err, tuple(y.shape)))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_token_and_column_sharding_two_gpus():
+    if torch.cuda.device_count() < 2:
+        pytest.skip('needs two GPUs')
+    import torch.multiprocessing as mp
+    world = 2
+    ctx = mp.get_context('spawn')
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_worker, args=(r, world, port, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    results = [q.get(timeout=300) for _ in range(world)]
+    for p in procs:
+        p.join(timeout=120)
+        assert p.exitcode == 0
+    for rank, same, ok_scale, err, shape in results:
+        assert same >= 0.999, f'rank {rank}: identical values {same}'
+        assert ok_scale
+        assert err <= 2e-2 and shape == (16, 640)
