@@ -306,12 +306,21 @@ w4_umma_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__
         asm volatile("bar.sync 1, 128;" ::: "memory");
         if (*reinterpret_cast<volatile int*>(s_last) && n < p.N) {
           __threadfence();
-          for (int tok = 0; tok < ntok; ++tok) {
-            float acc = 0.f;
-            for (int z = 0; z < p.ksplit; ++z)
-              acc += __ldcg(&p.partials[(((int64_t)z * p.M + m0 + tok) * p.ncg + cg) * U_COLS + r]);
-            const float poison = aborted ? __int_as_float(0x7fc00000) : 0.f;
-            outp[(m0 + tok) * p.N + n] = from_f32<XT>(sc * (acc - zr * p.xsum[m0 + tok]) + poison);
+          const float poison = aborted ? __int_as_float(0x7fc00000) : 0.f;
+          for (int tok0 = 0; tok0 < ntok; tok0 += 8) {      // eight tokens' slices in flight at a time
+            float a8[8];
+#pragma unroll
+            for (int u = 0; u < 8; ++u) a8[u] = 0.f;
+            for (int z = 0; z < p.ksplit; ++z) {
+#pragma unroll
+              for (int u = 0; u < 8; ++u)
+                if (tok0 + u < ntok)
+                  a8[u] += __ldcg(&p.partials[(((int64_t)z * p.M + m0 + tok0 + u) * p.ncg + cg) * U_COLS + r]);
+            }
+#pragma unroll
+            for (int u = 0; u < 8; ++u)
+              if (tok0 + u < ntok)
+                outp[(m0 + tok0 + u) * p.N + n] = from_f32<XT>(sc * (a8[u] - zr * p.xsum[m0 + tok0 + u]) + poison);
           }
         }
       } else if (aborted && n < p.N) {
@@ -359,6 +368,10 @@ UmmaPlan plan_w4_umma(int64_t M, int64_t N, int64_t K, int x_dtype) {
   const int sms = sm_count();
   int64_t kmax = std::max<int64_t>(1, total_stages / 8);          // at least 8 stages per CTA
   if (base > (int64_t)(U_TICKET_BYTES / sizeof(int))) kmax = 1;
+  // Split-K only when the tiles alone cannot occupy the SMs: the slice reduction costs
+  // ksplit x tokens reads per epilogue thread, which is only cheap for few tokens.
+  if (2 * base >= sms) kmax = 1;
+  if (pl.NT > 64) kmax = std::min<int64_t>(kmax, 4);
   kmax = std::min<int64_t>(kmax, 64);
   int64_t best = 1;
   double best_eff = 0.0;
