@@ -237,13 +237,9 @@ def run_ours(args):
     total_weights = layers * sum(k * n for _, k, n in LINEARS)
 
     def step_resident():
-        out = []
-        for weights, captured in zip(model, acts):
-            for name, _, _ in LINEARS:
-                Q, params = gg.gptq(weights[name], list(captured[name].chunk(CALIB_BATCHES)),
-                                   block_size=BLOCK_SIZE, damping=DAMP)
-                out.append(G.pack_matrix(Q, params))
-        return out
+        jobs = [(weights[name], list(captured[name].chunk(CALIB_BATCHES)))
+                for weights, captured in zip(model, acts) for name, _, _ in LINEARS]
+        return gg.gptq_many(jobs, block_size=BLOCK_SIZE, damping=DAMP, pack=True, streams=args.streams)
 
     # ---- value: device-resident ----
     for _ in range(args.warmup):
@@ -352,7 +348,7 @@ def run_ours(args):
         jobs = [(host_w[i][name], list(host_acts[i % distinct][name].chunk(CALIB_BATCHES)))
                 for i in range(layers) for name, _, _ in LINEARS]
         outs = [host_out[i][name] for i in range(layers) for name, _, _ in LINEARS]
-        gg.gptq_many(jobs, block_size=BLOCK_SIZE, damping=DAMP, pack=True, out_host=outs)
+        gg.gptq_many(jobs, block_size=BLOCK_SIZE, damping=DAMP, pack=True, out_host=outs, streams=args.streams)
         torch.cuda.synchronize()
 
     for _ in range(min(args.warmup, 3)):
@@ -394,6 +390,7 @@ def run_ours(args):
                 'config': {'workload': workload_name(layers), 'weights_per_step_per_gpu': total_weights,
                            'l2': 'inputs larger than L2 (each linear reads 0.2-0.8 GB of activations)',
                            'parallelism': f'{world} independent models, one per GPU, no data-path collective',
+                           'linears_in_flight_per_gpu': args.streams,
                            'resident_activation_bytes_per_gpu': acts_dev_bytes, 'setup_seconds': setup_s},
                 'clocks': clocks, 'e2e': e2e, 'gpu_launches': int(launches), 'roofline': roofline,
                 'cpu_baseline': cpu_baseline, 'stage_ms_one_block': stages, 'w4_matmul': w4}
@@ -480,6 +477,7 @@ def main():
     ap.add_argument('--impl', default='ours', choices=['ours', 'reference'])
     ap.add_argument('--layers', type=int, default=N_LAYERS, help='blocks to quantize (12 = the full workload)')
     ap.add_argument('--skip-matmul', action='store_true')
+    ap.add_argument('--streams', type=int, default=3, help='independent linears in flight (compute streams)')
     ap.add_argument('--only-matmul', action='store_true', help='run only the packed-int4 matmul sweep')
     ap.add_argument('--matmul-shapes', default='', help='comma list of KxNxM cases for --only-matmul')
     ap.add_argument('--skip-cpu', action='store_true')

@@ -237,8 +237,15 @@ def _quantize(Wf, L, params, block_size, out_dtype, want_codes=False):
     return Q, codes
 
 
+def _raise_status(st):
+    if st >> 8:
+        raise RuntimeError('a device-side wait timed out while accumulating the Hessian')
+    if st != 0:
+        raise ValueError('NaN when computing Hinv. Features NaN?')      # gptq.py:194-196
+
+
 def gptq(W, xs, block_size=128, actorder=False, damping=0.01, use_fp64=False, *,
-         bits=4, H=None, return_codes=False):
+         bits=4, H=None, return_codes=False, _defer=None):
     """Quantize W (K x N) with calibration batches xs.  Returns (Q, params) like the
     reference (gptq.py:182-212): Q holds the dequantised values in W's dtype and
     params = {'scale', 'zero', 'maxq'}.
@@ -281,11 +288,11 @@ def gptq(W, xs, block_size=128, actorder=False, damping=0.01, use_fp64=False, *,
         Q = Q[invperm, :].contiguous()
         if codes is not None:
             codes = codes[invperm, :].contiguous()
-    st = int((status | (h_status << 8)).item())              # gptq.py:194-196 (one host sync per call)
-    if st >> 8:
-        raise RuntimeError('a device-side wait timed out while accumulating the Hessian')
-    if st != 0:
-        raise ValueError('NaN when computing Hinv. Features NaN?')
+    combined = status | (h_status << 8)
+    if _defer is not None:
+        _defer.append(combined)          # the caller checks the status words after its own synchronisation
+    else:
+        _raise_status(int(combined.item()))                  # gptq.py:194-196 (one host sync per call)
     out_params = {'scale': _out(params['scale'], as_np), 'zero': _out(params['zero'], as_np),
                   'maxq': params['maxq']}
     if return_codes:
@@ -393,25 +400,37 @@ def unpack_matrix(weight, dtype=None):
 # --------------------------------------------------------------------------
 # many layers with host-resident inputs: copies overlap the previous layer's compute
 # --------------------------------------------------------------------------
-def gptq_many(jobs, block_size=128, actorder=False, damping=0.01, bits=4, pack=True, out_host=None):
-    """Run ``gptq`` (and ``pack_matrix`` when `pack`) over a sequence of ``(W, xs)`` jobs.
+def gptq_many(jobs, block_size=128, actorder=False, damping=0.01, bits=4, pack=True, out_host=None, streams=3):
+    """Run ``gptq`` (and ``pack_matrix`` when `pack`) over a sequence of independent ``(W, xs)`` jobs.
 
     This is the loop the reference's interpreter runs layer by layer
-    (quantize_interpreter.py:151-299) with its host<->device ``device_put`` traffic: while
-    job i is being quantized on the current stream, the weights and calibration batches of
-    job i+1 are copied from (pinned) host memory on a second stream.  Device-resident inputs
-    are used in place.  `out_host`, if given, is a list of ``(packed, scale, zero)`` pinned
-    host tensors that receive each packed result (device->host, asynchronously).
-    Returns the list of results (QuantizedMatrix when `pack`, else ``(Q, params)``).
+    (quantize_interpreter.py:151-299) with its host<->device ``device_put`` traffic, for jobs
+    whose inputs already exist (captured calibration activations):
+
+    * host-resident inputs (pinned) of job i+1 are copied on a copy stream while earlier jobs
+      compute; device-resident inputs are used in place;
+    * jobs are issued round-robin on `streams` compute streams, so the latency-bound parts of
+      one layer (Cholesky panels, the sequential quantize loop) overlap the Hessian GEMM of the
+      next ones; each stream has its own scratch buffers;
+    * the NaN / not-positive-definite status words are read once, after all jobs were issued.
+
+    `out_host`, if given, is a list of ``(packed, scale, zero)`` pinned host tensors that receive
+    each packed result (device->host, asynchronously).  Returns the list of results
+    (QuantizedMatrix when `pack`, else ``(Q, params)``), valid after the function returns.
     """
     jobs = list(jobs)
     if not jobs:
         return []
-    compute = torch.cuda.current_stream()
-    copier = torch.cuda.Stream()
     device = _dev()
+    main = torch.cuda.current_stream()
+    copier = torch.cuda.Stream()
+    workers = [torch.cuda.Stream() for _ in range(max(1, int(streams)))]
+    start = main.record_event()
+    copier.wait_event(start)
+    for w in workers:
+        w.wait_event(start)
 
-    def stage(job):
+    def stage(job, consumer):
         W, xs = job
         with torch.cuda.stream(copier):
             Wd = W if (isinstance(W, torch.Tensor) and W.is_cuda) else _to_dev(W)
@@ -420,41 +439,49 @@ def gptq_many(jobs, block_size=128, actorder=False, damping=0.01, bits=4, pack=T
             if host and len(host) == len(xs):
                 ts = [x if isinstance(x, torch.Tensor) else torch.from_numpy(np.ascontiguousarray(x)) for x in xs]
                 K = ts[0].shape[-1]
-                same = all(t.dtype == ts[0].dtype and t.shape[-1] == K for t in ts)
-                if same:
+                if all(t.dtype == ts[0].dtype and t.shape[-1] == K for t in ts):
                     rows = [t.numel() // K for t in ts]
                     buf = torch.empty((sum(rows), K), dtype=ts[0].dtype, device=device)
-                    views, r0 = [], 0
+                    xd, r0 = [], 0
                     for t, r in zip(ts, rows):
                         v = buf[r0:r0 + r]
                         v.copy_(t.reshape(r, K), non_blocking=True)
-                        views.append(v)
+                        xd.append(v)
                         r0 += r
-                    xd = views
-                    buf.record_stream(compute)
+                    buf.record_stream(consumer)
                 else:
                     xd = [_to_dev(t) for t in ts]
             else:
                 xd = [_to_dev(x) for x in xs]
             for t in [Wd] + xd:
                 if isinstance(t, torch.Tensor) and t.is_cuda:
-                    t.record_stream(compute)
+                    t.record_stream(consumer)
             ev = copier.record_event()
         return Wd, xd, ev
 
-    results = []
-    nxt = stage(jobs[0])
+    results, deferred = [], []
+    nxt = stage(jobs[0], workers[0])
     for i in range(len(jobs)):
         Wd, xd, ev = nxt
         if i + 1 < len(jobs):
-            nxt = stage(jobs[i + 1])
-        compute.wait_event(ev)
-        Q, params = gptq(Wd, xd, block_size=block_size, actorder=actorder, damping=damping, bits=bits)
-        res = pack_matrix(Q, params) if pack else (Q, params)
-        if out_host is not None and pack:
-            p, s, z = out_host[i]
-            p.copy_(res.int_weight, non_blocking=True)
-            s.copy_(res.scale, non_blocking=True)
-            z.copy_(res.zero, non_blocking=True)
+            nxt = stage(jobs[i + 1], workers[(i + 1) % len(workers)])
+        ws = workers[i % len(workers)]
+        with torch.cuda.stream(ws):
+            ws.wait_event(ev)
+            Q, params = gptq(Wd, xd, block_size=block_size, actorder=actorder, damping=damping, bits=bits,
+                             _defer=deferred)
+            res = pack_matrix(Q, params) if pack else (Q, params)
+            if out_host is not None and pack:
+                p, s, z = out_host[i]
+                p.copy_(res.int_weight, non_blocking=True)
+                s.copy_(res.scale, non_blocking=True)
+                z.copy_(res.zero, non_blocking=True)
+            for t in ((res.int_weight, res.scale, res.zero) if pack else (Q, params['scale'], params['zero'])):
+                t.record_stream(main)
         results.append(res)
+    for w in workers:
+        main.wait_event(w.record_event())
+    main.wait_event(copier.record_event())
+    if deferred:
+        _raise_status(int(torch.stack([d.to(device) for d in deferred]).max().item()))
     return results
