@@ -414,3 +414,29 @@ def test_hessian_tensor_path_half(G, dtype):
     ref = (X.double().numpy().T @ X.double().numpy()) / 2048
     got = host(G.accumulate_H([X.cuda()]))
     assert np.allclose(got, ref, atol=5e-6, rtol=1e-5)
+
+
+def test_gptq_many_matches_sequential(G):
+    """Jobs issued on several streams with host- and device-resident inputs give exactly the
+    results of one-at-a-time calls; a bad job still raises."""
+    rng = np.random.default_rng(123)
+    jobs_np = []
+    for i, (K, N) in enumerate([(256, 192), (128, 320), (256, 64), (384, 128), (128, 96)]):
+        W = (0.02 * rng.standard_normal((K, N))).astype(np.float32)
+        xs = [rng.standard_normal((512, K)).astype(np.float32) for _ in range(2)]
+        jobs_np.append((W, xs))
+    seq = []
+    for W, xs in jobs_np:
+        Q, p = G.gptq(dev(W), [dev(x) for x in xs], block_size=64)
+        seq.append(G.pack_matrix(Q, p))
+    mixed = [(dev(W), [dev(x) for x in xs]) if i % 2 else (torch.from_numpy(W).pin_memory(), [torch.from_numpy(x).pin_memory() for x in xs])
+             for i, (W, xs) in enumerate(jobs_np)]
+    for streams in (1, 3):
+        got = G.gptq_many(mixed, block_size=64, streams=streams)
+        torch.cuda.synchronize()
+        for a, b in zip(got, seq):
+            assert torch.equal(a.int_weight, b.int_weight)
+            assert torch.equal(a.scale, b.scale) and torch.equal(a.zero, b.zero)
+    bad = list(mixed) + [(dev(jobs_np[0][0]), [dev(np.full((8, 256), np.nan, dtype=np.float32))])]
+    with pytest.raises(ValueError):
+        G.gptq_many(bad, block_size=64)
