@@ -75,6 +75,52 @@ def _workspace(nbytes, zeroed=False, tag='ws'):
     return buf
 
 
+class _Arena:
+    """Named, grow-only device buffers for the temporaries of one compute stream.  While an arena
+    is active (`gptq_many`), the temporaries of `gptq` come from it instead of the allocator, so
+    a steady stream of jobs performs no device allocation at all.  Outgrown buffers are kept
+    until `release()` (called after a device synchronisation)."""
+
+    def __init__(self):
+        self.bufs = {}
+        self.old = []
+
+    def get(self, tag, shape, dtype, zero=False):
+        n = 1
+        for d in shape:
+            n *= int(d)
+        nbytes = max(n * torch.empty((), dtype=dtype).element_size(), 16)
+        buf = self.bufs.get(tag)
+        if buf is None or buf.numel() < nbytes:
+            if buf is not None:
+                self.old.append(buf)
+            buf = torch.empty(int(nbytes * 1.25) + 256, dtype=torch.uint8, device=_dev())
+            self.bufs[tag] = buf
+        t = buf[:nbytes].view(dtype)[:n].view(*shape) if n else torch.empty(shape, dtype=dtype, device=_dev())
+        if zero:
+            t.zero_()
+        return t
+
+    def release(self):
+        self.old.clear()
+
+
+_ARENA = None          # the arena of the job being enqueued (set by gptq_many)
+_arena_cache = {}
+
+
+def _tmp(tag, shape, dtype, zero=False):
+    if _ARENA is not None:
+        return _ARENA.get(tag, shape, dtype, zero)
+    return (torch.zeros if zero else torch.empty)(tuple(shape), dtype=dtype, device=_dev())
+
+
+def _workspace_for(nbytes):
+    if _ARENA is not None:
+        return _ARENA.get('ws', (int(nbytes),), torch.uint8)
+    return _workspace(nbytes)
+
+
 def _view3(shape, axis):
     outer = int(np.prod(shape[:axis], dtype=np.int64)) if axis > 0 else 1
     inner = int(np.prod(shape[axis + 1:], dtype=np.int64)) if axis + 1 < len(shape) else 1
@@ -154,7 +200,7 @@ def _accumulate_raw(xs, H=None, status=None):
         if not b.is_contiguous():
             b = b.contiguous()
         if H is None:
-            H = torch.zeros((K, K), dtype=torch.float32, device=b.device)
+            H = _tmp('H', (K, K), torch.float32, zero=True)
         n = b.shape[0]
         rows = n
         if b.dtype != torch.float32:
@@ -163,7 +209,7 @@ def _accumulate_raw(xs, H=None, status=None):
             chunk = b[r0:r0 + rows]
             m = chunk.shape[0]
             need = lib.jgq_hessian_workspace_bytes(m, K, _DT[chunk.dtype])
-            ws = _workspace(need) if need else None
+            ws = _workspace_for(need) if need else None
             check(lib.jgq_hessian_accum(chunk.data_ptr(), _DT[chunk.dtype], m, K, H.data_ptr(),
                                         _ptr(ws), need, _ptr(status), _stream()))
         n_total += n
@@ -216,10 +262,10 @@ def get_col_quantize_params(W, bits=4):
 def _damp_and_invert(Wf, H, damping):
     """In place on Wf (dead rows zeroed) and H (destroyed).  Returns (L, status tensor)."""
     K, N = Wf.shape
-    L = torch.empty((K, K), dtype=torch.float32, device=Wf.device)
-    status = torch.zeros(1, dtype=torch.int32, device=Wf.device)
+    L = _tmp('L', (K, K), torch.float32)
+    status = _tmp('status', (1,), torch.int32, zero=True)
     need = lib.jgq_damp_invert_workspace_bytes(K)
-    ws = _workspace(need)
+    ws = _workspace_for(need)
     check(lib.jgq_damp_invert(Wf.data_ptr(), N, H.data_ptr(), K, float(damping), L.data_ptr(),
                               ws.data_ptr(), need, status.data_ptr(), _stream()))
     return L, status
@@ -227,10 +273,10 @@ def _damp_and_invert(Wf, H, damping):
 
 def _quantize(Wf, L, params, block_size, out_dtype, want_codes=False):
     K, N = Wf.shape
-    Q = torch.empty((K, N), dtype=out_dtype, device=Wf.device)
+    Q = _tmp('Q', (K, N), out_dtype)
     codes = torch.empty((K, N), dtype=torch.uint8, device=Wf.device) if want_codes else None
     need = lib.jgq_gptq_quantize_workspace_bytes(K, N, block_size)
-    ws = _workspace(need)
+    ws = _workspace_for(need)
     check(lib.jgq_gptq_quantize(Wf.data_ptr(), L.data_ptr(), params['scale'].data_ptr(),
                                 params['zero'].data_ptr(), K, N, block_size, params['maxq'],
                                 Q.data_ptr(), _DT[out_dtype], _ptr(codes), ws.data_ptr(), need, _stream()))
@@ -262,12 +308,13 @@ def gptq(W, xs, block_size=128, actorder=False, damping=0.01, use_fp64=False, *,
     if Wd.dim() != 2:
         raise ValueError('gptq expects a 2-D weight (K, N)')
     orig_dtype = Wd.dtype if Wd.dtype in _DT else torch.float32
-    Wf = Wd.to(torch.float32, copy=True).contiguous()        # gptq.py:184 (private copy, updated in place)
+    Wf = _tmp('Wf', tuple(Wd.shape), torch.float32)           # gptq.py:184 (private copy, updated in place)
+    Wf.copy_(Wd)
     K, N = Wf.shape
     if K % block_size != 0:
         raise ValueError(f'K={K} must be a multiple of block_size={block_size}')
     params = _col_params(Wf, bits)                           # gptq.py:185 (before any fix-up)
-    h_status = torch.zeros(1, dtype=torch.int32, device=Wf.device)
+    h_status = _tmp('h_status', (1,), torch.int32, zero=True)
     if H is None:
         Hd, n = _accumulate_raw(xs, status=h_status)
         Hd = _finalize_H(Hd, n)                              # gptq.py:187
@@ -418,70 +465,101 @@ def gptq_many(jobs, block_size=128, actorder=False, damping=0.01, bits=4, pack=T
     each packed result (device->host, asynchronously).  Returns the list of results
     (QuantizedMatrix when `pack`, else ``(Q, params)``), valid after the function returns.
     """
+    global _ARENA
     jobs = list(jobs)
     if not jobs:
         return []
     device = _dev()
+    nw = max(1, int(streams))
+    key = (torch.cuda.current_device(), nw)
+    state = _arena_cache.get(key)
+    if state is None:
+        state = {'copier': torch.cuda.Stream(), 'workers': [torch.cuda.Stream() for _ in range(nw)],
+                 'arenas': [_Arena() for _ in range(nw)]}
+        _arena_cache[key] = state
+    copier, workers, arenas = state['copier'], state['workers'], state['arenas']
     main = torch.cuda.current_stream()
-    copier = torch.cuda.Stream()
-    workers = [torch.cuda.Stream() for _ in range(max(1, int(streams)))]
     start = main.record_event()
     copier.wait_event(start)
     for w in workers:
         w.wait_event(start)
+    done = [None] * nw               # completion event of the last job issued on each worker
 
-    def stage(job, consumer):
+    def stage(job, wi):
+        """Device copies of a job's inputs.  Host inputs are copied on the copy stream into the
+        worker's arena (after the worker's previous job, which used the same buffers, has finished)."""
         W, xs = job
+        arena = arenas[wi]
+        xs = list(xs)
+        w_host = not (isinstance(W, torch.Tensor) and W.is_cuda)
+        x_host = bool(xs) and all(not (isinstance(x, torch.Tensor) and x.is_cuda) for x in xs)
+        if not w_host and not x_host:
+            return W, [_to_dev(x) for x in xs], None
         with torch.cuda.stream(copier):
-            Wd = W if (isinstance(W, torch.Tensor) and W.is_cuda) else _to_dev(W)
-            xs = list(xs)
-            host = [x for x in xs if not (isinstance(x, torch.Tensor) and x.is_cuda)]
-            if host and len(host) == len(xs):
+            if done[wi] is not None:
+                copier.wait_event(done[wi])
+            Wd = W
+            if w_host:
+                Wt = W if isinstance(W, torch.Tensor) else torch.from_numpy(np.ascontiguousarray(W))
+                Wd = arena.get('Wstage', tuple(Wt.shape), Wt.dtype)
+                Wd.copy_(Wt, non_blocking=True)
+            xd = xs
+            if x_host:
                 ts = [x if isinstance(x, torch.Tensor) else torch.from_numpy(np.ascontiguousarray(x)) for x in xs]
                 K = ts[0].shape[-1]
                 if all(t.dtype == ts[0].dtype and t.shape[-1] == K for t in ts):
                     rows = [t.numel() // K for t in ts]
-                    buf = torch.empty((sum(rows), K), dtype=ts[0].dtype, device=device)
+                    buf = arena.get('Xstage', (sum(rows), K), ts[0].dtype)
                     xd, r0 = [], 0
                     for t, r in zip(ts, rows):
                         v = buf[r0:r0 + r]
                         v.copy_(t.reshape(r, K), non_blocking=True)
                         xd.append(v)
                         r0 += r
-                    buf.record_stream(consumer)
                 else:
-                    xd = [_to_dev(t) for t in ts]
+                    xd = [arena.get(f'Xstage{j}', tuple(t.shape), t.dtype) for j, t in enumerate(ts)]
+                    for v, t in zip(xd, ts):
+                        v.copy_(t, non_blocking=True)
             else:
                 xd = [_to_dev(x) for x in xs]
-            for t in [Wd] + xd:
-                if isinstance(t, torch.Tensor) and t.is_cuda:
-                    t.record_stream(consumer)
             ev = copier.record_event()
         return Wd, xd, ev
 
     results, deferred = [], []
-    nxt = stage(jobs[0], workers[0])
-    for i in range(len(jobs)):
-        Wd, xd, ev = nxt
-        if i + 1 < len(jobs):
-            nxt = stage(jobs[i + 1], workers[(i + 1) % len(workers)])
-        ws = workers[i % len(workers)]
-        with torch.cuda.stream(ws):
-            ws.wait_event(ev)
-            Q, params = gptq(Wd, xd, block_size=block_size, actorder=actorder, damping=damping, bits=bits,
-                             _defer=deferred)
-            res = pack_matrix(Q, params) if pack else (Q, params)
-            if out_host is not None and pack:
-                p, s, z = out_host[i]
-                p.copy_(res.int_weight, non_blocking=True)
-                s.copy_(res.scale, non_blocking=True)
-                z.copy_(res.zero, non_blocking=True)
-            for t in ((res.int_weight, res.scale, res.zero) if pack else (Q, params['scale'], params['zero'])):
-                t.record_stream(main)
-        results.append(res)
+    try:
+        nxt = stage(jobs[0], 0)
+        for i in range(len(jobs)):
+            Wd, xd, ev = nxt
+            wi = i % nw
+            ws = workers[wi]
+            with torch.cuda.stream(ws):
+                if ev is not None:
+                    ws.wait_event(ev)
+                _ARENA = arenas[wi]
+                try:
+                    Q, params = gptq(Wd, xd, block_size=block_size, actorder=actorder, damping=damping, bits=bits,
+                                     _defer=deferred)
+                finally:
+                    _ARENA = None
+                res = pack_matrix(Q, params) if pack else (Q.clone(), params)
+                if out_host is not None and pack:
+                    p, s, z = out_host[i]
+                    p.copy_(res.int_weight, non_blocking=True)
+                    s.copy_(res.scale, non_blocking=True)
+                    z.copy_(res.zero, non_blocking=True)
+                for t in ((res.int_weight, res.scale, res.zero) if pack else (res[0], params['scale'], params['zero'])):
+                    t.record_stream(main)
+                done[wi] = ws.record_event()
+            results.append(res)
+            if i + 1 < len(jobs):
+                nxt = stage(jobs[i + 1], (i + 1) % nw)
+    finally:
+        _ARENA = None
     for w in workers:
         main.wait_event(w.record_event())
     main.wait_event(copier.record_event())
-    if deferred:
-        _raise_status(int(torch.stack([d.to(device) for d in deferred]).max().item()))
+    st = int(torch.stack(deferred).max().item()) if deferred else 0      # synchronises with every worker
+    for a in arenas:
+        a.release()
+    _raise_status(st)
     return results
