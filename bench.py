@@ -477,7 +477,7 @@ def main():
     ap.add_argument('--impl', default='ours', choices=['ours', 'reference'])
     ap.add_argument('--layers', type=int, default=N_LAYERS, help='blocks to quantize (12 = the full workload)')
     ap.add_argument('--skip-matmul', action='store_true')
-    ap.add_argument('--streams', type=int, default=4, help='independent linears in flight (compute streams)')
+    ap.add_argument('--streams', type=int, default=8, help='independent linears in flight (compute streams)')
     ap.add_argument('--only-matmul', action='store_true', help='run only the packed-int4 matmul sweep')
     ap.add_argument('--matmul-shapes', default='', help='comma list of KxNxM cases for --only-matmul')
     ap.add_argument('--skip-cpu', action='store_true')

@@ -447,7 +447,7 @@ def unpack_matrix(weight, dtype=None):
 # --------------------------------------------------------------------------
 # many layers with host-resident inputs: copies overlap the previous layer's compute
 # --------------------------------------------------------------------------
-def gptq_many(jobs, block_size=128, actorder=False, damping=0.01, bits=4, pack=True, out_host=None, streams=4):
+def gptq_many(jobs, block_size=128, actorder=False, damping=0.01, bits=4, pack=True, out_host=None, streams=8):
     """Run ``gptq`` (and ``pack_matrix`` when `pack`) over a sequence of independent ``(W, xs)`` jobs.
 
     This is the loop the reference's interpreter runs layer by layer
