@@ -291,7 +291,11 @@ def run_ours(args):
     roofline = {'kernel': 'hessian_accum (H += X^T X, K=3072, n=65536, 16 batches)', 'bound': 'tensor',
                 'achieved': achieved_tf, 'peak': peak_tf, 'unit': 'TFLOP/s', 'frac': achieved_tf / peak_tf,
                 'peak_source': 'MEASURED_PEAKS.json bf16_tflops_sustained' if peaks else 'fallback 1.4 PFLOP/s sustained',
-                'launches_per_hessian': h_launches, 'ms_per_hessian': h_ms, 'traffic': None}
+                'launches_per_hessian': h_launches, 'ms_per_hessian': h_ms,
+                'note': 'time covers the bf16 split, the tcgen05 kernel and the slice reduction of one Hessian',
+                'traffic': 2.154e9,
+                'traffic_source': 'ncu dram__bytes_read+write of the hessian_umma_kernel launch for K=3072, n=65536 '
+                                  '(profiles/hessian_umma_k3072_gpt2_block.md)'}
 
     # ---- per-stage device time of one block (explains `value`; not part of it) ----
     stages = {}
