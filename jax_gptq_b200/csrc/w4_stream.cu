@@ -22,6 +22,16 @@
 #include <algorithm>
 #include <cstring>
 
+#ifndef JGQ_SV_BIAS
+#define JGQ_SV_BIAS 1
+#endif
+#ifndef JGQ_SV_PF
+#define JGQ_SV_PF 1
+#endif
+#ifndef JGQ_SV_MINB
+#define JGQ_SV_MINB 3
+#endif
+
 namespace jgq {
 
 constexpr int S_NST = 4;                      // stages in flight per CTA
@@ -38,6 +48,8 @@ struct StreamParams {
   int ncg, mtiles, spc;        // channel groups, token tiles, stages per (tile, group)
   int64_t S;                   // total stages = mtiles * ncg * spc
   int G;                       // CTAs (<= S)
+  uint32_t emask, emagic;      // nibble expansion: operand = (bytes & emask) | emagic (kept out of the
+                               // instruction stream so that the pair is one logic instruction)
   int maxc;                    // slice slots per group
 };
 
@@ -45,8 +57,68 @@ __device__ __forceinline__ int stream_cta_of(int64_t idx, int64_t S, int G) {
   return (int)(((idx + 1) * G + S - 1) / S) - 1;     // the c with c*S/G <= idx < (c+1)*S/G
 }
 
+// Nibble expansion without the subtraction: the operand holds OFFSET + code and the
+// constant is folded into the zero point at the end, out = scale * (acc - (zero + OFFSET) * sum_k x).
+// f16: byte (code << 4) under exponent 2^6 is 64 + code; bf16: byte (code) under exponent 2^7 is 128 + code.
+__device__ __forceinline__ uint4 lds128(uint32_t addr) {
+  uint4 v;
+  asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
+  return v;
+}
+
+template <typename CT> struct Biased;
+template <> struct Biased<__half> {
+  static constexpr float kOffset = 64.f;
+  __device__ static __forceinline__ uint32_t other(uint32_t w) { return w << 4; }          // low nibbles moved up
+  static constexpr uint32_t kMask = 0x00F000F0u, kMagic = 0x54005400u;
+  __device__ static __forceinline__ uint32_t pick(uint32_t w, uint32_t o, uint32_t sel, uint32_t mask, uint32_t magic) {
+    return (__byte_perm(o, w, sel) & mask) | magic;        // (even k, odd k) of byte sel
+  }
+};
+template <> struct Biased<__nv_bfloat16> {
+  static constexpr float kOffset = 128.f;
+  __device__ static __forceinline__ uint32_t other(uint32_t w) { return w >> 4; }          // high nibbles moved down
+  static constexpr uint32_t kMask = 0x000F000Fu, kMagic = 0x43004300u;
+  __device__ static __forceinline__ uint32_t pick(uint32_t w, uint32_t o, uint32_t sel, uint32_t mask, uint32_t magic) {
+    return (__byte_perm(w, o, sel) & mask) | magic;
+  }
+};
+
+// One 16-step with biased operands (same fragment roles as w4_step).
+template <typename CT, int NTOK, bool kSplitX>
+__device__ __forceinline__ void w4_step_biased(float (&acc)[NTOK][8][4], float (&accx)[NTOK][4], const uint4& r0,
+                                               const uint4& r1, const uint32_t (&xb)[NTOK][2],
+                                               const uint32_t (&xlo)[NTOK][2], uint32_t mask, uint32_t magic) {
+  const uint32_t w0[4] = {r0.x, r0.y, r0.z, r0.w};
+  const uint32_t w1[4] = {r1.x, r1.y, r1.z, r1.w};
+#pragma unroll
+  for (int wi = 0; wi < 2; ++wi) {
+    const uint32_t u0 = w0[wi], u0s = Biased<CT>::other(u0), v0 = w0[wi + 2], v0s = Biased<CT>::other(v0);
+    const uint32_t u1 = w1[wi], u1s = Biased<CT>::other(u1), v1 = w1[wi + 2], v1s = Biased<CT>::other(v1);
+#pragma unroll
+    for (int bi = 0; bi < 4; ++bi) {
+      const uint32_t sel = (uint32_t)bi | ((uint32_t)bi << 4) | ((uint32_t)(4 + bi) << 8) | ((uint32_t)(4 + bi) << 12);
+      const uint32_t a0 = Biased<CT>::pick(u0, u0s, sel, mask, magic);
+      const uint32_t a1 = Biased<CT>::pick(v0, v0s, sel, mask, magic);
+      const uint32_t a2 = Biased<CT>::pick(u1, u1s, sel, mask, magic);
+      const uint32_t a3 = Biased<CT>::pick(v1, v1s, sel, mask, magic);
+#pragma unroll
+      for (int t = 0; t < NTOK; ++t) {
+        mma_wx<CT>(acc[t][wi * 4 + bi], a0, a1, a2, a3, xb[t]);
+        if (kSplitX) mma_wx<CT>(acc[t][wi * 4 + bi], a0, a1, a2, a3, xlo[t]);
+      }
+    }
+  }
+  const uint32_t one = MmaType<CT>::ones();
+#pragma unroll
+  for (int t = 0; t < NTOK; ++t) {
+    mma_wx<CT>(accx[t], one, one, one, one, xb[t]);
+    if (kSplitX) mma_wx<CT>(accx[t], one, one, one, one, xlo[t]);
+  }
+}
+
 template <typename XT, typename CT, int NTOK, typename ZST>
-__global__ void __launch_bounds__(S_THREADS, NTOK == 1 ? 3 : 2)
+__global__ void __launch_bounds__(S_THREADS, NTOK == 1 ? JGQ_SV_MINB : 2)
 w4_stream_kernel(const __grid_constant__ CUtensorMap wmap, const StreamParams p) {
   using namespace umma;
   constexpr bool kSplitX = std::is_same<XT, float>::value;
@@ -83,16 +155,14 @@ w4_stream_kernel(const __grid_constant__ CUtensorMap wmap, const StreamParams p)
     // ===================== producer: one 16 KB box per stage =====================
     if (lane == 0) {
       int issued = 0;
+      int pg = (int)(idx_begin / p.spc), pst = (int)(idx_begin - (int64_t)pg * p.spc);
       for (int s = 0; s < nstage; ++s) {
         const int slot = s % S_NST;
         if (s >= S_NST && !mbar_wait(&empty_bar[slot], ((s / S_NST) & 1) ^ 1, abort_flag)) break;
-        const int64_t idx = idx_begin + s;
-        const int64_t gid = idx / p.spc;
-        const int st = (int)(idx - gid * p.spc);
-        const int cg = (int)(gid % p.ncg);
         mbar_expect_tx(&full_bar[slot], S_STAGE_BYTES);
-        tma_load_2d(ring + slot * S_STAGE_BYTES, &wmap, cg * WCOLS, st * S_ROWS, &full_bar[slot]);
+        tma_load_2d(ring + slot * S_STAGE_BYTES, &wmap, pg * WCOLS, pst * S_ROWS, &full_bar[slot]);
         issued = s + 1;
+        if (++pst == p.spc) { pst = 0; ++pg; }
       }
       if (*abort_flag) {
         for (int s = max(0, issued - S_NST); s < issued; ++s) {
@@ -120,73 +190,112 @@ w4_stream_kernel(const __grid_constant__ CUtensorMap wmap, const StreamParams p)
   };
   clear_acc();
 
+  // Activation fragments: lane (g, q) needs x[8t + g][16*step + 2q .. +1] and [.. + 8 + 2q .. +1].
+  // A warp owns steps warp, warp + 4, .. of every stage and loads all of a stage's fragments at once;
+  // 16-bit activations are fetched one stage ahead, so their latency never meets the arithmetic.
+  constexpr int UPS = S_STEPS / WWARPS;
+  const uint32_t ring_u32 = smem_u32(ring);
+  // byte rows 8*sl + q and 8*sl + q + 4: row & 7 is q and q + 4
+  const uint32_t off_a = q * WCOLS + ((g ^ q) << 4), off_b = (q + 4) * WCOLS + ((g ^ (q + 4)) << 4);
+  const int kwords = (int)(p.K / 2);          // 32-bit words per 16-bit activation row
+  const uint32_t* xrow[NTOK];
+  bool xok[NTOK];
+#pragma unroll
+  for (int t = 0; t < NTOK; ++t) {
+    const int64_t m = 8 * t + g;
+    xok[t] = !kSplitX && m < p.M;                // rows past M read row 0 and are zeroed by a select
+    xrow[t] = reinterpret_cast<const uint32_t*>(x) + (xok[t] ? m : 0) * (int64_t)kwords + q;
+  }
+  uint32_t xcur[UPS][NTOK][2], xnxt[UPS][NTOK][2], xlo[UPS][NTOK][2];
+  auto load_stage = [&](int st_, uint32_t (&dst)[UPS][NTOK][2]) {
+    const int wb = 8 * (st_ * S_STEPS + warp);
+    const bool inside = 8 * (st_ + 1) * S_STEPS <= kwords;
+    if (inside) {
+#pragma unroll
+      for (int u = 0; u < UPS; ++u)
+#pragma unroll
+        for (int t = 0; t < NTOK; ++t) {
+          const int w = wb + 8 * WWARPS * u;
+          const uint32_t v0 = __ldg(xrow[t] + w), v1 = __ldg(xrow[t] + w + 4);
+          dst[u][t][0] = xok[t] ? v0 : 0u;
+          dst[u][t][1] = xok[t] ? v1 : 0u;
+        }
+    } else {
+#pragma unroll
+      for (int u = 0; u < UPS; ++u)
+#pragma unroll
+        for (int t = 0; t < NTOK; ++t) {
+          const int w = wb + 8 * WWARPS * u;
+          dst[u][t][0] = (xok[t] && w + q < kwords) ? __ldg(xrow[t] + w) : 0u;
+          dst[u][t][1] = (xok[t] && w + 4 + q < kwords) ? __ldg(xrow[t] + w + 4) : 0u;
+        }
+    }
+  };
+
+  int gid = (int)(idx_begin / p.spc);                       // channel group of the current stage
+  int st = (int)(idx_begin - (int64_t)gid * p.spc);         // stage inside the group
+  if (JGQ_SV_PF == 2 && !kSplitX && nstage > 0) load_stage(st, xcur);
+#pragma unroll
+  for (int u = 0; u < UPS; ++u)
+#pragma unroll
+    for (int t = 0; t < NTOK; ++t) { xlo[u][t][0] = xlo[u][t][1] = 0u; xnxt[u][t][0] = xnxt[u][t][1] = 0u; }
+
   bool alive = true;      // false after a timed-out wait: keep walking the barriers, skip the work
   for (int s = 0; s < nstage; ++s) {
-    const int64_t idx = idx_begin + s;
-    const int64_t gid = idx / p.spc;
-    const int st = (int)(idx - gid * p.spc);
-    const int cg = (int)(gid % p.ncg), mtile = (int)(gid / p.ncg);
-    const int64_t m0 = (int64_t)mtile * ROWS;
+    const int cg = gid;
+    const int64_t m0 = 0;
+    const int st_next = (st + 1 == p.spc) ? 0 : st + 1;
 
     if (alive) {
       const int slot = s % S_NST;
+      if constexpr (kSplitX) {
+#pragma unroll
+        for (int u = 0; u < UPS; ++u)
+          load_xfrags<XT, NTOK>(x, 0, p.M, 16 * ((int64_t)st * S_STEPS + WWARPS * u + warp), p.K, g, q, xcur[u], xlo[u]);
+      } else if (JGQ_SV_PF == 1) {
+        load_stage(st, xcur);
+      } else if (s + 1 < nstage) {
+        load_stage(st_next, xnxt);
+      }
       alive = __all_sync(0xffffffffu, mbar_wait(&full_bar[slot], (s / S_NST) & 1, abort_flag));
       if (alive) {
-        const uint8_t* tile = ring + slot * S_STAGE_BYTES;
-        const int64_t step0 = (int64_t)st * S_STEPS;
-        // activation fragments: lane (g, q) needs x[m0 + 8t + g][16*step + 2q .. +1] and [.. + 8 + 2q .. +1]
-        uint32_t xb[NTOK][2], xlo[NTOK][2];
-        const uint32_t* xrow[NTOK];            // 16-bit activations: row pointer in 32-bit words, or null
-#pragma unroll
-        for (int t = 0; t < NTOK; ++t) {
-          const int64_t m = m0 + 8 * t + g;
-          xrow[t] = (!kSplitX && m < p.M) ? reinterpret_cast<const uint32_t*>(x) + (m * p.K) / 2 + q : nullptr;
-        }
-        const int kwords = (int)(p.K / 2);     // 32-bit words per activation row
-        auto fetch_x = [&](int64_t step) {
-          if (kSplitX) {
-            load_xfrags<XT, NTOK>(x, m0, p.M, 16 * step, p.K, g, q, xb, xlo);
-          } else {
-            const int w0 = (int)(8 * step);
-#pragma unroll
-            for (int t = 0; t < NTOK; ++t) {
-              xb[t][0] = (xrow[t] && w0 + q < kwords) ? __ldg(xrow[t] + w0) : 0u;
-              xb[t][1] = (xrow[t] && w0 + 4 + q < kwords) ? __ldg(xrow[t] + w0 + 4) : 0u;
-              xlo[t][0] = xlo[t][1] = 0u;
-            }
-          }
-        };
-        fetch_x(step0 + warp);
+        const uint32_t tile = ring_u32 + slot * S_STAGE_BYTES;
         // byte rows 8*sl + q and + 4 of step sl; 16-byte chunk g, swizzled by row & 7.  The next step's
         // two shared-memory loads are issued before the current step's arithmetic.
         auto tile_load = [&](int sl, uint4& a, uint4& b) {
-          const int ra = 8 * sl + q, rb = ra + 4;
-          a = *reinterpret_cast<const uint4*>(tile + ra * WCOLS + ((g ^ (ra & 7)) << 4));
-          b = *reinterpret_cast<const uint4*>(tile + rb * WCOLS + ((g ^ (rb & 7)) << 4));
+          a = lds128(tile + sl * (8 * WCOLS) + off_a);
+          b = lds128(tile + sl * (8 * WCOLS) + off_b);
         };
         uint4 n0, n1;
         tile_load(warp, n0, n1);
 #pragma unroll
-        for (int u = 0; u < S_STEPS / WWARPS; ++u) {
+        for (int u = 0; u < UPS; ++u) {
           const int sl = WWARPS * u + warp;                 // step inside the stage
-          uint32_t cb[NTOK][2], clo[NTOK][2];
-#pragma unroll
-          for (int t = 0; t < NTOK; ++t) { cb[t][0] = xb[t][0]; cb[t][1] = xb[t][1]; clo[t][0] = xlo[t][0]; clo[t][1] = xlo[t][1]; }
           const uint4 r0 = n0, r1 = n1;
-          if (u + 1 < S_STEPS / WWARPS) {
-            fetch_x(step0 + sl + WWARPS);
-            tile_load(sl + WWARPS, n0, n1);
-          }
+          if (u + 1 < UPS) tile_load(sl + WWARPS, n0, n1);
           // rows past the end of the matrix arrive as zeros (TMA fill) and their activations are zero too
-          w4_step<CT, NTOK, kSplitX>(acc, accx, r0, r1, cb, clo);
+#if JGQ_SV_BIAS
+          w4_step_biased<CT, NTOK, kSplitX>(acc, accx, r0, r1, xcur[u], xlo[u], p.emask, p.emagic);
+#else
+          w4_step<CT, NTOK, kSplitX>(acc, accx, r0, r1, xcur[u], xlo[u]);
+#endif
         }
         __syncwarp();
         if (lane == 0) mbar_arrive(&empty_bar[slot]);
       }
+      if constexpr (!kSplitX && JGQ_SV_PF == 2) {
+#pragma unroll
+        for (int u = 0; u < UPS; ++u)
+#pragma unroll
+          for (int t = 0; t < NTOK; ++t) { xcur[u][t][0] = xnxt[u][t][0]; xcur[u][t][1] = xnxt[u][t][1]; }
+      }
     }
+    const int st_now = st;
+    st = st_next;
+    if (st_next == 0) ++gid;
 
     // ---- flush when the (token tile, channel group) ends here ----
-    const bool last_of_group = (st == p.spc - 1) || (s == nstage - 1);
+    const bool last_of_group = (st_now == p.spc - 1) || (s == nstage - 1);
     if (!last_of_group) continue;
 
     // reduce the 4 consumer warps into warp 0
@@ -220,13 +329,13 @@ w4_stream_kernel(const __grid_constant__ CUtensorMap wmap, const StreamParams p)
     }
 
     if (warp == 0) {
-      const int first_c = stream_cta_of(gid * p.spc, p.S, p.G);
-      const int last_c = stream_cta_of((gid + 1) * p.spc - 1, p.S, p.G);
+      const int first_c = stream_cta_of((int64_t)cg * p.spc, p.S, p.G);
+      const int last_c = stream_cta_of((int64_t)(cg + 1) * p.spc - 1, p.S, p.G);
       const int ncontrib = last_c - first_c + 1;
       bool write_out = true;
       if (ncontrib > 1) {
         // publish this CTA's slice: [group][slot][token row][132]
-        float* slice = p.partials + (((int64_t)gid * p.maxc + (blockIdx.x - first_c)) * ROWS) * PSTRIDE;
+        float* slice = p.partials + (((int64_t)cg * p.maxc + (blockIdx.x - first_c)) * ROWS) * PSTRIDE;
 #pragma unroll
         for (int t = 0; t < NTOK; ++t)
 #pragma unroll
@@ -245,15 +354,15 @@ w4_stream_kernel(const __grid_constant__ CUtensorMap wmap, const StreamParams p)
         __syncwarp();
         int last = 0;
         if (lane == 0) {
-          const int old = atomicAdd(&p.tickets[gid], 1);
+          const int old = atomicAdd(&p.tickets[cg], 1);
           last = (old == ncontrib - 1);
-          if (last) p.tickets[gid] = 0;             // ready for the next launch
+          if (last) p.tickets[cg] = 0;             // ready for the next launch
         }
         last = __shfl_sync(0xffffffffu, last, 0);
         write_out = last != 0;
         if (write_out) {
           __threadfence();
-          const float* base = p.partials + ((int64_t)gid * p.maxc * ROWS) * PSTRIDE;
+          const float* base = p.partials + ((int64_t)cg * p.maxc * ROWS) * PSTRIDE;
 #pragma unroll
           for (int t = 0; t < NTOK; ++t)
 #pragma unroll
@@ -293,7 +402,7 @@ w4_stream_kernel(const __grid_constant__ CUtensorMap wmap, const StreamParams p)
         }
       }
       if (write_out) {
-        // out = scale * (acc - zero * sum_k x); lane (g, q): channels 16g..16g+15, tokens 8t + 2q, + 1
+        // out = scale * (acc - (zero + offset) * sum_k x); lane (g, q): channels 16g..16g+15, tokens 8t + 2q, + 1
         const float poison = (alive && !*abort_flag) ? 0.f : __int_as_float(0x7fc00000);
         const int64_t cbase = (int64_t)cg * WCOLS;
 #pragma unroll
@@ -302,7 +411,7 @@ w4_stream_kernel(const __grid_constant__ CUtensorMap wmap, const StreamParams p)
           for (int b = 0; b < 8; ++b) {
             const int64_t n = cbase + 16 * g + 8 * i + b;
             if (n >= p.N) continue;
-            const float sc = zs_to_f32<ZST>(p.scale, n), z = zs_to_f32<ZST>(p.zero, n);
+            const float sc = zs_to_f32<ZST>(p.scale, n), z = zs_to_f32<ZST>(p.zero, n) + (JGQ_SV_BIAS ? Biased<CT>::kOffset : 0.f);
 #pragma unroll
             for (int t = 0; t < NTOK; ++t)
 #pragma unroll
@@ -366,6 +475,8 @@ int launch_w4_stream(const StreamPlan& pl, const void* x, int x_dtype, const uin
   p.partials = (float*)((char*)ws + 4096);
   p.M = M; p.N = N; p.K = K;
   p.ncg = pl.ncg; p.mtiles = 1; p.spc = pl.spc; p.S = pl.S; p.G = pl.G; p.maxc = pl.maxc;
+  if (x_dtype == JGQ_F16) { p.emask = Biased<__half>::kMask; p.emagic = Biased<__half>::kMagic; }
+  else { p.emask = Biased<__nv_bfloat16>::kMask; p.emagic = Biased<__nv_bfloat16>::kMagic; }
   const bool zf = zs_dtype == JGQ_F32;
 #define JGQ_STREAM(XT, CT)                                                                        \
   if (pl.ntok == 1)                                                                               \
