@@ -8,6 +8,7 @@
 // a batch is split over CTAs; the slices are written to the workspace and summed
 // in a fixed order, so results do not depend on scheduling.
 #include "common.cuh"
+#include "hessian_plan.cuh"
 #include "sgemm.cuh"
 #include <algorithm>
 
@@ -68,12 +69,6 @@ static int hessian_splits(int64_t n, int64_t K) {
   if (s > 64) s = 64;
   return (int)std::max<int64_t>(1, s);
 }
-
-// tensor-core path (hessian_umma.cu)
-struct HessPlan { int use; int planes; int nseg; int S; int tokens_per_slice; size_t plane_bytes; size_t part_bytes; };
-HessPlan plan_hessian_umma(int64_t n, int64_t K, int x_dtype);
-int launch_hessian_umma(const HessPlan& pl, const void* X, int x_dtype, int64_t n, int64_t K, float* H, void* ws,
-                        int32_t* status, cudaStream_t s);
 
 static size_t simt_workspace_bytes(int64_t n, int64_t K, int x_dtype);
 

@@ -20,6 +20,7 @@
 // (one elected lane each, 4-stage mbarrier ring), warps 2-5 = epilogue
 // (TMEM -> registers -> global).
 #include "umma.cuh"
+#include "hessian_plan.cuh"
 #include <algorithm>
 #include <cstdlib>
 #include <cstring>
@@ -208,8 +209,6 @@ hessian_umma_kernel(const __grid_constant__ CUtensorMap map0, const __grid_const
 }
 
 // ------------------------------------------------------------------ host ----
-struct HessPlan { int use; int planes; int nseg; int S; int tokens_per_slice; size_t plane_bytes; size_t part_bytes; };
-
 static int hessian_path_override() {      // 0 = automatic, 1 = FFMA only, 2 = tensor path whenever legal
   static int v = -1;
   if (v < 0) {

@@ -27,6 +27,7 @@
 // are written to the workspace; the CTA that takes the last ticket of a
 // channel group adds the slices in slice order and writes the result.
 #include "w4_common.cuh"
+#include "w4_plans.cuh"
 #include <algorithm>
 #include <cstdlib>
 #include <cstring>
@@ -321,24 +322,6 @@ static int launch_tb(const void* x, const uint8_t* packed, const void* zero, con
   w4_tb_kernel<XT, ZST><<<grid, 256, 0, s>>>((const XT*)x, packed, zero, scale, (XT*)out, M, N, K);
   return check_launch("w4_matmul_tb");
 }
-
-// tensor-path forward kernel (w4_umma.cu)
-struct UmmaPlan {
-  int use; int NT; int planes; int raw_stages; int a_stages; int x_stages; int mtiles; int ncg; int ksplit; int stages_per_split; int tmem_cols;
-  size_t smem_bytes; size_t xsum_bytes; size_t plane_bytes; size_t part_bytes;
-};
-UmmaPlan plan_w4_umma(int64_t M, int64_t N, int64_t K, int x_dtype);
-size_t w4_umma_workspace_bytes(const UmmaPlan& pl);
-int launch_w4_umma(const UmmaPlan& pl, const void* x, int x_dtype, const uint8_t* packed, const void* zero,
-                   const void* scale, int zs_dtype, void* out, int64_t M, int64_t N, int64_t K, void* ws,
-                   cudaStream_t s);
-
-// persistent TMA-streamed decode kernel (w4_stream.cu)
-struct StreamPlan { int use; int ntok; int ncg; int spc; int64_t S; int G; int maxc; size_t part_bytes; };
-StreamPlan plan_w4_stream(int64_t M, int64_t N, int64_t K);
-int launch_w4_stream(const StreamPlan& pl, const void* x, int x_dtype, const uint8_t* packed, const void* zero,
-                     const void* scale, int zs_dtype, void* out, int64_t M, int64_t N, int64_t K, void* ws,
-                     cudaStream_t s);
 
 static int w4_path_override() {        // JGQ_W4_PATH=direct: direct-load decode kernel; =mma: no tcgen05 either
   static int v = -1;

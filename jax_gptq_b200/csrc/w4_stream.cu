@@ -1,52 +1,65 @@
-// Decode-sized packed-int4 forward matmul, TMA-streamed and persistent.
+// Decode-sized packed-int4 forward matmul (M <= 16), TMA-streamed and persistent.
 //
-// HBM-bound: what matters is the number of bytes in flight per SM.  Measured on B200, a
-// producer lane streaming 4 KB TMA boxes reaches about 3 TB/s, 16 KB boxes about 5 TB/s, so
-// the weights move in 128-byte-row x 128-channel boxes (16 KB = 16 contraction steps),
-// four of them in flight per CTA, three CTAs per SM.
+// The weights move in 128-byte-row x 128-channel boxes (16 KB = 16 contraction steps) written
+// with the 128-byte swizzle; every CTA keeps three of them in flight and up to four CTAs
+// (four warps each) share an SM.  A ring of such boxes alone streams at 6.3-6.5 TB/s on B200;
+// the kernel is bound by the integer / logic pipe that expands nibbles into MMA operands.
 //
-// The grid is one resident wave.  Work is the list of all stages, ordered by (token tile,
-// channel group, contraction position); CTA c owns the contiguous range
-// [c*S/G, (c+1)*S/G) of it, so every CTA streams the same number of bytes whatever N and K
-// are.  A CTA accumulates while it stays inside one channel group and flushes when the
-// group changes or its range ends: the four consumer warps are reduced through shared
-// memory, the slice goes to the workspace, and the CTA that draws the group's last ticket
-// adds the group's slices in CTA order and applies scale / zero.  No floating-point atomics.
+// There is no producer warp.  Thread 0 issues the first boxes; after that the warp that is the
+// last to finish with a slot (a shared-memory counter tells) issues the box three stages ahead
+// into it.  All four warps compute.
 //
-// Consumers use the same fragment mapping as the direct-load kernel (w4_matmul.cu): weights
-// are the 16-row MMA operand, lane (g, q) owns channels 16g..16g+15 and byte rows q, q+4 of
-// a step.  The boxes are written with the 128-byte swizzle, so the four byte rows a quarter
-// warp reads land in different banks.
+// Nibble expansion is two instructions per operand register: a byte permute that puts the low
+// and the high nibble of one byte into the two halves, and one logic operation (and-mask,
+// or-exponent, both constants held as kernel parameters).  The operand then reads
+// OFFSET + code (64 for f16, 128 for bf16); the offset is folded into the zero point,
+// out = scale * (acc - (zero + OFFSET) * sum_k x), with sum_k x from an MMA against ones.
+//
+// The grid is one resident wave.  Work is the list of all stages, ordered by (channel group,
+// contraction position); CTA c owns the contiguous range [c*S/G, (c+1)*S/G) of it, so every
+// CTA streams the same number of bytes whatever N and K are.  A CTA accumulates while it
+// stays inside one channel group and flushes when the group changes or its range ends: the
+// warps park their fragments in shared memory, thread c adds up channel c, the slice goes to
+// the workspace, and the CTA that draws the group's last ticket adds the group's slices in
+// CTA order and applies scale / zero.  No floating-point atomics: results are deterministic.
+//
+// Fragment mapping: weights are the 16-row MMA operand, lane (g, q) owns channels
+// 16g..16g+15 and byte rows q, q+4 of a step; the swizzle spreads the byte rows a quarter
+// warp reads over different banks.
+//
+// Building with -DJGQ_SV_TRACE adds per-CTA timestamps (entry, first box, last stage, exit)
+// and an extra exported function that copies them out; the library proper never defines it.
 #include "w4_common.cuh"
+#include "w4_plans.cuh"
 #include "umma.cuh"
 #include <algorithm>
 #include <cstring>
 
-#ifndef JGQ_SV_BIAS
-#define JGQ_SV_BIAS 1
-#endif
-#ifndef JGQ_SV_PF
-#define JGQ_SV_PF 1
-#endif
-#ifndef JGQ_SV_MINB
-#define JGQ_SV_MINB 3
-#endif
 
 namespace jgq {
 
-constexpr int S_NST = 4;                      // stages in flight per CTA
+#ifdef JGQ_SV_TRACE
+__device__ unsigned long long g_trace[8 * 1024];
+__device__ __forceinline__ unsigned long long gtime() { unsigned long long t; asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t)); return t; }
+#define TRACE(i) do { if (threadIdx.x == 0 && blockIdx.x < 1024) { g_trace[8 * blockIdx.x + (i)] = gtime(); if ((i) == 0) { unsigned sm; asm volatile("mov.u32 %0, %smid;" : "=r"(sm)); g_trace[8 * blockIdx.x + 4] = sm; } } } while (0)
+#else
+#define TRACE(i) do {} while (0)
+#endif
+
+constexpr int S_NST = 3;                      // stages in flight per CTA
 constexpr int S_STEPS = 16;                   // contraction steps (8 byte rows each) per stage
 constexpr int S_ROWS = 8 * S_STEPS;           // byte rows per stage
 constexpr int S_STAGE_BYTES = S_ROWS * WCOLS; // 16 KB
 constexpr int S_RING_BYTES = S_NST * S_STAGE_BYTES + 1024;
-constexpr int S_THREADS = (WWARPS + 1) * 32;
+constexpr int S_THREADS = WWARPS * 32;
+constexpr int S_CTAS1 = 4, S_CTAS2 = 3;       // CTAs per SM the register budget is set for (8 / 16 token rows)
 
 struct StreamParams {
   const void* x; const void* zero; const void* scale; void* out;
   float* partials; int* tickets;
   int64_t M, N, K;
-  int ncg, mtiles, spc;        // channel groups, token tiles, stages per (tile, group)
-  int64_t S;                   // total stages = mtiles * ncg * spc
+  int ncg, mtiles, spc;        // channel groups, token tiles (always 1), stages per group
+  int64_t S;                   // total stages = ncg * spc
   int G;                       // CTAs (<= S)
   uint32_t emask, emagic;      // nibble expansion: operand = (bytes & emask) | emagic (kept out of the
                                // instruction stream so that the pair is one logic instruction)
@@ -118,62 +131,54 @@ __device__ __forceinline__ void w4_step_biased(float (&acc)[NTOK][8][4], float (
 }
 
 template <typename XT, typename CT, int NTOK, typename ZST>
-__global__ void __launch_bounds__(S_THREADS, NTOK == 1 ? JGQ_SV_MINB : 2)
+__global__ void __launch_bounds__(S_THREADS, NTOK == 1 ? S_CTAS1 : S_CTAS2)
 w4_stream_kernel(const __grid_constant__ CUtensorMap wmap, const StreamParams p) {
   using namespace umma;
   constexpr bool kSplitX = std::is_same<XT, float>::value;
   constexpr int ROWS = 8 * NTOK;
   extern __shared__ uint8_t ring_raw[];
   uint8_t* ring = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(ring_raw) + 1023) & ~uintptr_t(1023));
-  __shared__ __align__(16) float red[ROWS][PSTRIDE];
   __shared__ __align__(8) uint64_t full_bar[S_NST];
-  __shared__ __align__(8) uint64_t empty_bar[S_NST];
+  __shared__ int issued[S_NST];        // last stage whose box was issued into the slot (-1: none)
+  __shared__ int done[S_NST];          // consumer warps that have finished with the slot's current stage
   __shared__ int s_abort;
   __shared__ int s_last;
+
+  // fragments are parked here for the flush: [warp][token row < rows][132]
+  float* red = reinterpret_cast<float*>(ring + S_NST * S_STAGE_BYTES);
+  const int rows = (int)(p.M < ROWS ? p.M : ROWS);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, q = lane & 3;
   const XT* __restrict__ x = reinterpret_cast<const XT*>(p.x);
   XT* __restrict__ out = reinterpret_cast<XT*>(p.out);
-  const int64_t KB = p.K / 2;
-  const int64_t total_steps = (KB + 7) / 8;
   const int64_t idx_begin = ((int64_t)blockIdx.x * p.S) / p.G;
   const int64_t idx_end = ((int64_t)(blockIdx.x + 1) * p.S) / p.G;
   const int nstage = (int)(idx_end - idx_begin);
   volatile int* abort_flag = &s_abort;
+  const int g_begin = (int)(idx_begin / p.spc);                       // channel group of the first stage
+  const int st_begin = (int)(idx_begin - (int64_t)g_begin * p.spc);   // and its position inside the group
 
+  // Stage j of this CTA (j counted from its first) is the box at (group, position) below.  There is no
+  // producer warp: the first S_NST boxes are issued here, and afterwards the warp that is last to
+  // finish with a slot (a shared-memory counter tells) issues the box S_NST stages ahead into it.
+  auto issue_stage = [&](int j) {
+    const int lin = st_begin + j;
+    const int gg = g_begin + lin / p.spc, ss = lin % p.spc;
+    const int slot = j % S_NST;
+    issued[slot] = j;
+    mbar_expect_tx(&full_bar[slot], S_STAGE_BYTES);
+    tma_load_2d(ring + slot * S_STAGE_BYTES, &wmap, gg * WCOLS, ss * S_ROWS, &full_bar[slot]);
+  };
+  TRACE(0);
   if (threadIdx.x == 0) {
-    for (int i = 0; i < S_NST; ++i) { mbar_init(&full_bar[i], 1); mbar_init(&empty_bar[i], WWARPS); }
+    for (int i = 0; i < S_NST; ++i) { mbar_init(&full_bar[i], 1); done[i] = 0; issued[i] = -1; }
     s_abort = 0;
-    s_last = 0;
     fence_barrier_init();
     prefetch_tensormap(&wmap);
+    for (int j = 0; j < S_NST && j < nstage; ++j) issue_stage(j);
   }
   __syncthreads();
-
-  if (warp == WWARPS) {
-    // ===================== producer: one 16 KB box per stage =====================
-    if (lane == 0) {
-      int issued = 0;
-      int pg = (int)(idx_begin / p.spc), pst = (int)(idx_begin - (int64_t)pg * p.spc);
-      for (int s = 0; s < nstage; ++s) {
-        const int slot = s % S_NST;
-        if (s >= S_NST && !mbar_wait(&empty_bar[slot], ((s / S_NST) & 1) ^ 1, abort_flag)) break;
-        mbar_expect_tx(&full_bar[slot], S_STAGE_BYTES);
-        tma_load_2d(ring + slot * S_STAGE_BYTES, &wmap, pg * WCOLS, pst * S_ROWS, &full_bar[slot]);
-        issued = s + 1;
-        if (++pst == p.spc) { pst = 0; ++pg; }
-      }
-      if (*abort_flag) {
-        for (int s = max(0, issued - S_NST); s < issued; ++s) {
-          const long long t0 = clock64();
-          while (!mbar_try_wait(&full_bar[s % S_NST], (s / S_NST) & 1) && clock64() - t0 < 20000000LL) {}
-        }
-      }
-    }
-  }
-
-  if (warp == WWARPS) return;      // consumers synchronise among themselves with a named barrier
 
   float acc[NTOK][8][4];
   float accx[NTOK][4];
@@ -191,8 +196,8 @@ w4_stream_kernel(const __grid_constant__ CUtensorMap wmap, const StreamParams p)
   clear_acc();
 
   // Activation fragments: lane (g, q) needs x[8t + g][16*step + 2q .. +1] and [.. + 8 + 2q .. +1].
-  // A warp owns steps warp, warp + 4, .. of every stage and loads all of a stage's fragments at once;
-  // 16-bit activations are fetched one stage ahead, so their latency never meets the arithmetic.
+  // A warp owns steps warp, warp + 4, .. of every stage and loads all of a stage's fragments at once,
+  // before it waits for the stage's box.
   constexpr int UPS = S_STEPS / WWARPS;
   const uint32_t ring_u32 = smem_u32(ring);
   // byte rows 8*sl + q and 8*sl + q + 4: row & 7 is q and q + 4
@@ -206,7 +211,7 @@ w4_stream_kernel(const __grid_constant__ CUtensorMap wmap, const StreamParams p)
     xok[t] = !kSplitX && m < p.M;                // rows past M read row 0 and are zeroed by a select
     xrow[t] = reinterpret_cast<const uint32_t*>(x) + (xok[t] ? m : 0) * (int64_t)kwords + q;
   }
-  uint32_t xcur[UPS][NTOK][2], xnxt[UPS][NTOK][2], xlo[UPS][NTOK][2];
+  uint32_t xcur[UPS][NTOK][2], xlo[UPS][NTOK][2];
   auto load_stage = [&](int st_, uint32_t (&dst)[UPS][NTOK][2]) {
     const int wb = 8 * (st_ * S_STEPS + warp);
     const bool inside = 8 * (st_ + 1) * S_STEPS <= kwords;
@@ -232,13 +237,12 @@ w4_stream_kernel(const __grid_constant__ CUtensorMap wmap, const StreamParams p)
     }
   };
 
-  int gid = (int)(idx_begin / p.spc);                       // channel group of the current stage
-  int st = (int)(idx_begin - (int64_t)gid * p.spc);         // stage inside the group
-  if (JGQ_SV_PF == 2 && !kSplitX && nstage > 0) load_stage(st, xcur);
+  int gid = g_begin;                       // channel group of the current stage
+  int st = st_begin;                       // stage inside the group
 #pragma unroll
   for (int u = 0; u < UPS; ++u)
 #pragma unroll
-    for (int t = 0; t < NTOK; ++t) { xlo[u][t][0] = xlo[u][t][1] = 0u; xnxt[u][t][0] = xnxt[u][t][1] = 0u; }
+    for (int t = 0; t < NTOK; ++t) xlo[u][t][0] = xlo[u][t][1] = 0u;
 
   bool alive = true;      // false after a timed-out wait: keep walking the barriers, skip the work
   for (int s = 0; s < nstage; ++s) {
@@ -252,12 +256,11 @@ w4_stream_kernel(const __grid_constant__ CUtensorMap wmap, const StreamParams p)
 #pragma unroll
         for (int u = 0; u < UPS; ++u)
           load_xfrags<XT, NTOK>(x, 0, p.M, 16 * ((int64_t)st * S_STEPS + WWARPS * u + warp), p.K, g, q, xcur[u], xlo[u]);
-      } else if (JGQ_SV_PF == 1) {
+      } else {
         load_stage(st, xcur);
-      } else if (s + 1 < nstage) {
-        load_stage(st_next, xnxt);
       }
       alive = __all_sync(0xffffffffu, mbar_wait(&full_bar[slot], (s / S_NST) & 1, abort_flag));
+      if (s == 0) TRACE(1);
       if (alive) {
         const uint32_t tile = ring_u32 + slot * S_STAGE_BYTES;
         // byte rows 8*sl + q and + 4 of step sl; 16-byte chunk g, swizzled by row & 7.  The next step's
@@ -274,20 +277,20 @@ w4_stream_kernel(const __grid_constant__ CUtensorMap wmap, const StreamParams p)
           const uint4 r0 = n0, r1 = n1;
           if (u + 1 < UPS) tile_load(sl + WWARPS, n0, n1);
           // rows past the end of the matrix arrive as zeros (TMA fill) and their activations are zero too
-#if JGQ_SV_BIAS
           w4_step_biased<CT, NTOK, kSplitX>(acc, accx, r0, r1, xcur[u], xlo[u], p.emask, p.emagic);
-#else
-          w4_step<CT, NTOK, kSplitX>(acc, accx, r0, r1, xcur[u], xlo[u]);
-#endif
         }
         __syncwarp();
-        if (lane == 0) mbar_arrive(&empty_bar[slot]);
-      }
-      if constexpr (!kSplitX && JGQ_SV_PF == 2) {
-#pragma unroll
-        for (int u = 0; u < UPS; ++u)
-#pragma unroll
-          for (int t = 0; t < NTOK; ++t) { xcur[u][t][0] = xnxt[u][t][0]; xcur[u][t][1] = xnxt[u][t][1]; }
+        if (lane == 0) {
+          int old;
+          asm volatile("atom.acq_rel.cta.shared.add.u32 %0, [%1], 1;" : "=r"(old) : "r"(smem_u32(&done[slot])) : "memory");
+          if (old == WWARPS - 1) {               // every warp has read the slot: refill it
+            done[slot] = 0;
+            if (s + S_NST < nstage) {
+              asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+              issue_stage(s + S_NST);
+            }
+          }
+        }
       }
     }
     const int st_now = st;
@@ -298,136 +301,106 @@ w4_stream_kernel(const __grid_constant__ CUtensorMap wmap, const StreamParams p)
     const bool last_of_group = (st_now == p.spc - 1) || (s == nstage - 1);
     if (!last_of_group) continue;
 
-    // reduce the 4 consumer warps into warp 0
-    // fragment element (t, b, i): token 8t + 2q + (i & 1), channel 16g + b + 8 * (i >> 1)
-    for (int w = 1; w < WWARPS; ++w) {
-      if (warp == w) {
+    if (s == nstage - 1) TRACE(2);
+    // Every warp parks its fragment in shared memory; then thread c owns channel c of the group for
+    // all token rows.  Fragment element (t, b, i): token 8t + 2q + (i & 1), channel 16g + b + 8 * (i >> 1).
 #pragma unroll
-        for (int t = 0; t < NTOK; ++t) {
+    for (int t = 0; t < NTOK; ++t) {
 #pragma unroll
-          for (int b = 0; b < 8; ++b)
+      for (int b = 0; b < 8; ++b)
 #pragma unroll
-            for (int i = 0; i < 4; ++i)
-              red[8 * t + 2 * q + (i & 1)][16 * g + b + 8 * (i >> 1)] = acc[t][b][i];
-          if (g == 0) { red[8 * t + 2 * q][WCOLS] = accx[t][0]; red[8 * t + 2 * q + 1][WCOLS] = accx[t][1]; }
+        for (int i = 0; i < 4; ++i) {
+          const int r = 8 * t + 2 * q + (i & 1);
+          if (r < rows) red[(warp * rows + r) * PSTRIDE + 16 * g + b + 8 * (i >> 1)] = acc[t][b][i];
+        }
+      if (g == 0) {
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          const int r = 8 * t + 2 * q + h;
+          if (r < rows) red[(warp * rows + r) * PSTRIDE + WCOLS] = accx[t][h];
         }
       }
-      asm volatile("bar.sync 1, 128;" ::: "memory");
-      if (warp == 0) {
-#pragma unroll
-        for (int t = 0; t < NTOK; ++t) {
-#pragma unroll
-          for (int b = 0; b < 8; ++b)
-#pragma unroll
-            for (int i = 0; i < 4; ++i)
-              acc[t][b][i] += red[8 * t + 2 * q + (i & 1)][16 * g + b + 8 * (i >> 1)];
-          accx[t][0] += red[8 * t + 2 * q][WCOLS];
-          accx[t][1] += red[8 * t + 2 * q + 1][WCOLS];
-        }
-      }
-      asm volatile("bar.sync 1, 128;" ::: "memory");
     }
-
-    if (warp == 0) {
+    __syncthreads();
+    {
+      const int c = threadIdx.x;                      // channel inside the group
+      const int64_t n = (int64_t)cg * WCOLS + c;
+      // scale and zero are fetched before the ticket so that their latency overlaps the exchange
+      float sc = 0.f, z = 0.f;
+      if (n < p.N) { sc = zs_to_f32<ZST>(p.scale, n); z = zs_to_f32<ZST>(p.zero, n) + Biased<CT>::kOffset; }
+      float v[ROWS], xs[ROWS];
+#pragma unroll
+      for (int r = 0; r < ROWS; ++r) {
+        v[r] = 0.f; xs[r] = 0.f;
+        if (r < rows) {
+#pragma unroll
+          for (int w = 0; w < WWARPS; ++w) { v[r] += red[(w * rows + r) * PSTRIDE + c]; xs[r] += red[(w * rows + r) * PSTRIDE + WCOLS]; }
+        }
+      }
       const int first_c = stream_cta_of((int64_t)cg * p.spc, p.S, p.G);
       const int last_c = stream_cta_of((int64_t)(cg + 1) * p.spc - 1, p.S, p.G);
       const int ncontrib = last_c - first_c + 1;
       bool write_out = true;
       if (ncontrib > 1) {
-        // publish this CTA's slice: [group][slot][token row][132]
+        // publish this CTA's slice [group][slot][token row][132] and draw a ticket
         float* slice = p.partials + (((int64_t)cg * p.maxc + (blockIdx.x - first_c)) * ROWS) * PSTRIDE;
 #pragma unroll
-        for (int t = 0; t < NTOK; ++t)
-#pragma unroll
-          for (int h = 0; h < 2; ++h) {
-            float* dst = slice + (8 * t + 2 * q + h) * PSTRIDE + 16 * g;
-#pragma unroll
-            for (int i = 0; i < 2; ++i)
-#pragma unroll
-              for (int b4 = 0; b4 < 2; ++b4)
-                *reinterpret_cast<float4*>(dst + 8 * i + 4 * b4) =
-                    make_float4(acc[t][4 * b4 + 0][2 * i + h], acc[t][4 * b4 + 1][2 * i + h],
-                                acc[t][4 * b4 + 2][2 * i + h], acc[t][4 * b4 + 3][2 * i + h]);
-            if (g == 0) dst[WCOLS - 16 * g] = accx[t][h];
+        for (int r = 0; r < ROWS; ++r)
+          if (r < rows) {
+            slice[r * PSTRIDE + c] = v[r];
+            if (c == 0) slice[r * PSTRIDE + WCOLS] = xs[r];
           }
         __threadfence();
-        __syncwarp();
-        int last = 0;
-        if (lane == 0) {
+        __syncthreads();
+        if (threadIdx.x == 0) {
           const int old = atomicAdd(&p.tickets[cg], 1);
-          last = (old == ncontrib - 1);
-          if (last) p.tickets[cg] = 0;             // ready for the next launch
+          const int last = (old == ncontrib - 1);
+          if (last) p.tickets[cg] = 0;               // ready for the next launch
+          s_last = last;
         }
-        last = __shfl_sync(0xffffffffu, last, 0);
-        write_out = last != 0;
+        __syncthreads();
+        write_out = s_last != 0;
         if (write_out) {
           __threadfence();
           const float* base = p.partials + ((int64_t)cg * p.maxc * ROWS) * PSTRIDE;
 #pragma unroll
-          for (int t = 0; t < NTOK; ++t)
+          for (int r = 0; r < ROWS; ++r) { v[r] = 0.f; xs[r] = 0.f; }
+          for (int zc = 0; zc < ncontrib; ++zc)       // slices are added in CTA order: deterministic
 #pragma unroll
-            for (int h = 0; h < 2; ++h) {
-#pragma unroll
-              for (int b = 0; b < 8; ++b) { acc[t][b][h] = 0.f; acc[t][b][2 + h] = 0.f; }
-              float xs = 0.f;
-              for (int z0 = 0; z0 < ncontrib; z0 += 2) {
-                float4 v[2][4];
-                float xv[2];
-#pragma unroll
-                for (int zz = 0; zz < 2; ++zz) {
-                  if (z0 + zz < ncontrib) {
-                    const float* src = base + ((int64_t)(z0 + zz) * ROWS + 8 * t + 2 * q + h) * PSTRIDE;
-#pragma unroll
-                    for (int j = 0; j < 4; ++j) v[zz][j] = __ldcg(reinterpret_cast<const float4*>(src + 16 * g + 4 * j));
-                    xv[zz] = __ldcg(src + WCOLS);
-                  }
-                }
-#pragma unroll
-                for (int zz = 0; zz < 2; ++zz) {
-                  if (z0 + zz < ncontrib) {
-#pragma unroll
-                    for (int i = 0; i < 2; ++i)
-#pragma unroll
-                      for (int b4 = 0; b4 < 2; ++b4) {
-                        const float4 w = v[zz][2 * i + b4];
-                        acc[t][4 * b4 + 0][2 * i + h] += w.x; acc[t][4 * b4 + 1][2 * i + h] += w.y;
-                        acc[t][4 * b4 + 2][2 * i + h] += w.z; acc[t][4 * b4 + 3][2 * i + h] += w.w;
-                      }
-                    xs += xv[zz];
-                  }
-                }
+            for (int r = 0; r < ROWS; ++r)
+              if (r < rows) {
+                v[r] += __ldcg(base + ((int64_t)zc * ROWS + r) * PSTRIDE + c);
+                xs[r] += __ldcg(base + ((int64_t)zc * ROWS + r) * PSTRIDE + WCOLS);
               }
-              accx[t][h] = xs;
-            }
         }
       }
-      if (write_out) {
-        // out = scale * (acc - (zero + offset) * sum_k x); lane (g, q): channels 16g..16g+15, tokens 8t + 2q, + 1
+      if (write_out && n < p.N) {
+        // out = scale * (acc - (zero + offset) * sum_k x)
         const float poison = (alive && !*abort_flag) ? 0.f : __int_as_float(0x7fc00000);
-        const int64_t cbase = (int64_t)cg * WCOLS;
 #pragma unroll
-        for (int i = 0; i < 2; ++i)
-#pragma unroll
-          for (int b = 0; b < 8; ++b) {
-            const int64_t n = cbase + 16 * g + 8 * i + b;
-            if (n >= p.N) continue;
-            const float sc = zs_to_f32<ZST>(p.scale, n), z = zs_to_f32<ZST>(p.zero, n) + (JGQ_SV_BIAS ? Biased<CT>::kOffset : 0.f);
-#pragma unroll
-            for (int t = 0; t < NTOK; ++t)
-#pragma unroll
-              for (int h = 0; h < 2; ++h) {
-                const int64_t m = m0 + 8 * t + 2 * q + h;
-                if (m < p.M) out[m * p.N + n] = from_f32<XT>(sc * (acc[t][b][2 * i + h] - z * accx[t][h]) + poison);
-              }
-          }
+        for (int r = 0; r < ROWS; ++r)
+          if (r < rows) out[(int64_t)r * p.N + n] = from_f32<XT>(sc * (v[r] - z * xs[r]) + poison);
       }
     }
+    __syncthreads();           // the parking area is reused by the next flush
     clear_acc();
+  }
+
+  TRACE(3);
+  // After a timed-out wait some boxes may still be in flight: give them a bounded time to land before
+  // the CTA's shared memory is released.
+  __syncthreads();
+  if (threadIdx.x == 0 && *abort_flag) {
+    for (int i = 0; i < S_NST; ++i) {
+      const int j = issued[i];
+      if (j < 0) continue;
+      const long long t0 = clock64();
+      while (!mbar_try_wait(&full_bar[i], (j / S_NST) & 1) && clock64() - t0 < 20000000LL) {}
+    }
   }
 }
 
 // ------------------------------------------------------------------ host ----
-struct StreamPlan { int use; int ntok; int ncg; int spc; int64_t S; int G; int maxc; size_t part_bytes; };
 
 StreamPlan plan_w4_stream(int64_t M, int64_t N, int64_t K) {
   StreamPlan pl;
@@ -440,7 +413,11 @@ StreamPlan plan_w4_stream(int64_t M, int64_t N, int64_t K) {
   const int64_t total_steps = cdiv(K / 2, 8);
   pl.spc = (int)cdiv(total_steps, S_STEPS);
   pl.S = (int64_t)pl.ncg * pl.spc;
-  pl.G = (int)std::min<int64_t>((pl.ntok == 1 ? 3 : 2) * (int64_t)sm_count(), std::max<int64_t>(1, pl.S / 2));   // one resident wave, >= 2 stages each
+  // CTAs per SM: the register cap of the launch bounds, or what fits in 227 KB of shared memory
+  pl.smem_bytes = S_RING_BYTES + (int)(WWARPS * M * PSTRIDE * sizeof(float));
+  const int by_smem = (227 * 1024) / (pl.smem_bytes + 1024 + 256);
+  const int per_sm = std::max(1, std::min(pl.ntok == 1 ? S_CTAS1 : S_CTAS2, by_smem));
+  pl.G = (int)std::min<int64_t>(per_sm * (int64_t)sm_count(), std::max<int64_t>(1, pl.S / 2));   // one resident wave, >= 2 stages each
   const int64_t per = pl.S / pl.G;                    // every CTA streams per or per + 1 stages
   pl.maxc = (int)cdiv(pl.spc, per) + 1;
   pl.part_bytes = align_up((size_t)pl.ncg * pl.maxc * 8 * pl.ntok * PSTRIDE * sizeof(float), 256);
@@ -454,11 +431,12 @@ static int launch_stream_inst(const StreamPlan& pl, const StreamParams& p, const
   int dev = 0;
   cudaGetDevice(&dev);
   if (dev >= 0 && dev < 64 && !attr_set[dev]) {
-    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, S_RING_BYTES) != cudaSuccess)
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, S_RING_BYTES + WWARPS * 8 * NTOK * PSTRIDE * (int)sizeof(float)) != cudaSuccess)
       return fail(JGQ_ERR_CUDA, "w4_matmul: cannot raise the dynamic shared memory limit");
+    cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout, 100);   // a hint: all of it as shared memory
     attr_set[dev] = true;
   }
-  kern<<<(unsigned)pl.G, S_THREADS, S_RING_BYTES, s>>>(wmap, p);
+  kern<<<(unsigned)pl.G, S_THREADS, pl.smem_bytes, s>>>(wmap, p);
   return check_launch("w4_stream");
 }
 
@@ -487,5 +465,11 @@ int launch_w4_stream(const StreamPlan& pl, const void* x, int x_dtype, const uin
   JGQ_STREAM(__nv_bfloat16, __nv_bfloat16);
 #undef JGQ_STREAM
 }
+
+#ifdef JGQ_SV_TRACE
+extern "C" int jgq_dbg_trace(unsigned long long* host) {
+  return (int)cudaMemcpyFromSymbol(host, g_trace, sizeof(unsigned long long) * 8 * 1024);
+}
+#endif
 
 }  // namespace jgq

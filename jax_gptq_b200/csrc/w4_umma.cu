@@ -20,6 +20,7 @@
 // for the expansion, everything else on the tensor pipe); at large M it is tensor-bound.
 #include "umma.cuh"
 #include "w4_common.cuh"
+#include "w4_plans.cuh"
 #include <algorithm>
 #include <cstring>
 
@@ -338,10 +339,6 @@ w4_umma_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__
 }
 
 // ------------------------------------------------------------------ host ----
-struct UmmaPlan {
-  int use; int NT; int planes; int raw_stages; int a_stages; int x_stages; int mtiles; int ncg; int ksplit; int stages_per_split; int tmem_cols;
-  size_t smem_bytes; size_t xsum_bytes; size_t plane_bytes; size_t part_bytes;
-};
 
 UmmaPlan plan_w4_umma(int64_t M, int64_t N, int64_t K, int x_dtype) {
   UmmaPlan pl;
