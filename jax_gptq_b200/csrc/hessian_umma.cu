@@ -10,14 +10,18 @@
 // same fp32 TMEM accumulator (the dropped b2^T b2 term is O(2^-18)).  bf16 / fp16
 // batches are used as they are, one MMA per step, products exact.
 //
-// Work decomposition: H is symmetric, only blocks on or below the diagonal are
-// produced.  A CTA owns a 128-row panel x a segment of up to 256 columns (one
-// 128 x 256 fp32 accumulator = 256 TMEM columns) and a slice of the token range.
-// Token slices exist only to fill the 148 SMs evenly; their results go to
-// separate buffers that are summed in slice order (no floating-point atomics).
+// Work decomposition: H is symmetric, only 256 x 256 tiles on or below the diagonal are
+// produced.  A CTA owns one tile and a slice of the token range: two 128 x 256 fp32
+// accumulators (all 512 TMEM columns) share the B operand, so a 16-token step moves
+// 512 feature columns through L2 -> shared memory for 2 x 128 x 256 x 16 MACs per term -
+// a third fewer bytes per flop than one 128-row accumulator, which was operand-bound.
+// On diagonal tiles B is the panel itself (nothing extra is loaded) and the upper
+// accumulator only covers the first 128 columns.  Token slices exist only to fill the
+// 148 SMs evenly; their results go to separate buffers that are summed in slice order
+// (no floating-point atomics).
 //
 // Roles inside a CTA (192 threads): warp 0 = TMA producer, warp 1 = MMA issuer
-// (one elected lane each, 4-stage mbarrier ring), warps 2-5 = epilogue
+// (one elected lane each, 3-stage mbarrier ring of 64 KB stages), warps 2-5 = epilogue
 // (TMEM -> registers -> global).
 #include "umma.cuh"
 #include "hessian_plan.cuh"
@@ -27,14 +31,23 @@
 
 namespace jgq {
 
-constexpr int HT_M = 128, HT_N = 256, HT_BK = 32, HT_STAGES = 4, HT_THREADS = 192;
-constexpr int HT_BOX_BYTES = 64 * HT_BK * 2;                 // 64 features x 32 tokens x 2 B = 4096
-constexpr int HT_PLANE_BYTES = (2 + 4) * HT_BOX_BYTES;       // A: 2 boxes, B: up to 4 boxes
-constexpr int HT_STAGE_BYTES = 2 * HT_PLANE_BYTES;           // two planes
-constexpr int HT_SMEM_BYTES = HT_STAGES * HT_STAGE_BYTES + 1024 /*alignment*/ + 256 /*barriers*/;
+constexpr int HT_M = 128;                                     // rows of one MMA / one accumulator
+constexpr int HT_PANEL = 256, HT_N = 256;                     // tile: two accumulators x 256 columns
+#ifndef JGQ_HT_BK
+#define JGQ_HT_BK 32
+#endif
+constexpr int HT_BK = JGQ_HT_BK, HT_THREADS = 192;            // tokens per stage
+constexpr int HT_BOX_BYTES = 64 * HT_BK * 2;                  // 64 features x HT_BK tokens x 2 B
+constexpr int HT_STAGES = 192 * 1024 / (2 * 6 * HT_BOX_BYTES); // ring depth of 128-row tiles (the deeper one)
+// a stage holds two planes of (A boxes + 4 B boxes): 256-row tiles 2 x 8 boxes, 128-row tiles
+// 2 x 6 boxes; the ring is as deep as 192 KB allow.
+constexpr int HT_RING_BYTES = 192 * 1024;
+constexpr int HT_SMEM_BYTES = HT_RING_BYTES + 1024 /*alignment*/ + 256 /*barriers*/;
+constexpr int HT_TMEM_COLS = 2 * HT_N;                        // all 512 columns
 
 struct HessParams {
   int K, n, planes, fmt;
+  int panel;               // tile height: 256 (two accumulators) or 128
   int nseg, S, tokens_per_slice;
   float* out;              // H (S == 1, accumulated into) or slice buffers (S > 1, overwritten)
   int64_t slice_stride;    // elements between slice buffers
@@ -70,7 +83,11 @@ hessian_umma_kernel(const __grid_constant__ CUtensorMap map0, const __grid_const
   using namespace umma;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + HT_STAGES * HT_STAGE_BYTES);
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + HT_RING_BYTES);
+  const int a_boxes = p.panel == HT_PANEL ? 4 : 2;            // boxes of the A operand per plane
+  const int plane_bytes = (a_boxes + 4) * HT_BOX_BYTES;
+  const int stage_bytes = 2 * plane_bytes;
+  const int nst = HT_RING_BYTES / stage_bytes;                // ring depth
   uint64_t* empty_bar = full_bar + HT_STAGES;
   uint64_t* acc_bar = empty_bar + HT_STAGES;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_bar + 1);
@@ -81,17 +98,34 @@ hessian_umma_kernel(const __grid_constant__ CUtensorMap map0, const __grid_const
   // ---- which panel / segment / token slice ----
   const int slice = blockIdx.x / p.nseg;
   int seg = blockIdx.x % p.nseg;
-  int I = 0;
-  while (true) {
-    const int cnt = (I + 2) / 2;          // segments of panel I = ceil((I + 1) / 2)
-    if (seg < cnt) break;
-    seg -= cnt;
-    ++I;
+  int I = 0, row0, col0, rows_a, nb, nb0;
+  bool diag;
+  if (p.panel == HT_PANEL) {
+    while (seg > I) { seg -= I + 1; ++I; }     // panel I has segments 0..I
+    row0 = I * HT_PANEL;
+    col0 = seg * HT_N;
+    diag = seg == I;                           // B is the panel itself: nothing extra to load
+    rows_a = min(HT_PANEL, p.K - row0);
+    nb = min(HT_N, ((p.K - col0 + 15) / 16) * 16);             // MMA width of the full segment
+    nb0 = diag ? min(nb, HT_M) : nb;           // on the diagonal rows 0..127 only need columns 0..127
+  } else {
+    // small K: 128-row panels, one accumulator, segments of up to 256 columns up to the diagonal
+    while (true) {
+      const int cnt = (I + 2) / 2;             // segments of panel I = ceil((I + 1) / 2)
+      if (seg < cnt) break;
+      seg -= cnt;
+      ++I;
+    }
+    row0 = I * HT_M;
+    col0 = seg * HT_N;
+    diag = false;
+    rows_a = min(HT_M, p.K - row0);
+    nb = min(min(HT_N, (I + 1) * HT_M - col0), ((p.K - col0 + 15) / 16) * 16);
+    nb0 = nb;
   }
-  const int row0 = I * HT_M;
-  const int col0 = seg * HT_N;
-  const int width = min(HT_N, (I + 1) * HT_M - col0);     // 128 or 256
-  const int groups_b = width / 64;
+  const int groups_a = (rows_a + 63) / 64;
+  const bool two = rows_a > HT_M;              // the second accumulator has rows
+  const int groups_b = diag ? 0 : (nb + 63) / 64;
   const int tok0 = slice * p.tokens_per_slice;
   const int tok_end = min(p.n, tok0 + p.tokens_per_slice);
   const int nchunks = (tok_end - tok0 + HT_BK - 1) / HT_BK;
@@ -105,7 +139,7 @@ hessian_umma_kernel(const __grid_constant__ CUtensorMap map0, const __grid_const
     if (p.planes > 1) prefetch_tensormap(&map1);
   }
   if (warp == 1) {
-    tmem_alloc(tmem_slot, HT_N);
+    tmem_alloc(tmem_slot, HT_TMEM_COLS);
     tmem_relinquish();
   }
   tc_fence_before();
@@ -116,52 +150,60 @@ hessian_umma_kernel(const __grid_constant__ CUtensorMap map0, const __grid_const
   if (warp == 0) {
     // ===================== TMA producer =====================
     if (lane == 0) {
-      const uint32_t stage_tx = (uint32_t)(p.planes * (2 + groups_b) * HT_BOX_BYTES);
+      const uint32_t stage_tx = (uint32_t)(p.planes * (groups_a + groups_b) * HT_BOX_BYTES);
       int issued = 0;
       for (int kc = 0; kc < nchunks; ++kc) {
-        const int st = kc % HT_STAGES;
-        if (kc >= HT_STAGES && !mbar_wait(&empty_bar[st], ((kc / HT_STAGES) & 1) ^ 1, abort_flag)) break;
+        const int st = kc % nst;
+        if (kc >= nst && !mbar_wait(&empty_bar[st], ((kc / nst) & 1) ^ 1, abort_flag)) break;
         mbar_expect_tx(&full_bar[st], stage_tx);
         const int tok = tok0 + kc * HT_BK;
-        uint8_t* sb = smem + st * HT_STAGE_BYTES;
+        uint8_t* sb = smem + st * stage_bytes;
         for (int pl = 0; pl < p.planes; ++pl) {
           const CUtensorMap* m = pl == 0 ? &map0 : &map1;
-          uint8_t* pb = sb + pl * HT_PLANE_BYTES;
-          tma_load_2d(pb + 0 * HT_BOX_BYTES, m, row0, tok, &full_bar[st]);
-          tma_load_2d(pb + 1 * HT_BOX_BYTES, m, row0 + 64, tok, &full_bar[st]);
+          uint8_t* pb = sb + pl * plane_bytes;
+          for (int g = 0; g < groups_a; ++g)
+            tma_load_2d(pb + g * HT_BOX_BYTES, m, row0 + 64 * g, tok, &full_bar[st]);
           for (int g = 0; g < groups_b; ++g)
-            tma_load_2d(pb + (2 + g) * HT_BOX_BYTES, m, col0 + 64 * g, tok, &full_bar[st]);
+            tma_load_2d(pb + (a_boxes + g) * HT_BOX_BYTES, m, col0 + 64 * g, tok, &full_bar[st]);
         }
         issued = kc + 1;
       }
       if (*abort_flag) {
         // let copies that are still in flight land before the CTA gives its shared memory back
-        for (int kc = max(0, issued - HT_STAGES); kc < issued; ++kc) {
+        for (int kc = max(0, issued - nst); kc < issued; ++kc) {
           const long long t0 = clock64();
-          while (!mbar_try_wait(&full_bar[kc % HT_STAGES], (kc / HT_STAGES) & 1) && clock64() - t0 < 20000000LL) {}
+          while (!mbar_try_wait(&full_bar[kc % nst], (kc / nst) & 1) && clock64() - t0 < 20000000LL) {}
         }
       }
     }
   } else if (warp == 1) {
     // ===================== MMA issuer =====================
     if (lane == 0) {
-      const uint32_t idesc = make_idesc_f16(p.fmt, 1, 1, HT_M, width);
+      const uint32_t idesc0 = make_idesc_f16(p.fmt, 1, 1, HT_M, nb0);
+      const uint32_t idesc1 = make_idesc_f16(p.fmt, 1, 1, HT_M, nb);
       const int nterms = p.planes > 1 ? 3 : 1;
+      const int b_box = diag ? 0 : a_boxes;       // first box of the B operand inside a plane
       bool ok = true;
       for (int kc = 0; kc < nchunks && ok; ++kc) {
-        const int st = kc % HT_STAGES;
-        ok = mbar_wait(&full_bar[st], (kc / HT_STAGES) & 1, abort_flag);
+        const int st = kc % nst;
+        ok = mbar_wait(&full_bar[st], (kc / nst) & 1, abort_flag);
         if (!ok) break;
         tc_fence_after();
-        const uint32_t sb = smem_u32(smem + st * HT_STAGE_BYTES);
+        const uint32_t sb = smem_u32(smem + st * stage_bytes);
 #pragma unroll
         for (int k16 = 0; k16 < HT_BK / 16; ++k16) {
           for (int t = 0; t < nterms; ++t) {
             const int pa = (t == 2) ? 1 : 0, pbn = (t == 1) ? 1 : 0;     // (0,0) (0,1) (1,0)
-            const uint64_t da = make_desc_sw128(sb + pa * HT_PLANE_BYTES + k16 * 2048, HT_BOX_BYTES, 1024);
-            const uint64_t db = make_desc_sw128(sb + pbn * HT_PLANE_BYTES + 2 * HT_BOX_BYTES + k16 * 2048,
+            const uint32_t acc_on = (kc > 0 || k16 > 0 || t > 0) ? 1u : 0u;
+            const uint64_t db = make_desc_sw128(sb + pbn * plane_bytes + b_box * HT_BOX_BYTES + k16 * 2048,
                                                 HT_BOX_BYTES, 1024);
-            mma_f16_ss(tmem_acc, da, db, idesc, (kc > 0 || k16 > 0 || t > 0) ? 1u : 0u);
+            const uint64_t da0 = make_desc_sw128(sb + pa * plane_bytes + k16 * 2048, HT_BOX_BYTES, 1024);
+            mma_f16_ss(tmem_acc, da0, db, idesc0, acc_on);
+            if (two) {
+              const uint64_t da1 = make_desc_sw128(sb + pa * plane_bytes + 2 * HT_BOX_BYTES + k16 * 2048,
+                                                   HT_BOX_BYTES, 1024);
+              mma_f16_ss(tmem_acc + HT_N, da1, db, idesc1, acc_on);
+            }
           }
         }
         mma_commit(&empty_bar[st]);     // frees the stage once these MMAs have read it
@@ -174,24 +216,27 @@ hessian_umma_kernel(const __grid_constant__ CUtensorMap map0, const __grid_const
     tc_fence_after();
     if (ok) {
       const int q = warp & 3;                       // TMEM lane quarter this warp may read
-      const int i = row0 + 32 * q + lane;
       float* out = p.out + (int64_t)slice * p.slice_stride;
-      for (int c = 0; c < width; c += 32) {
-        uint32_t r[32];
-        tmem_ld_32x32(tmem_acc + ((uint32_t)(32 * q) << 16) + (uint32_t)c, r);
-        tmem_ld_wait();
-        if (i < p.K) {
-          float* dst = out + (int64_t)i * p.K + col0 + c;
+      for (int a = 0; a < (two ? 2 : 1); ++a) {
+        const int i = row0 + HT_M * a + 32 * q + lane;
+        const int width = a == 0 ? nb0 : nb;
+        for (int c = 0; c < width; c += 32) {
+          uint32_t r[32];
+          tmem_ld_32x32(tmem_acc + (uint32_t)(HT_N * a) + ((uint32_t)(32 * q) << 16) + (uint32_t)c, r);
+          tmem_ld_wait();
+          if (i < p.K) {
+            float* dst = out + (int64_t)i * p.K + col0 + c;
 #pragma unroll
-          for (int v = 0; v < 8; ++v) {
-            if (col0 + c + 4 * v < p.K) {
-              float4 o = make_float4(__uint_as_float(r[4 * v]), __uint_as_float(r[4 * v + 1]),
-                                     __uint_as_float(r[4 * v + 2]), __uint_as_float(r[4 * v + 3]));
-              if (p.S == 1) {
-                const float4 h = *reinterpret_cast<const float4*>(dst + 4 * v);
-                o.x += h.x; o.y += h.y; o.z += h.z; o.w += h.w;
+            for (int v = 0; v < 8; ++v) {
+              if (c + 4 * v < width && col0 + c + 4 * v < p.K) {
+                float4 o = make_float4(__uint_as_float(r[4 * v]), __uint_as_float(r[4 * v + 1]),
+                                       __uint_as_float(r[4 * v + 2]), __uint_as_float(r[4 * v + 3]));
+                if (p.S == 1) {
+                  const float4 h = *reinterpret_cast<const float4*>(dst + 4 * v);
+                  o.x += h.x; o.y += h.y; o.z += h.z; o.w += h.w;
+                }
+                *reinterpret_cast<float4*>(dst + 4 * v) = o;
               }
-              *reinterpret_cast<float4*>(dst + 4 * v) = o;
             }
           }
         }
@@ -204,7 +249,7 @@ hessian_umma_kernel(const __grid_constant__ CUtensorMap map0, const __grid_const
   if (threadIdx.x == 0 && *abort_flag && p.status) atomicOr(p.status, JGQ_STATUS_TIMEOUT);
   if (warp == 1) {
     tc_fence_after();
-    tmem_dealloc(tmem_acc, HT_N);
+    tmem_dealloc(tmem_acc, HT_TMEM_COLS);
   }
 }
 
@@ -226,12 +271,20 @@ HessPlan plan_hessian_umma(int64_t n, int64_t K, int x_dtype) {
   if (ov != 2 && (K < 256 || n < 512)) return pl;     // tiny problems: the FFMA path is already launch-bound
   pl.use = 1;
   pl.planes = (x_dtype == JGQ_F32) ? 2 : 1;
-  const int64_t T = cdiv(K, HT_M);
+  // 256-row tiles need a third fewer operand bytes per flop; with few tiles (small K) the
+  // 128-row tiles balance better over the SMs and need fewer token slices
+  pl.panel = K >= 1536 ? HT_PANEL : HT_M;
   int64_t nseg = 0;
-  for (int64_t I = 0; I < T; ++I) nseg += (I + 2) / 2;
+  if (pl.panel == HT_PANEL) {
+    const int64_t T = cdiv(K, HT_PANEL);
+    nseg = T * (T + 1) / 2;                     // 256 x 256 tiles on or below the diagonal
+  } else {
+    const int64_t T = cdiv(K, HT_M);
+    for (int64_t I = 0; I < T; ++I) nseg += (I + 2) / 2;
+  }
   pl.nseg = (int)nseg;
   const int sms = sm_count();
-  int64_t smax = std::min<int64_t>(16, std::max<int64_t>(1, n / 1024));
+  int64_t smax = std::min<int64_t>(pl.panel == HT_PANEL ? 32 : 16, std::max<int64_t>(1, n / 1024));
   while (smax > 1 && (size_t)smax * K * K * sizeof(float) > ((size_t)512 << 20)) --smax;
   int best = 1;
   double best_eff = 0.0;
@@ -275,6 +328,7 @@ int launch_hessian_umma(const HessPlan& pl, const void* X, int x_dtype, int64_t 
   if (rc) return rc;
   HessParams p;
   p.K = (int)K; p.n = (int)n; p.planes = pl.planes; p.fmt = (x_dtype == JGQ_F16) ? 0 : 1;
+  p.panel = pl.panel;
   p.nseg = pl.nseg; p.S = pl.S; p.tokens_per_slice = pl.tokens_per_slice;
   p.out = pl.S > 1 ? part : H;
   p.slice_stride = pl.S > 1 ? K * K : 0;

@@ -390,9 +390,11 @@ def test_config1_matmul_after_gptq(G):
 
 
 # ------------------------------------------------- Hessian on the tensor path ----
-@pytest.mark.parametrize('n,K', [(1024, 256), (4096, 768), (2000, 320), (8192, 1024), (777, 512)])
+@pytest.mark.parametrize('n,K', [(1024, 256), (4096, 768), (2000, 320), (8192, 1024), (777, 512),
+                                 (4096, 1536), (3000, 1800), (2048, 1928), (16384, 3072)])
 def test_hessian_tensor_path_fp32(G, n, K):
-    """fp32 batches go through the bf16-split tcgen05 kernel (K % 8 == 0, K >= 256, n >= 512)."""
+    """fp32 batches go through the bf16-split tcgen05 kernel (K % 8 == 0, K >= 256, n >= 512):
+    128-row tiles below K = 1536, 256-row tiles with two accumulators from there on, ragged edges included."""
     rng = np.random.default_rng(90 + K)
     X = (rng.standard_normal((n, K)) * rng.uniform(0.1, 3.0, size=K) + rng.uniform(-0.5, 0.5, size=K)).astype(np.float32)
     ref = (X.astype(np.float64).T @ X.astype(np.float64)) / n
@@ -407,10 +409,11 @@ def test_hessian_tensor_path_fp32(G, n, K):
     assert np.array_equal(a, again), 'Hessian accumulation must be deterministic'
 
 
+@pytest.mark.parametrize('K', [512, 1800])
 @pytest.mark.parametrize('dtype', [torch.float16, torch.bfloat16])
-def test_hessian_tensor_path_half(G, dtype):
+def test_hessian_tensor_path_half(G, dtype, K):
     rng = np.random.default_rng(95)
-    X = torch.from_numpy(rng.standard_normal((2048, 512)).astype(np.float32)).to(dtype)
+    X = torch.from_numpy(rng.standard_normal((2048, K)).astype(np.float32)).to(dtype)
     ref = (X.double().numpy().T @ X.double().numpy()) / 2048
     got = host(G.accumulate_H([X.cuda()]))
     assert np.allclose(got, ref, atol=5e-6, rtol=1e-5)
