@@ -239,7 +239,7 @@ def run_ours(args):
     def step_resident():
         jobs = [(weights[name], list(captured[name].chunk(CALIB_BATCHES)))
                 for weights, captured in zip(model, acts) for name, _, _ in LINEARS]
-        return gg.gptq_many(jobs, block_size=BLOCK_SIZE, damping=DAMP, pack=True, streams=args.streams)
+        return gg.gptq_many(jobs, block_size=BLOCK_SIZE, damping=DAMP, pack=True, streams=args.streams, hessian_stream=not args.no_hessian_stream)
 
     # ---- value: device-resident ----
     for _ in range(args.warmup):
@@ -352,7 +352,8 @@ def run_ours(args):
         jobs = [(host_w[i][name], list(host_acts[i % distinct][name].chunk(CALIB_BATCHES)))
                 for i in range(layers) for name, _, _ in LINEARS]
         outs = [host_out[i][name] for i in range(layers) for name, _, _ in LINEARS]
-        gg.gptq_many(jobs, block_size=BLOCK_SIZE, damping=DAMP, pack=True, out_host=outs, streams=args.streams)
+        gg.gptq_many(jobs, block_size=BLOCK_SIZE, damping=DAMP, pack=True, out_host=outs, streams=args.streams,
+                     hessian_stream=not args.no_hessian_stream)
         torch.cuda.synchronize()
 
     for _ in range(min(args.warmup, 3)):
@@ -481,7 +482,9 @@ def main():
     ap.add_argument('--impl', default='ours', choices=['ours', 'reference'])
     ap.add_argument('--layers', type=int, default=N_LAYERS, help='blocks to quantize (12 = the full workload)')
     ap.add_argument('--skip-matmul', action='store_true')
-    ap.add_argument('--streams', type=int, default=8, help='independent linears in flight (compute streams)')
+    ap.add_argument('--streams', type=int, default=12, help='independent linears in flight (compute streams)')
+    ap.add_argument('--no-hessian-stream', action='store_true',
+                    help='issue every Hessian GEMM on its linear\'s own stream instead of one lower-priority stream')
     ap.add_argument('--only-matmul', action='store_true', help='run only the packed-int4 matmul sweep')
     ap.add_argument('--matmul-shapes', default='', help='comma list of KxNxM cases for --only-matmul')
     ap.add_argument('--skip-cpu', action='store_true')

@@ -43,7 +43,8 @@ enum {
 };
 
 /* bits of the device status word */
-enum { JGQ_STATUS_NOT_PD = 1, JGQ_STATUS_NAN = 2, JGQ_STATUS_TIMEOUT = 4 };
+enum { JGQ_STATUS_NOT_PD = 1, JGQ_STATUS_NAN = 2, JGQ_STATUS_TIMEOUT = 4,
+       JGQ_STATUS_LAYOUT = 8 /* a kernel found its shared memory misaligned and did nothing */ };
 
 int jgq_version(void);
 const char* jgq_last_error(void);
@@ -81,7 +82,7 @@ int jgq_col_params(const float* W, int64_t K, int64_t N, int maxq,
  * calibration batch X of n rows (x_dtype F32/F16/BF16, row-major n x K).
  * jgq_hessian_finalize divides by the total sample count and mirrors the
  * lower triangle, giving (1/n) sum x x^T, which accumulate_H returns.
- * dev_status (may be null) receives JGQ_STATUS_TIMEOUT if a bounded device-side
+ * dev_status (may be null) receives JGQ_STATUS_LAYOUT if the kernel could not run, JGQ_STATUS_TIMEOUT if a bounded device-side
  * wait of the tensor-core kernel ran out. */
 size_t jgq_hessian_workspace_bytes(int64_t n, int64_t K, int x_dtype);
 int jgq_hessian_accum(const void* X, int x_dtype, int64_t n, int64_t K, float* H,

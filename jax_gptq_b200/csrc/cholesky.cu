@@ -13,8 +13,10 @@
 //            (3) trailing   A[i,j] -= A[i,k] A[j,k]^T         (FFMA GEMM, lower tiles)
 //            (5) S[i>k, <=k] += A[i,k] X[k, <=k]              (FFMA GEMM)
 //
-// S lives in the not-yet-final part of X.  Everything is fp32 with IEEE
-// division and square root.
+// (3) and (5) are blocked a second time: four panels form an outer block; a step applies
+// its rank-64 update only to the block's own columns of A and rows of S, and the rest of
+// the matrix gets one update of depth 256 per outer block.  S lives in the not-yet-final
+// part of X.  Everything is fp32 with IEEE division and square root.
 #include "common.cuh"
 #include "sgemm.cuh"
 #include <algorithm>
@@ -22,6 +24,7 @@
 namespace jgq {
 
 constexpr int CB = 64;          // panel width
+constexpr int COB = 4;          // panels per outer block (deferred updates of depth 256)
 constexpr int CPAD = CB + 1;
 
 // ---- (0) diagonal statistics: dead features, damping increment ----------------
@@ -335,6 +338,11 @@ extern "C" int jgq_damp_invert(float* W, int64_t N, float* H, int64_t K, float d
   float* damp_add = (float*)(dead + align_up((size_t)K, 256));
   float* X = H;   // H's storage is reused for the triangular inverse once A is built
 
+  prefer_shared_carveout<diag_stats_kernel>();
+  prefer_shared_carveout<build_reversed_kernel>();
+  prefer_shared_carveout<zero_dead_rows_kernel>();
+  prefer_shared_carveout<chol_step_kernel>();
+  prefer_shared_carveout<reverse_transpose_kernel>();
   diag_stats_kernel<<<1, 1024, 0, s>>>(H, Ki, damping, dead, damp_add);
   JGQ_LAUNCHED();
   {
@@ -350,20 +358,40 @@ extern "C" int jgq_damp_invert(float* W, int64_t N, float* H, int64_t K, float d
   if (cudaMemsetAsync(X, 0, (size_t)K * K * sizeof(float), s) != cudaSuccess)
     return fail(JGQ_ERR_CUDA, "damp_invert: memset failed");
 
+  // Two-level blocking: inside an outer block of COB panels the rank-64 updates only touch the
+  // block's own columns of A and its own rows of S; everything beyond the block gets one update of
+  // depth 64 * COB when the block is finished, which is where nearly all the arithmetic is.
   const int nblk = (int)cdiv(K, CB);
-  for (int kb = 0; kb < nblk; ++kb) {
-    const int r1 = (kb + 1) * CB;            // first row below the diagonal block
-    const int below = Ki - r1;
-    const int nb = std::min(CB, Ki - kb * CB);
-    const int tiles_below = below > 0 ? (int)cdiv(below, CB) : 0;
-    chol_step_kernel<<<(unsigned)(1 + tiles_below + kb), 256, 0, s>>>(A, X, Ki, kb, tiles_below, dev_status);
-    JGQ_LAUNCHED();
-    if (below > 0) {
-      // (3) trailing update of A (lower tiles) and (5) update of the pending part of X, one launch
-      const float* P = A + (int64_t)r1 * K + (int64_t)kb * CB;
-      const GemmParams g0 = make_gemm_params(P, K, P, K, A + (int64_t)r1 * K + r1, K, below, below, nb, -1.f, 1.f, 1);
-      const GemmParams g1 = make_gemm_params(P, K, X + (int64_t)kb * CB * K, K, X + (int64_t)r1 * K, K,
-                                             below, r1, nb, 1.f, 1.f, 0);
+  for (int ob = 0; ob < nblk; ob += COB) {
+    const int c_begin = ob * CB;                                   // first column of the outer block
+    const int c_end = std::min(Ki, (ob + COB) * CB);               // one past its last column
+    for (int kb = ob; kb < std::min(nblk, ob + COB); ++kb) {
+      const int r1 = std::min(Ki, (kb + 1) * CB);      // first row below the diagonal block
+      const int below = Ki - r1;
+      const int nb = std::min(CB, Ki - kb * CB);
+      const int tiles_below = below > 0 ? (int)cdiv(below, CB) : 0;
+      chol_step_kernel<<<(unsigned)(1 + tiles_below + kb), 256, 0, s>>>(A, X, Ki, kb, tiles_below, dev_status);
+      JGQ_LAUNCHED();
+      if (c_end > r1) {
+        // (3) A[r1:, r1:c_end] -= P P[r1:c_end]^T (lower tiles) and (5) S[r1:c_end, :r1] += P[r1:c_end] X[k, :r1]
+        const float* P = A + (int64_t)r1 * K + (int64_t)kb * CB;
+        GemmParams g0 = make_gemm_params(P, K, P, K, A + (int64_t)r1 * K + r1, K, below, c_end - r1, nb,
+                                         -1.f, 1.f, 1);
+        GemmParams g1 = make_gemm_params(P, K, X + (int64_t)kb * CB * K, K, X + (int64_t)r1 * K, K,
+                                         c_end - r1, r1, nb, 1.f, 1.f, 0);
+        const int rc = launch_sgemm_dual(g0, true, g1, false, s);
+        if (rc) return rc;
+      }
+    }
+    if (c_end < Ki) {
+      // the block's whole panel Pb = A[c_end:, c_begin:c_end] at once:
+      // A[c_end:, c_end:] -= Pb Pb^T (lower tiles)   and   S[c_end:, :c_end] += Pb X[c_begin:c_end, :c_end]
+      const int below = Ki - c_end, depth = c_end - c_begin;
+      const float* Pb = A + (int64_t)c_end * K + c_begin;
+      GemmParams g0 = make_gemm_params(Pb, K, Pb, K, A + (int64_t)c_end * K + c_end, K, below, below, depth,
+                                       -1.f, 1.f, 1);
+      GemmParams g1 = make_gemm_params(Pb, K, X + (int64_t)c_begin * K, K, X + (int64_t)c_end * K, K,
+                                       below, c_end, depth, 1.f, 1.f, 0);
       const int rc = launch_sgemm_dual(g0, true, g1, false, s);
       if (rc) return rc;
     }

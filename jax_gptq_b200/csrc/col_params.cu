@@ -53,6 +53,7 @@ extern "C" int jgq_col_params(const float* W, int64_t K, int64_t N, int maxq,
   JGQ_REQUIRE(maxq >= 1 && maxq <= 255, JGQ_ERR_ARG, "col_params: maxq %d out of range", maxq);
   JGQ_REQUIRE(W && scale && zero, JGQ_ERR_ARG, "col_params: null pointer");
   dim3 block(kCols, kRowLanes);
+  prefer_shared_carveout<col_params_kernel>();
   col_params_kernel<<<(unsigned)cdiv(N, kCols), block, 0, (cudaStream_t)stream>>>(W, K, N, (float)maxq, scale, zero);
   return check_launch("col_params");
 }

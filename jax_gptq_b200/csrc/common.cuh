@@ -36,6 +36,20 @@ inline int check_launch(const char* what) {
   return JGQ_OK;
 }
 
+// Asks for the largest shared-memory carve-out for a kernel (once per device).  The kernels of the
+// latency-bound stages are meant to share SMs with the Hessian kernel, which needs that carve-out;
+// CTAs of kernels that prefer different L1 / shared-memory splits do not run on one SM together.
+template <auto Kern>
+inline void prefer_shared_carveout() {
+  static bool done[64] = {false};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64 || done[dev]) return;
+  cudaFuncSetAttribute(reinterpret_cast<const void*>(Kern), cudaFuncAttributePreferredSharedMemoryCarveout,
+                       cudaSharedmemCarveoutMaxShared);
+  cudaGetLastError();      // a hint: a refusal is not an error
+  done[dev] = true;
+}
+
 inline bool aligned(const void* p, size_t a) { return (reinterpret_cast<uintptr_t>(p) % a) == 0; }
 inline int64_t cdiv(int64_t a, int64_t b) { return (a + b - 1) / b; }
 inline size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }

@@ -111,6 +111,7 @@ extern "C" int jgq_hessian_accum(const void* X, int x_dtype, int64_t n, int64_t 
     if (pl.S > 1) {
       const float* part = (const float*)((const char*)ws + 2 * pl.plane_bytes);
       dim3 blk(32, 8), grd((unsigned)cdiv(K, 32), (unsigned)cdiv(K, 8));
+      prefer_shared_carveout<reduce_splits_kernel>();
       reduce_splits_kernel<<<grd, blk, 0, s>>>(H, part, (int)K, pl.S);
       return check_launch("hessian_reduce");
     }
@@ -144,6 +145,7 @@ extern "C" int jgq_hessian_finalize(float* H, int64_t K, double n_total, void* s
   JGQ_REQUIRE(n_total > 0, JGQ_ERR_ARG, "hessian_finalize: sample count must be positive");
   JGQ_REQUIRE(H, JGQ_ERR_ARG, "hessian_finalize: null pointer");
   dim3 blk(32, 8), grd((unsigned)cdiv(K, 32), (unsigned)cdiv(K, 32));
+  prefer_shared_carveout<finalize_kernel>();
   finalize_kernel<<<grd, blk, 0, (cudaStream_t)stream>>>(H, (int)K, (float)n_total);
   return check_launch("hessian_finalize");
 }

@@ -42,7 +42,10 @@ constexpr int HT_STAGES = 192 * 1024 / (2 * 6 * HT_BOX_BYTES); // ring depth of 
 // a stage holds two planes of (A boxes + 4 B boxes): 256-row tiles 2 x 8 boxes, 128-row tiles
 // 2 x 6 boxes; the ring is as deep as 192 KB allow.
 constexpr int HT_RING_BYTES = 192 * 1024;
-constexpr int HT_SMEM_BYTES = HT_RING_BYTES + 1024 /*alignment*/ + 256 /*barriers*/;
+// No alignment slack: the dynamic shared memory is declared 1024-byte aligned (the kernel checks it).
+// 192 KB + 256 B leaves room on the SM for one CTA of the Cholesky kernels (33 KB) beside this one, so
+// that their FFMA work overlaps the tensor work here.
+constexpr int HT_SMEM_BYTES = HT_RING_BYTES + 256 /*barriers*/;
 constexpr int HT_TMEM_COLS = 2 * HT_N;                        // all 512 columns
 
 struct HessParams {
@@ -81,8 +84,8 @@ __global__ void __launch_bounds__(HT_THREADS, 1)
 hessian_umma_kernel(const __grid_constant__ CUtensorMap map0, const __grid_constant__ CUtensorMap map1,
                     const HessParams p) {
   using namespace umma;
-  extern __shared__ uint8_t smem_raw[];
-  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  uint8_t* smem = smem_raw;
   uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + HT_RING_BYTES);
   const int a_boxes = p.panel == HT_PANEL ? 4 : 2;            // boxes of the A operand per plane
   const int plane_bytes = (a_boxes + 4) * HT_BOX_BYTES;
@@ -130,6 +133,10 @@ hessian_umma_kernel(const __grid_constant__ CUtensorMap map0, const __grid_const
   const int tok_end = min(p.n, tok0 + p.tokens_per_slice);
   const int nchunks = (tok_end - tok0 + HT_BK - 1) / HT_BK;
 
+  if ((smem_u32(smem) & 1023u) != 0u) {       // the swizzled boxes need 1024-byte aligned stages
+    if (threadIdx.x == 0 && p.status) atomicOr(p.status, JGQ_STATUS_LAYOUT);
+    return;
+  }
   if (threadIdx.x == 0) {
     for (int s = 0; s < HT_STAGES; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
     mbar_init(acc_bar, 1);
@@ -315,6 +322,7 @@ int launch_hessian_umma(const HessPlan& pl, const void* X, int x_dtype, int64_t 
     w += 2 * pl.plane_bytes;
     const int64_t total4 = n * K / 4;
     const int blocks = (int)std::min<int64_t>(cdiv(total4, 256), (int64_t)sm_count() * 16);
+    prefer_shared_carveout<split_bf16_kernel<float>>();
     split_bf16_kernel<float><<<blocks, 256, 0, s>>>((const float*)X, P0, P1, total4);
     JGQ_LAUNCHED();
     plane0 = P0;

@@ -275,6 +275,7 @@ extern "C" int jgq_pack_matrix(const void* Q, int q_dtype, const float* scale, c
   cudaStream_t s = (cudaStream_t)stream;
   if (q_dtype == JGQ_F32 && inner % 4 == 0 && aligned(Q, 16) && aligned(scale, 16) && aligned(zero, 16) &&
       aligned(packed, 4)) {
+    prefer_shared_carveout<pack_matrix_vec4_kernel>();
     pack_matrix_vec4_kernel<<<grid_for(total / 4, kPackThreads), kPackThreads, 0, s>>>(
         (const float4*)Q, (const float4*)scale, (const float4*)zero, (uint32_t*)packed, outer, half, inner / 4);
   } else if (q_dtype == JGQ_F32) {

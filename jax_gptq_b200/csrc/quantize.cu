@@ -166,6 +166,8 @@ static int launch_block(const float* W, const float* L, const float* scale, cons
     std::call_once(flags[dev], []() {
       cudaFuncSetAttribute(gptq_block_kernel<QT, TPB>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                            (128 * 128 + 128 * TPB) * (int)sizeof(float));
+      cudaFuncSetAttribute(gptq_block_kernel<QT, TPB>, cudaFuncAttributePreferredSharedMemoryCarveout,
+                           cudaSharedmemCarveoutMaxShared);
     });
   }
   gptq_block_kernel<QT, TPB><<<(unsigned)cdiv(N, TPB), TPB, smem, s>>>(

@@ -67,8 +67,15 @@ __device__ __forceinline__ void gemm_store_tile(float (*S)[GBM + GPAD], const fl
   }
 }
 
+// Shared-memory tiles of one CTA; the caller owns them so that kernels that select between
+// instantiations of sgemm_body at run time hold one copy, not one per instantiation.
+struct GemmSmem {
+  float As[2][GBK][GBM + GPAD];
+  float Bs[2][GBK][GBN + GPAD];
+};
+
 template <bool A_KC, bool B_KC>
-__device__ __forceinline__ void sgemm_body(const GemmParams& p, const int zsplit) {
+__device__ __forceinline__ void sgemm_body(const GemmParams& p, const int zsplit, GemmSmem& sm) {
   const int m0 = blockIdx.y * GBM, n0 = blockIdx.x * GBN;
   if (m0 >= p.M || n0 >= p.N) return;
   if (p.tri && n0 > m0 + GBM - 1) return;
@@ -76,8 +83,8 @@ __device__ __forceinline__ void sgemm_body(const GemmParams& p, const int zsplit
   const int kend = min(p.Kd, kbeg + p.k_chunk);
   float* __restrict__ C = p.C + (int64_t)zsplit * p.c_split_stride;
 
-  __shared__ __align__(16) float As[2][GBK][GBM + GPAD];
-  __shared__ __align__(16) float Bs[2][GBK][GBN + GPAD];
+  float (&As)[2][GBK][GBM + GPAD] = sm.As;
+  float (&Bs)[2][GBK][GBN + GPAD] = sm.Bs;
 
   const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
   float acc[8][8];
@@ -158,20 +165,22 @@ __device__ __forceinline__ void sgemm_body(const GemmParams& p, const int zsplit
 }
 
 template <bool A_KC, bool B_KC>
-__global__ void __launch_bounds__(GTHREADS)
+__global__ void __launch_bounds__(GTHREADS, 2)
 sgemm_kernel(const GemmParams p) {
-  sgemm_body<A_KC, B_KC>(p, blockIdx.z);
+  __shared__ __align__(16) GemmSmem sm;
+  sgemm_body<A_KC, B_KC>(p, blockIdx.z, sm);
 }
 
 // Two independent products in one launch (blockIdx.z selects the problem); A has the
 // contraction index contiguous in both, B's layout is a per-problem flag.
 struct GemmDualParams { GemmParams p[2]; int b_kc[2]; };
 
-static __global__ void __launch_bounds__(GTHREADS)
+static __global__ void __launch_bounds__(GTHREADS, 2)
 sgemm_dual_kernel(const GemmDualParams dp) {
+  __shared__ __align__(16) GemmSmem sm;
   const int z = blockIdx.z;
-  if (dp.b_kc[z]) sgemm_body<true, true>(dp.p[z], 0);
-  else            sgemm_body<true, false>(dp.p[z], 0);
+  if (dp.b_kc[z]) sgemm_body<true, true>(dp.p[z], 0, sm);
+  else            sgemm_body<true, false>(dp.p[z], 0, sm);
 }
 
 // Host-side launcher.  `splits` > 1 slices the contraction range over blockIdx.z,
@@ -195,6 +204,7 @@ inline int launch_sgemm_dual(const GemmParams& p0, bool b_kc0, const GemmParams&
   const int gx = (int)std::max(cdiv(std::max(p0.N, 0), GBN), cdiv(std::max(p1.N, 0), GBN));
   const int gy = (int)std::max(cdiv(std::max(p0.M, 0), GBM), cdiv(std::max(p1.M, 0), GBM));
   if (gx <= 0 || gy <= 0) return JGQ_OK;
+  prefer_shared_carveout<sgemm_dual_kernel>();
   sgemm_dual_kernel<<<dim3((unsigned)gx, (unsigned)gy, 2), GTHREADS, 0, s>>>(dp);
   return check_launch("sgemm_dual");
 }
@@ -213,6 +223,10 @@ inline int launch_sgemm(bool a_kc, bool b_kc, const float* A, int64_t lda, const
   if (chunk < GBK) chunk = GBK;
   p.k_chunk = chunk; p.c_split_stride = c_split_stride;
   dim3 grid((unsigned)cdiv(N, GBN), (unsigned)cdiv(M, GBM), (unsigned)splits);
+  prefer_shared_carveout<sgemm_kernel<true, true>>();
+  prefer_shared_carveout<sgemm_kernel<true, false>>();
+  prefer_shared_carveout<sgemm_kernel<false, true>>();
+  prefer_shared_carveout<sgemm_kernel<false, false>>();
   if (a_kc && b_kc)        sgemm_kernel<true, true><<<grid, GTHREADS, 0, s>>>(p);
   else if (a_kc && !b_kc)  sgemm_kernel<true, false><<<grid, GTHREADS, 0, s>>>(p);
   else if (!a_kc && b_kc)  sgemm_kernel<false, true><<<grid, GTHREADS, 0, s>>>(p);

@@ -79,8 +79,7 @@ def gptq_token_sharded(W, xs_local, block_size=128, actorder=False, damping=0.01
     H_sum, n_local = G._accumulate_raw(xs_local, status=status)
     H_sum, n = allreduce_hessian(H_sum, n_local, group)
     H = G._finalize_H(H_sum, n)
-    if int(status.item()) != 0:
-        raise RuntimeError('a device-side wait timed out while accumulating the Hessian')
+    G._raise_status(int(status.item()) << 8)
     c0, c1 = (0, Wd.shape[1])
     if shard_columns and world > 1:
         c0, c1 = shard_range(Wd.shape[1], rank, world, multiple)

@@ -229,8 +229,7 @@ def accumulate_H(xs, use_fp64=False):
     status = torch.zeros(1, dtype=torch.int32, device=_dev())
     H, n = _accumulate_raw(xs, status=status)
     H = _finalize_H(H, n)
-    if int(status.item()) != 0:
-        raise RuntimeError('a device-side wait timed out while accumulating the Hessian')
+    _raise_status(int(status.item()) << 8)
     return _out(H, as_np)
 
 
@@ -285,13 +284,15 @@ def _quantize(Wf, L, params, block_size, out_dtype, want_codes=False):
 
 def _raise_status(st):
     if st >> 8:
+        if (st >> 8) & 8:
+            raise RuntimeError('the Hessian kernel found its shared memory misaligned and did not run')
         raise RuntimeError('a device-side wait timed out while accumulating the Hessian')
     if st != 0:
         raise ValueError('NaN when computing Hinv. Features NaN?')      # gptq.py:194-196
 
 
 def gptq(W, xs, block_size=128, actorder=False, damping=0.01, use_fp64=False, *,
-         bits=4, H=None, return_codes=False, _defer=None):
+         bits=4, H=None, return_codes=False, _defer=None, _hess=None):
     """Quantize W (K x N) with calibration batches xs.  Returns (Q, params) like the
     reference (gptq.py:182-212): Q holds the dequantised values in W's dtype and
     params = {'scale', 'zero', 'maxq'}.
@@ -315,7 +316,11 @@ def gptq(W, xs, block_size=128, actorder=False, damping=0.01, use_fp64=False, *,
         raise ValueError(f'K={K} must be a multiple of block_size={block_size}')
     params = _col_params(Wf, bits)                           # gptq.py:185 (before any fix-up)
     h_status = _tmp('h_status', (1,), torch.int32, zero=True)
-    if H is None:
+    if _hess is not None:
+        # (finalized Hessian, its status word, event) produced on another stream; used in place
+        Hd, h_status, ready = _hess
+        torch.cuda.current_stream().wait_event(ready)
+    elif H is None:
         Hd, n = _accumulate_raw(xs, status=h_status)
         Hd = _finalize_H(Hd, n)                              # gptq.py:187
     else:
@@ -447,7 +452,11 @@ def unpack_matrix(weight, dtype=None):
 # --------------------------------------------------------------------------
 # many layers with host-resident inputs: copies overlap the previous layer's compute
 # --------------------------------------------------------------------------
-def gptq_many(jobs, block_size=128, actorder=False, damping=0.01, bits=4, pack=True, out_host=None, streams=8):
+_issued_hook = None      # test / measurement hook, see gptq_many
+
+
+def gptq_many(jobs, block_size=128, actorder=False, damping=0.01, bits=4, pack=True, out_host=None, streams=8,
+              hessian_stream=True):
     """Run ``gptq`` (and ``pack_matrix`` when `pack`) over a sequence of independent ``(W, xs)`` jobs.
 
     This is the loop the reference's interpreter runs layer by layer
@@ -459,6 +468,9 @@ def gptq_many(jobs, block_size=128, actorder=False, damping=0.01, bits=4, pack=T
     * jobs are issued round-robin on `streams` compute streams, so the latency-bound parts of
       one layer (Cholesky panels, the sequential quantize loop) overlap the Hessian GEMM of the
       next ones; each stream has its own scratch buffers;
+    * with `hessian_stream` the Hessian GEMMs, which fill every SM, all go to one stream of lower
+      priority and the compute streams get the higher priority, so that the many short kernels of
+      the latency-bound parts are placed first whenever an SM frees up;
     * the NaN / not-positive-definite status words are read once, after all jobs were issued.
 
     `out_host`, if given, is a list of ``(packed, scale, zero)`` pinned host tensors that receive
@@ -471,13 +483,17 @@ def gptq_many(jobs, block_size=128, actorder=False, damping=0.01, bits=4, pack=T
         return []
     device = _dev()
     nw = max(1, int(streams))
-    key = (torch.cuda.current_device(), nw)
+    key = (torch.cuda.current_device(), nw, bool(hessian_stream))
     state = _arena_cache.get(key)
     if state is None:
-        state = {'copier': torch.cuda.Stream(), 'workers': [torch.cuda.Stream() for _ in range(nw)],
+        state = {'copier': torch.cuda.Stream(),
+                 'workers': [torch.cuda.Stream(priority=-1 if hessian_stream else 0) for _ in range(nw)],
+                 'hstream': torch.cuda.Stream(priority=0) if hessian_stream else None,
+                 'harena': _Arena(),
                  'arenas': [_Arena() for _ in range(nw)]}
         _arena_cache[key] = state
-    copier, workers, arenas = state['copier'], state['workers'], state['arenas']
+    copier, workers, arenas, hstream = state['copier'], state['workers'], state['arenas'], state['hstream']
+    harena = state['harena']
     main = torch.cuda.current_stream()
     start = main.record_event()
     copier.wait_event(start)
@@ -525,20 +541,57 @@ def gptq_many(jobs, block_size=128, actorder=False, damping=0.01, bits=4, pack=T
             ev = copier.record_event()
         return Wd, xd, ev
 
-    results, deferred = [], []
+    # Worker of every job: the one with the least work queued so far.  The cost model only has to
+    # rank jobs (the sequential part of a job grows like K^2 (K + N) / 64 panel steps), so that the
+    # few large-K jobs of a model do not all land on the same stream.
+    def cost(job):
+        shp = tuple(job[0].shape)
+        K, N = (shp + (1, 1))[:2]
+        return float(K) * K * (K + N) + 1e7
+    load = [0.0] * nw
+    owner = [0] * len(jobs)
+    # issue order: with a Hessian stream the expensive jobs go first, so that their long sequential
+    # parts run beside the remaining Hessian GEMMs instead of after them
+    order = sorted(range(len(jobs)), key=lambda i: -cost(jobs[i])) if hstream is not None else list(range(len(jobs)))
+    for i in order:
+        wi = min(range(nw), key=lambda j: (load[j], j))
+        owner[i] = wi
+        load[wi] += cost(jobs[i])
+    nslots = nw + 2                  # Hessians that may exist at a time (finished or being used)
+    slot_free = [None] * nslots
+
+    results, deferred = [None] * len(jobs), []
     try:
-        nxt = stage(jobs[0], 0)
-        for i in range(len(jobs)):
+        nxt = stage(jobs[order[0]], owner[order[0]])
+        for pos, i in enumerate(order):
             Wd, xd, ev = nxt
-            wi = i % nw
+            wi = owner[i]
             ws = workers[wi]
+            hess = None
+            if hstream is not None:
+                slot = pos % nslots
+                with torch.cuda.stream(hstream):
+                    if ev is not None:
+                        hstream.wait_event(ev)
+                    if slot_free[slot] is not None:
+                        hstream.wait_event(slot_free[slot])
+                    _ARENA = harena
+                    try:
+                        K = int(_to_dev(xd[0]).shape[-1])
+                        hs = harena.get(f'hstatus{slot}', (1,), torch.int32, zero=True)
+                        Hbuf = harena.get(f'H{slot}', (K, K), torch.float32, zero=True)
+                        Hd, n = _accumulate_raw(xd, H=Hbuf, status=hs)
+                        Hd = _finalize_H(Hd, n)
+                    finally:
+                        _ARENA = None
+                    hess = (Hd, hs, hstream.record_event())
             with torch.cuda.stream(ws):
                 if ev is not None:
                     ws.wait_event(ev)
                 _ARENA = arenas[wi]
                 try:
                     Q, params = gptq(Wd, xd, block_size=block_size, actorder=actorder, damping=damping, bits=bits,
-                                     _defer=deferred)
+                                     _defer=deferred, _hess=hess)
                 finally:
                     _ARENA = None
                 res = pack_matrix(Q, params) if pack else (Q.clone(), params)
@@ -550,16 +603,24 @@ def gptq_many(jobs, block_size=128, actorder=False, damping=0.01, bits=4, pack=T
                 for t in ((res.int_weight, res.scale, res.zero) if pack else (res[0], params['scale'], params['zero'])):
                     t.record_stream(main)
                 done[wi] = ws.record_event()
-            results.append(res)
-            if i + 1 < len(jobs):
-                nxt = stage(jobs[i + 1], (i + 1) % nw)
+                if hstream is not None:
+                    slot_free[pos % nslots] = done[wi]
+            results[i] = res
+            if pos + 1 < len(order):
+                j = order[pos + 1]
+                nxt = stage(jobs[j], owner[j])
     finally:
         _ARENA = None
     for w in workers:
         main.wait_event(w.record_event())
+    if hstream is not None:
+        main.wait_event(hstream.record_event())
     main.wait_event(copier.record_event())
+    if _issued_hook is not None:
+        _issued_hook()                   # every launch of the call has been issued; nothing has been waited for
     st = int(torch.stack(deferred).max().item()) if deferred else 0      # synchronises with every worker
     for a in arenas:
         a.release()
+    harena.release()
     _raise_status(st)
     return results
