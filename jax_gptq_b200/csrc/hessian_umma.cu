@@ -33,18 +33,15 @@ namespace jgq {
 
 constexpr int HT_M = 128;                                     // rows of one MMA / one accumulator
 constexpr int HT_PANEL = 256, HT_N = 256;                     // tile: two accumulators x 256 columns
-#ifndef JGQ_HT_BK
-#define JGQ_HT_BK 32
-#endif
-constexpr int HT_BK = JGQ_HT_BK, HT_THREADS = 192;            // tokens per stage
+constexpr int HT_RING_BYTES_MAX = 192 * 1024;
+constexpr int HT_BK = 32, HT_THREADS = 192;                   // tokens per stage (16-token stages measured 1.6x slower)
 constexpr int HT_BOX_BYTES = 64 * HT_BK * 2;                  // 64 features x HT_BK tokens x 2 B
-constexpr int HT_STAGES = 192 * 1024 / (2 * 6 * HT_BOX_BYTES); // ring depth of 128-row tiles (the deeper one)
-// a stage holds two planes of (A boxes + 4 B boxes): 256-row tiles 2 x 8 boxes, 128-row tiles
-// 2 x 6 boxes; the ring is as deep as 192 KB allow.
-constexpr int HT_RING_BYTES = 192 * 1024;
+constexpr int HT_STAGES = HT_RING_BYTES_MAX / (2 * 6 * HT_BOX_BYTES); // most stages a ring can have (128-row tiles)
+// a stage holds two planes of (A boxes + 4 B boxes): 256-row tiles 2 x 8 boxes = 64 KB, two stages;
+// 128-row tiles 2 x 6 boxes = 48 KB, two stages as well.  A deeper ring (192 KB) measured no faster, and
+// 128 KB leave about 98 KB of the SM's shared memory to the kernels of other streams.
+constexpr int HT_RING_BYTES = 128 * 1024;
 // No alignment slack: the dynamic shared memory is declared 1024-byte aligned (the kernel checks it).
-// 192 KB + 256 B leaves room on the SM for one CTA of the Cholesky kernels (33 KB) beside this one, so
-// that their FFMA work overlaps the tensor work here.
 constexpr int HT_SMEM_BYTES = HT_RING_BYTES + 256 /*barriers*/;
 constexpr int HT_TMEM_COLS = 2 * HT_N;                        // all 512 columns
 

@@ -453,6 +453,7 @@ def unpack_matrix(weight, dtype=None):
 # many layers with host-resident inputs: copies overlap the previous layer's compute
 # --------------------------------------------------------------------------
 _issued_hook = None      # test / measurement hook, see gptq_many
+_trace = None            # measurement: a list that receives (job, 'hessian' | 'done', timing event)
 
 
 def gptq_many(jobs, block_size=128, actorder=False, damping=0.01, bits=4, pack=True, out_host=None, streams=8,
@@ -585,6 +586,10 @@ def gptq_many(jobs, block_size=128, actorder=False, damping=0.01, bits=4, pack=T
                     finally:
                         _ARENA = None
                     hess = (Hd, hs, hstream.record_event())
+                    if _trace is not None:
+                        e = torch.cuda.Event(enable_timing=True)
+                        e.record()
+                        _trace.append((i, 'hessian', e))
             with torch.cuda.stream(ws):
                 if ev is not None:
                     ws.wait_event(ev)
@@ -603,6 +608,10 @@ def gptq_many(jobs, block_size=128, actorder=False, damping=0.01, bits=4, pack=T
                 for t in ((res.int_weight, res.scale, res.zero) if pack else (res[0], params['scale'], params['zero'])):
                     t.record_stream(main)
                 done[wi] = ws.record_event()
+                if _trace is not None:
+                    e = torch.cuda.Event(enable_timing=True)
+                    e.record()
+                    _trace.append((i, 'done', e))
                 if hstream is not None:
                     slot_free[pos % nslots] = done[wi]
             results[i] = res
