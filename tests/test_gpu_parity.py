@@ -139,7 +139,7 @@ def test_accumulate_H_large_split(G):
 
 
 # ------------------------------------------------------- damp + Cholesky inverse ----
-@pytest.mark.parametrize('K', [32, 64, 100, 256, 768])
+@pytest.mark.parametrize('K', [32, 64, 100, 256, 768, 840, 1536])      # 840: ragged last panel inside an outer block
 def test_damp_invert_matches_oracle(G, K):
     import importlib; gg = importlib.import_module('jax_gptq_b200.gptq')
     rng = np.random.default_rng(30 + K)
@@ -248,6 +248,19 @@ def test_gptq_config1_dense_layer(G):
     W, xs = workloads.dense_layer()
     same, rel = _gptq_parity(G, W, xs, 128)
     print(f'config1: identical codes {same:.6f}, recon rel diff {rel:.2e}')
+
+
+def test_gptq_large_k(G):
+    """K = 1536: the Hessian takes the 256-row tiles, the Cholesky sweep six outer blocks, the quantize
+    loop twelve blocks with eleven tail updates."""
+    rng = np.random.default_rng(57)
+    K, N = 1536, 192
+    W = (0.05 * rng.standard_normal((K, N))).astype(np.float32)
+    mix = (rng.standard_normal((K, K)) / np.sqrt(K)).astype(np.float32)
+    xs = [(rng.standard_normal((1024, K)).astype(np.float32) @ mix + 0.3 * rng.standard_normal((1024, K)).astype(np.float32))
+          for _ in range(4)]
+    same, rel = _gptq_parity(G, W, xs, 128, min_same=0.995)
+    print(f'K=1536: identical codes {same:.6f}, recon rel diff {rel:.2e}')
 
 
 def test_gptq_correlated_activations(G):
