@@ -37,17 +37,18 @@ constexpr int HT_RING_BYTES_MAX = 192 * 1024;
 constexpr int HT_BK = 32, HT_THREADS = 192;                   // tokens per stage (16-token stages measured 1.6x slower)
 constexpr int HT_BOX_BYTES = 64 * HT_BK * 2;                  // 64 features x HT_BK tokens x 2 B
 constexpr int HT_STAGES = HT_RING_BYTES_MAX / (2 * 6 * HT_BOX_BYTES); // most stages a ring can have (128-row tiles)
-// a stage holds two planes of (A boxes + 4 B boxes): 256-row tiles 2 x 8 boxes = 64 KB, two stages;
-// 128-row tiles 2 x 6 boxes = 48 KB, two stages as well.  A deeper ring (192 KB) measured no faster, and
-// 128 KB leave about 98 KB of the SM's shared memory to the kernels of other streams.
-constexpr int HT_RING_BYTES = 128 * 1024;
+// a stage holds two planes of (A boxes + 4 B boxes): 256-row tiles 2 x 8 boxes = 64 KB, two stages
+// (a third measured no faster); 128-row tiles 2 x 6 boxes = 48 KB, three stages (two measured 5 % slower).
+// That leaves 80-100 KB of the SM's shared memory to the kernels of other streams.
 // No alignment slack: the dynamic shared memory is declared 1024-byte aligned (the kernel checks it).
-constexpr int HT_SMEM_BYTES = HT_RING_BYTES + 256 /*barriers*/;
+constexpr int HT_BAR_BYTES = 256;
+inline int hessian_ring_bytes(int panel) { return panel == HT_PANEL ? 2 * 64 * 1024 : 3 * 48 * 1024; }
 constexpr int HT_TMEM_COLS = 2 * HT_N;                        // all 512 columns
 
 struct HessParams {
   int K, n, planes, fmt;
   int panel;               // tile height: 256 (two accumulators) or 128
+  int ring_bytes;          // shared-memory ring; the barriers follow it
   int nseg, S, tokens_per_slice;
   float* out;              // H (S == 1, accumulated into) or slice buffers (S > 1, overwritten)
   int64_t slice_stride;    // elements between slice buffers
@@ -83,11 +84,11 @@ hessian_umma_kernel(const __grid_constant__ CUtensorMap map0, const __grid_const
   using namespace umma;
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   uint8_t* smem = smem_raw;
-  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + HT_RING_BYTES);
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + p.ring_bytes);
   const int a_boxes = p.panel == HT_PANEL ? 4 : 2;            // boxes of the A operand per plane
   const int plane_bytes = (a_boxes + 4) * HT_BOX_BYTES;
   const int stage_bytes = 2 * plane_bytes;
-  const int nst = HT_RING_BYTES / stage_bytes;                // ring depth
+  const int nst = p.ring_bytes / stage_bytes;                 // ring depth
   uint64_t* empty_bar = full_bar + HT_STAGES;
   uint64_t* acc_bar = empty_bar + HT_STAGES;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_bar + 1);
@@ -334,6 +335,8 @@ int launch_hessian_umma(const HessPlan& pl, const void* X, int x_dtype, int64_t 
   HessParams p;
   p.K = (int)K; p.n = (int)n; p.planes = pl.planes; p.fmt = (x_dtype == JGQ_F16) ? 0 : 1;
   p.panel = pl.panel;
+  p.ring_bytes = hessian_ring_bytes(pl.panel);
+  const int smem_bytes = p.ring_bytes + HT_BAR_BYTES;
   p.nseg = pl.nseg; p.S = pl.S; p.tokens_per_slice = pl.tokens_per_slice;
   p.out = pl.S > 1 ? part : H;
   p.slice_stride = pl.S > 1 ? K * K : 0;
@@ -342,10 +345,11 @@ int launch_hessian_umma(const HessPlan& pl, const void* X, int x_dtype, int64_t 
   int dev = 0;
   cudaGetDevice(&dev);
   if (dev >= 0 && dev < 64 && !attr_set[dev]) {
-    cudaFuncSetAttribute(hessian_umma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, HT_SMEM_BYTES);
+    cudaFuncSetAttribute(hessian_umma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                         HT_RING_BYTES_MAX + HT_BAR_BYTES);
     attr_set[dev] = true;
   }
-  hessian_umma_kernel<<<(unsigned)(pl.nseg * pl.S), HT_THREADS, HT_SMEM_BYTES, s>>>(m0, m1, p);
+  hessian_umma_kernel<<<(unsigned)(pl.nseg * pl.S), HT_THREADS, smem_bytes, s>>>(m0, m1, p);
   return check_launch("hessian_umma");
 }
 
