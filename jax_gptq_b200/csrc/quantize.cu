@@ -12,15 +12,24 @@
 // is bit-identical to the fp32 oracle given the same inputs.
 //
 // After each block the remaining rows get the lazy-batch update
-//   W[end:, :] -= L[end:, start:end] @ errors           (FFMA GEMM, fp32)
+//   W[end:, :] -= L[end:, start:end] @ errors           (tensor-core GEMM, three TF32 products)
 #include "common.cuh"
 #include "sgemm.cuh"
 #include <algorithm>
+#include <cstdlib>
+#include <cstring>
 #include <mutex>
 
 namespace jgq {
 
 constexpr int SUB = 16;
+
+// JGQ_TAIL_GEMM=ffma keeps the lazy-batch tail update on the FFMA body (for comparisons).
+static int tail_on_tensor_cores() {
+  static int v = -1;
+  if (v < 0) { const char* e = getenv("JGQ_TAIL_GEMM"); v = (e && !strcmp(e, "ffma")) ? 0 : 1; }
+  return v;
+}
 
 template <typename QT, int TPB>
 __global__ void __launch_bounds__(TPB)
@@ -189,7 +198,7 @@ static int run_quantize(float* W, const float* L, const float* scale, const floa
     const int end = start + bs;
     if (end < K) {
       rc = launch_sgemm(true, false, L + (int64_t)end * K + start, K, E, N,
-                        W + (int64_t)end * N, N, K - end, (int)N, bs, -1.f, 1.f, 0, s);
+                        W + (int64_t)end * N, N, K - end, (int)N, bs, -1.f, 1.f, 0, s, 1, 0, tail_on_tensor_cores());
       if (rc) return rc;
     }
   }

@@ -24,9 +24,11 @@ struct GemmParams {
   int a_vec, b_vec;   // 16-byte vector loads are legal for A / B
   // split over the contraction index: slice z covers [z*k_chunk, (z+1)*k_chunk) and writes C + z*c_split_stride
   int k_chunk; int64_t c_split_stride;
+  int tc;             // 1: products on the tensor cores as three TF32 MMAs (lo*hi + hi*lo + hi*hi)
 };
 
-constexpr int GBM = 128, GBN = 128, GBK = 8, GTHREADS = 256, GPAD = 4;
+constexpr int GBM = 128, GBN = 128, GBK = 8, GTHREADS = 256;
+constexpr int GPAD = 8;     // row stride 136 floats: the MMA fragment loads (8 free x 4 contraction indices) hit 32 banks
 
 template <bool KC>
 __device__ __forceinline__ void gemm_load_tile(const float* __restrict__ P, int64_t ld, int vec,
@@ -164,11 +166,128 @@ __device__ __forceinline__ void sgemm_body(const GemmParams& p, const int zsplit
   }
 }
 
+// ---- the same product on the tensor cores with near-fp32 accuracy ---------------------------
+// Every fp32 operand is split as x = hi + lo with hi = tf32(x), lo = tf32(x - hi); the product
+// is accumulated in fp32 as lo*hi + hi*lo + hi*hi.  The split keeps 22 of the 24 significand
+// bits of an operand, so this body is for updates that tolerate 2^-21 relative error per
+// product (the lazy-batch tail update of the quantize loop), not for the Cholesky sweep.
+// mma.sync m16n8k8, 8 warps as 2 (rows) x 4 (columns), warp tile 64 x 32; same staging and
+// shared-memory tiles as the FFMA body.
+__device__ __forceinline__ void split_tf32(float x, uint32_t& hi, uint32_t& lo) {
+  asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(hi) : "f"(x));
+  const float r = x - __uint_as_float(hi);
+  asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(lo) : "f"(r));
+}
+__device__ __forceinline__ void mma_tf32(float (&d)[4], const uint32_t (&a)[4], const uint32_t (&b)[2]) {
+  asm volatile("mma.sync.aligned.m16n8k8.row.col.f32.tf32.tf32.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+               : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+               : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b[0]), "r"(b[1]));
+}
+
+template <bool A_KC, bool B_KC>
+__device__ __forceinline__ void sgemm_body_tc(const GemmParams& p, const int zsplit, GemmSmem& sm) {
+  const int m0 = blockIdx.y * GBM, n0 = blockIdx.x * GBN;
+  if (m0 >= p.M || n0 >= p.N) return;
+  if (p.tri && n0 > m0 + GBM - 1) return;
+  const int kbeg = zsplit * p.k_chunk;
+  const int kend = min(p.Kd, kbeg + p.k_chunk);
+  float* __restrict__ C = p.C + (int64_t)zsplit * p.c_split_stride;
+  float (&As)[2][GBK][GBM + GPAD] = sm.As;
+  float (&Bs)[2][GBK][GBN + GPAD] = sm.Bs;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int g = lane >> 2, q = lane & 3;
+  const int wm = (warp >> 2) * 64, wn = (warp & 3) * 32;
+  float acc[4][4][4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i)
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) acc[i][j][e] = 0.f;
+
+  float ra[4], rb[4];
+  int buf = 0;
+  if (kbeg < kend) {
+    gemm_load_tile<A_KC>(p.A, p.lda, p.a_vec, m0, p.M, kbeg, kend, ra);
+    gemm_load_tile<B_KC>(p.B, p.ldb, p.b_vec, n0, p.N, kbeg, kend, rb);
+    gemm_store_tile<A_KC>(As[0], ra);
+    gemm_store_tile<B_KC>(Bs[0], rb);
+  }
+  __syncthreads();
+  for (int k0 = kbeg; k0 < kend; k0 += GBK) {
+    const bool more = k0 + GBK < kend;
+    if (more) {
+      gemm_load_tile<A_KC>(p.A, p.lda, p.a_vec, m0, p.M, k0 + GBK, kend, ra);
+      gemm_load_tile<B_KC>(p.B, p.ldb, p.b_vec, n0, p.N, k0 + GBK, kend, rb);
+    }
+    // B fragments of the four 8-column blocks: b0 = (k = q, n = g), b1 = (k = q + 4, n = g)
+    uint32_t bh[4][2], bl[4][2];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      split_tf32(Bs[buf][q][wn + 8 * j + g], bh[j][0], bl[j][0]);
+      split_tf32(Bs[buf][q + 4][wn + 8 * j + g], bh[j][1], bl[j][1]);
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      // A fragment of a 16-row block: a0 = (g, q), a1 = (g + 8, q), a2 = (g, q + 4), a3 = (g + 8, q + 4)
+      uint32_t ah[4], al[4];
+      split_tf32(As[buf][q][wm + 16 * i + g], ah[0], al[0]);
+      split_tf32(As[buf][q][wm + 16 * i + 8 + g], ah[1], al[1]);
+      split_tf32(As[buf][q + 4][wm + 16 * i + g], ah[2], al[2]);
+      split_tf32(As[buf][q + 4][wm + 16 * i + 8 + g], ah[3], al[3]);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        mma_tf32(acc[i][j], al, bh[j]);
+        mma_tf32(acc[i][j], ah, bl[j]);
+        mma_tf32(acc[i][j], ah, bh[j]);
+      }
+    }
+    if (more) {
+      gemm_store_tile<A_KC>(As[buf ^ 1], ra);
+      gemm_store_tile<B_KC>(Bs[buf ^ 1], rb);
+    }
+    __syncthreads();
+    buf ^= 1;
+  }
+
+  // accumulator element e of block (i, j): row 16i + g + 8 (e >> 1), column 8j + 2q + (e & 1)
+  const bool c_vec2 = (p.ldc % 2 == 0) && ((reinterpret_cast<uintptr_t>(C) & 7) == 0);
+#pragma unroll
+  for (int i = 0; i < 4; ++i)
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      const int m = m0 + wm + 16 * i + g + 8 * h;
+      if (m >= p.M) continue;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const int n = n0 + wn + 8 * j + 2 * q;
+        float* cp = C + (int64_t)m * p.ldc + n;
+        const float v0 = acc[i][j][2 * h], v1 = acc[i][j][2 * h + 1];
+        if (c_vec2 && n + 1 < p.N) {
+          float2 o;
+          if (p.beta != 0.f) {
+            const float2 c = *reinterpret_cast<const float2*>(cp);
+            o.x = fmaf(p.alpha, v0, p.beta * c.x);
+            o.y = fmaf(p.alpha, v1, p.beta * c.y);
+          } else {
+            o.x = p.alpha * v0; o.y = p.alpha * v1;
+          }
+          *reinterpret_cast<float2*>(cp) = o;
+        } else {
+          if (n < p.N) cp[0] = (p.beta != 0.f) ? fmaf(p.alpha, v0, p.beta * cp[0]) : p.alpha * v0;
+          if (n + 1 < p.N) cp[1] = (p.beta != 0.f) ? fmaf(p.alpha, v1, p.beta * cp[1]) : p.alpha * v1;
+        }
+      }
+    }
+}
+
 template <bool A_KC, bool B_KC>
 __global__ void __launch_bounds__(GTHREADS, 2)
 sgemm_kernel(const GemmParams p) {
   __shared__ __align__(16) GemmSmem sm;
-  sgemm_body<A_KC, B_KC>(p, blockIdx.z, sm);
+  if (p.tc) sgemm_body_tc<A_KC, B_KC>(p, blockIdx.z, sm);
+  else      sgemm_body<A_KC, B_KC>(p, blockIdx.z, sm);
 }
 
 // Two independent products in one launch (blockIdx.z selects the problem); A has the
@@ -194,6 +313,7 @@ inline GemmParams make_gemm_params(const float* A, int64_t lda, const float* B, 
   p.b_vec = aligned(B, 16) && (ldb % 4 == 0);
   p.k_chunk = (int)cdiv(std::max(Kd, 1), GBK) * GBK;
   p.c_split_stride = 0;
+  p.tc = 0;
   return p;
 }
 
@@ -211,7 +331,7 @@ inline int launch_sgemm_dual(const GemmParams& p0, bool b_kc0, const GemmParams&
 
 inline int launch_sgemm(bool a_kc, bool b_kc, const float* A, int64_t lda, const float* B, int64_t ldb,
                         float* C, int64_t ldc, int M, int N, int Kd, float alpha, float beta, int tri,
-                        cudaStream_t s, int splits = 1, int64_t c_split_stride = 0) {
+                        cudaStream_t s, int splits = 1, int64_t c_split_stride = 0, int tc = 0) {
   if (M <= 0 || N <= 0) return JGQ_OK;
   GemmParams p;
   p.A = A; p.lda = lda; p.B = B; p.ldb = ldb; p.C = C; p.ldc = ldc;
@@ -222,6 +342,7 @@ inline int launch_sgemm(bool a_kc, bool b_kc, const float* A, int64_t lda, const
   int chunk = (int)cdiv(cdiv(Kd, splits), GBK) * GBK;
   if (chunk < GBK) chunk = GBK;
   p.k_chunk = chunk; p.c_split_stride = c_split_stride;
+  p.tc = tc;
   dim3 grid((unsigned)cdiv(N, GBN), (unsigned)cdiv(M, GBM), (unsigned)splits);
   prefer_shared_carveout<sgemm_kernel<true, true>>();
   prefer_shared_carveout<sgemm_kernel<true, false>>();

@@ -323,6 +323,9 @@ static int launch_tb(const void* x, const uint8_t* packed, const void* zero, con
   return check_launch("w4_matmul_tb");
 }
 
+constexpr int64_t kStreamRows = 16;          // token rows of one pass of the streaming kernel
+constexpr int64_t kStreamPassesMaxM = 48;    // up to three passes before the tensor-path kernel takes over
+
 static int w4_path_override() {        // JGQ_W4_PATH=direct: direct-load decode kernel; =mma: no tcgen05 either
   static int v = -1;
   if (v < 0) { const char* e = getenv("JGQ_W4_PATH"); v = !e ? 0 : !strcmp(e, "direct") ? 1 : !strcmp(e, "mma") ? 2 : 0; }
@@ -353,8 +356,8 @@ extern "C" size_t jgq_w4_matmul_workspace_bytes(int64_t M, int64_t N, int64_t K,
   if (up.use) bytes = std::max(bytes, w4_umma_workspace_bytes(up));
   const UmmaPlan up16 = plan_w4_umma(M, N, K, JGQ_F16);
   if (up16.use) bytes = std::max(bytes, w4_umma_workspace_bytes(up16));
-  const StreamPlan sp = plan_w4_stream(M, N, K);
-  if (sp.use) bytes = std::max(bytes, kTicketBytes + sp.part_bytes);
+  const StreamPlan sp = plan_w4_stream(std::min<int64_t>(M, kStreamPassesMaxM) > kStreamRows ? kStreamRows : M, N, K);
+  if (sp.use && M <= kStreamPassesMaxM) bytes = std::max(bytes, kTicketBytes + sp.part_bytes);
   return bytes;
 }
 
@@ -388,6 +391,25 @@ extern "C" int jgq_w4_matmul(const void* x, int x_dtype, const uint8_t* packed,
   if (w4_path_override() == 0) {
     const StreamPlan sp = plan_w4_stream(M, N, K);
     if (sp.use && aligned(packed, 16)) return launch_w4_stream(sp, x, x_dtype, packed, zero, scale, zs_dtype, out, M, N, K, ws, s);
+    // A few more tokens than one pass of the streaming kernel takes: one pass per 16 token rows (60 us
+    // each at 8192 x 28672) still beats the tensor-path kernel, which needs about 250 us for any M
+    // up to 256 on that shape.  The passes run one after the other on the stream and share the workspace.
+    if (M > kStreamRows && M <= kStreamPassesMaxM && aligned(packed, 16)) {
+      const size_t elt = x_dtype == JGQ_F32 ? 4 : 2;
+      bool ok = true;
+      for (int64_t r0 = 0; r0 < M && ok; r0 += kStreamRows)
+        ok = plan_w4_stream(std::min<int64_t>(kStreamRows, M - r0), N, K).use != 0;
+      if (ok) {
+        for (int64_t r0 = 0; r0 < M; r0 += kStreamRows) {
+          const int64_t rows = std::min<int64_t>(kStreamRows, M - r0);
+          const StreamPlan sp1 = plan_w4_stream(rows, N, K);
+          const int rc = launch_w4_stream(sp1, (const char*)x + (size_t)r0 * K * elt, x_dtype, packed, zero, scale, zs_dtype,
+                                          (char*)out + (size_t)r0 * N * elt, rows, N, K, ws, s);
+          if (rc) return rc;
+        }
+        return JGQ_OK;
+      }
+    }
   }
   if (!w4_force_mma_sync()) {
     const UmmaPlan up = plan_w4_umma(M, N, K, x_dtype);

@@ -176,7 +176,9 @@ w4_stream_kernel(const __grid_constant__ CUtensorMap wmap, const StreamParams p)
     s_abort = 0;
     fence_barrier_init();
     prefetch_tensormap(&wmap);
-    for (int j = 0; j < S_NST && j < nstage; ++j) issue_stage(j);
+    // Only the first box now: with every CTA asking for its whole ring at once nothing lands before
+    // 4 us.  The rest of the first round is issued when this box has arrived.
+    if (nstage > 0) issue_stage(0);
   }
   __syncthreads();
 
@@ -261,6 +263,8 @@ w4_stream_kernel(const __grid_constant__ CUtensorMap wmap, const StreamParams p)
       }
       alive = __all_sync(0xffffffffu, mbar_wait(&full_bar[slot], (s / S_NST) & 1, abort_flag));
       if (s == 0) TRACE(1);
+      if (s == 0 && threadIdx.x == 0)
+        for (int j = 1; j < S_NST && j < nstage; ++j) issue_stage(j);
       if (alive) {
         const uint32_t tile = ring_u32 + slot * S_STAGE_BYTES;
         // byte rows 8*sl + q and + 4 of step sl; 16-byte chunk g, swizzled by row & 7.  The next step's

@@ -5,8 +5,9 @@
 // One kernel serves decode-sized and prefill-sized M.  A CTA owns 128 output channels,
 // up to 256 tokens and a slice of the contraction range:
 //
-//   warp 0      TMA producer: raw packed bytes (32 byte rows x 128 channels = 64 k per stage)
-//               and the matching activation tile (tokens x 64 k), two mbarrier rings
+//   warp 0      TMA producer of raw packed bytes (32 byte rows x 128 channels = 64 k per stage),
+//               up to 16 stages = 64 KB ahead
+//   warp 10     TMA producer of the matching activation tiles (tokens x 64 k), its own ring
 //   warps 2-9   expand nibbles to bf16 / f16 with the magic-number trick and write them as
 //               the MMA's A operand: channels are the M dimension (128), stored M-major with
 //               128-byte swizzle, so a 16-byte load of raw bytes (16 channels of one byte row)
@@ -30,9 +31,10 @@ constexpr int U_COLS = 128;                    // channels per CTA (MMA M)
 constexpr int U_STAGE_K = 64;                  // contraction elements per stage
 constexpr int U_RAW_BYTES = 32 * U_COLS;       // 32 byte rows x 128 channels
 constexpr int U_A_BYTES = U_STAGE_K * U_COLS * 2;   // expanded A tile: 2 groups x 64 k x 128 B
-constexpr int U_MAX_ST = 8;                    // upper bound of every ring depth
+constexpr int U_MAX_ST = 16;                   // upper bound of every ring depth
 constexpr int U_DQ_WARPS = 8;
-constexpr int U_THREADS = (2 + U_DQ_WARPS) * 32;
+constexpr int U_XWARP = 2 + U_DQ_WARPS;        // the warp that loads activation tiles
+constexpr int U_THREADS = (3 + U_DQ_WARPS) * 32;
 constexpr size_t U_TICKET_BYTES = 4096;
 
 struct UmmaParams {
@@ -48,6 +50,7 @@ struct UmmaParams {
   int raw_stages, a_stages, x_stages;   // ring depths: raw bytes, expanded A tiles, activation tiles
   int stages_per_split, ksplit, ncg, mtiles;
   int tmem_cols;
+  uint32_t emask_lo, emask_hi, emagic;   // nibble expansion: (bits & mask) | emagic
 };
 
 template <typename T>
@@ -56,6 +59,25 @@ __global__ void xsum_kernel(const T* __restrict__ x, float* __restrict__ xsum, i
   const int64_t m = blockIdx.x;
   float s = 0.f;
   for (int64_t k = threadIdx.x; k < K; k += blockDim.x) s += to_f32<T>(x[m * K + k]);
+  for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+  if ((threadIdx.x & 31) == 0) part[threadIdx.x >> 5] = s;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float t = 0.f;
+    for (int w = 0; w < (int)(blockDim.x >> 5); ++w) t += part[w];
+    xsum[m] = t;
+  }
+}
+
+// sum over k of the two bf16 planes of a split fp32 activation row: exactly what the MMAs see, so that
+// the offset of the expanded codes cancels exactly in the epilogue
+__global__ void xsum_planes_kernel(const __nv_bfloat16* __restrict__ P0, const __nv_bfloat16* __restrict__ P1,
+                                   float* __restrict__ xsum, int64_t K) {
+  __shared__ float part[8];
+  const int64_t m = blockIdx.x;
+  float s = 0.f;
+  for (int64_t k = threadIdx.x; k < K; k += blockDim.x)
+    s += __bfloat162float(P0[m * K + k]) + __bfloat162float(P1[m * K + k]);
   for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
   if ((threadIdx.x & 31) == 0) part[threadIdx.x >> 5] = s;
   __syncthreads();
@@ -79,21 +101,28 @@ __global__ void split_x_bf16_kernel(const float* __restrict__ X, __nv_bfloat16* 
 
 // 8 codes of one 32-bit word (4 channels x {k even, k odd}) -> four 2-channel registers.
 // e02 / e13: k even, channels (0,2) / (1,3);  o02 / o13: k odd.
+// The integer / logic pipe is the scarce one (half rate), so the constants come from kernel
+// parameters (a mask and an exponent pattern as two immediates would cost two logic instructions
+// per register) and the magic offset is removed on the FMA pipe:
+//   f16:  0x6400 | c = 1024 + c -> subtract 1024;   0x6400 | c << 4 = 1024 + 16 c -> * 1/16 - 64
+//   bf16: 0x4300 | c = 128 + c  -> subtract 128 (a nibble does not fit above bit 3 of a bf16 mantissa
+//         without reaching the exponent, so the high nibbles are shifted down)
 template <int FMT>
-__device__ __forceinline__ void expand_word(uint32_t w, uint32_t& e02, uint32_t& e13, uint32_t& o02, uint32_t& o13) {
-  if (FMT == 0) {   // f16: 0x6400 | c = 1024 + c ; 0x6400 | (c << 4) = 1024 + 16 c
+__device__ __forceinline__ void expand_word(uint32_t w, uint32_t mask_lo, uint32_t mask_hi, uint32_t magic,
+                                            uint32_t& e02, uint32_t& e13, uint32_t& o02, uint32_t& o13) {
+  if (FMT == 0) {
     const uint32_t w8 = w >> 8;
-    uint32_t a = (w & 0x000F000Fu) | 0x64006400u, b = (w8 & 0x000F000Fu) | 0x64006400u;
-    uint32_t c = (w & 0x00F000F0u) | 0x64006400u, d = (w8 & 0x00F000F0u) | 0x64006400u;
+    uint32_t a = (w & mask_lo) | magic, b = (w8 & mask_lo) | magic;
+    uint32_t c = (w & mask_hi) | magic, d = (w8 & mask_hi) | magic;
     const __half2 k1024 = __half2half2(__float2half_rn(1024.f));
     const __half2 k16th = __half2half2(__float2half_rn(0.0625f)), k64 = __half2half2(__float2half_rn(-64.f));
     __half2 ra = __hsub2(*reinterpret_cast<__half2*>(&a), k1024), rb = __hsub2(*reinterpret_cast<__half2*>(&b), k1024);
     __half2 rc = __hfma2(*reinterpret_cast<__half2*>(&c), k16th, k64), rd = __hfma2(*reinterpret_cast<__half2*>(&d), k16th, k64);
     e02 = *reinterpret_cast<uint32_t*>(&ra); e13 = *reinterpret_cast<uint32_t*>(&rb);
     o02 = *reinterpret_cast<uint32_t*>(&rc); o13 = *reinterpret_cast<uint32_t*>(&rd);
-  } else {          // bf16: 0x4300 | c = 128 + c
-    uint32_t a = (w & 0x000F000Fu) | 0x43004300u, b = ((w >> 8) & 0x000F000Fu) | 0x43004300u;
-    uint32_t c = ((w >> 4) & 0x000F000Fu) | 0x43004300u, d = ((w >> 12) & 0x000F000Fu) | 0x43004300u;
+  } else {
+    uint32_t a = (w & mask_lo) | magic, b = ((w >> 8) & mask_lo) | magic;
+    uint32_t c = ((w >> 4) & mask_lo) | magic, d = ((w >> 12) & mask_lo) | magic;
     const __nv_bfloat162 k128 = __float2bfloat162_rn(128.f);
     __nv_bfloat162 ra = __hsub2(*reinterpret_cast<__nv_bfloat162*>(&a), k128);
     __nv_bfloat162 rb = __hsub2(*reinterpret_cast<__nv_bfloat162*>(&b), k128);
@@ -112,6 +141,7 @@ w4_umma_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   const int x_plane_bytes = p.NT * 128;
+  const int nt0 = min(p.NT, 256), nt1 = p.NT - nt0;      // tokens of the first / second accumulator
   const int x_stage_bytes = x_plane_bytes * p.planes;
   uint8_t* raw_ring = smem;
   const int RAW_ST = p.raw_stages, A_ST = p.a_stages;
@@ -149,6 +179,7 @@ w4_umma_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__
     fence_barrier_init();
     prefetch_tensormap(&wmap);
     prefetch_tensormap(&xmap0);
+    if (p.planes > 1) prefetch_tensormap(&xmap1);
   }
   if (warp == 1) {
     tmem_alloc(tmem_slot, (uint32_t)p.tmem_cols);
@@ -160,20 +191,17 @@ w4_umma_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__
   const uint32_t tmem_acc = *tmem_slot;
 
   if (warp == 0) {
-    // ===================== TMA producer =====================
+    // ===================== TMA producer, packed weights =====================
+    // Runs ahead of everything else by the whole raw ring (up to 64 KB per SM), independent of the
+    // activation ring: at small M the kernel lives on the weight bytes it has in flight.
     if (lane == 0) {
       int issued = 0;
       for (int i = 0; i < nst; ++i) {
-        const int rs = i % RAW_ST, xs = i % p.x_stages;
+        const int rs = i % RAW_ST;
         const int64_t stage = st_begin + i;
         if (i >= RAW_ST && !mbar_wait(&raw_empty[rs], ((i / RAW_ST) & 1) ^ 1, abort_flag)) break;
         mbar_expect_tx(&raw_full[rs], U_RAW_BYTES);
         tma_load_2d(raw_ring + rs * U_RAW_BYTES, &wmap, (int)cbase, (int)(stage * 32), &raw_full[rs]);
-        if (i >= p.x_stages && !mbar_wait(&x_empty[xs], ((i / p.x_stages) & 1) ^ 1, abort_flag)) break;
-        mbar_expect_tx(&x_full[xs], (uint32_t)x_stage_bytes);
-        tma_load_2d(x_ring + xs * x_stage_bytes, &xmap0, (int)(stage * U_STAGE_K), (int)m0, &x_full[xs]);
-        if (p.planes > 1)
-          tma_load_2d(x_ring + xs * x_stage_bytes + x_plane_bytes, &xmap1, (int)(stage * U_STAGE_K), (int)m0, &x_full[xs]);
         issued = i + 1;
       }
       if (*abort_flag) {
@@ -181,6 +209,25 @@ w4_umma_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__
           const long long t0 = clock64();
           while (!mbar_try_wait(&raw_full[i % RAW_ST], (i / RAW_ST) & 1) && clock64() - t0 < 20000000LL) {}
         }
+      }
+    }
+  } else if (warp == U_XWARP) {
+    // ===================== TMA producer, activation tiles =====================
+    if (lane == 0) {
+      int issued = 0;
+      for (int i = 0; i < nst; ++i) {
+        const int xs = i % p.x_stages;
+        const int64_t stage = st_begin + i;
+        if (i >= p.x_stages && !mbar_wait(&x_empty[xs], ((i / p.x_stages) & 1) ^ 1, abort_flag)) break;
+        mbar_expect_tx(&x_full[xs], (uint32_t)x_stage_bytes);
+        tma_load_2d(x_ring + xs * x_stage_bytes, &xmap0, (int)(stage * U_STAGE_K), (int)m0, &x_full[xs]);
+        if (nt1 > 0)     // second box of 256 token rows (one plane only at this size)
+          tma_load_2d(x_ring + xs * x_stage_bytes + 256 * 128, &xmap0, (int)(stage * U_STAGE_K), (int)m0 + 256, &x_full[xs]);
+        if (p.planes > 1)
+          tma_load_2d(x_ring + xs * x_stage_bytes + x_plane_bytes, &xmap1, (int)(stage * U_STAGE_K), (int)m0, &x_full[xs]);
+        issued = i + 1;
+      }
+      if (*abort_flag) {
         for (int i = max(0, issued - p.x_stages); i < issued; ++i) {
           const long long t0 = clock64();
           while (!mbar_try_wait(&x_full[i % p.x_stages], (i / p.x_stages) & 1) && clock64() - t0 < 20000000LL) {}
@@ -190,7 +237,8 @@ w4_umma_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__
   } else if (warp == 1) {
     // ===================== MMA issuer =====================
     if (lane == 0) {
-      const uint32_t idesc = make_idesc_f16(p.fmt, /*a M-major*/ 1, /*b K-major*/ 0, U_COLS, p.NT);
+      const uint32_t idesc = make_idesc_f16(p.fmt, /*a M-major*/ 1, /*b K-major*/ 0, U_COLS, nt0);
+      const uint32_t idesc1 = make_idesc_f16(p.fmt, 1, 0, U_COLS, nt1 > 0 ? nt1 : 16);
       bool ok = true;
       for (int i = 0; i < nst && ok; ++i) {
         const int as = i % A_ST, xs = i % p.x_stages;
@@ -206,6 +254,10 @@ w4_umma_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__
           for (int pl = 0; pl < p.planes; ++pl) {
             const uint64_t db = make_desc_sw128(x_base + pl * x_plane_bytes + k16 * 32, 16, 1024);
             mma_f16_ss(tmem_acc, da, db, idesc, (i > 0 || k16 > 0 || pl > 0) ? 1u : 0u);
+          }
+          if (nt1 > 0) {
+            const uint64_t db1 = make_desc_sw128(x_base + 256 * 128 + k16 * 32, 16, 1024);
+            mma_f16_ss(tmem_acc + 256, da, db1, idesc1, (i > 0 || k16 > 0) ? 1u : 0u);
           }
         }
         mma_commit(&a_empty[as]);
@@ -244,10 +296,10 @@ w4_umma_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__
 #pragma unroll
       for (int u = 0; u < 8; ++u) {
         uint32_t e[8], o[8];     // k even / k odd: 16 channels each, in expanded order
-        expand_word<FMT>(v[u].x, e[0], e[1], o[0], o[1]);
-        expand_word<FMT>(v[u].y, e[2], e[3], o[2], o[3]);
-        expand_word<FMT>(v[u].z, e[4], e[5], o[4], o[5]);
-        expand_word<FMT>(v[u].w, e[6], e[7], o[6], o[7]);
+        expand_word<FMT>(v[u].x, p.emask_lo, p.emask_hi, p.emagic, e[0], e[1], o[0], o[1]);
+        expand_word<FMT>(v[u].y, p.emask_lo, p.emask_hi, p.emagic, e[2], e[3], o[2], o[3]);
+        expand_word<FMT>(v[u].z, p.emask_lo, p.emask_hi, p.emagic, e[4], e[5], o[4], o[5]);
+        expand_word<FMT>(v[u].w, p.emask_lo, p.emask_hi, p.emagic, e[6], e[7], o[6], o[7]);
         const int ke = 2 * (4 * u + rsub), ko = ke + 1;
         *reinterpret_cast<uint4*>(grp + ke * 128 + (((ch0 + 0) ^ (ke & 7)) << 4)) = make_uint4(e[0], e[1], e[2], e[3]);
         *reinterpret_cast<uint4*>(grp + ke * 128 + (((ch0 + 1) ^ (ke & 7)) << 4)) = make_uint4(e[4], e[5], e[6], e[7]);
@@ -349,24 +401,35 @@ UmmaPlan plan_w4_umma(int64_t M, int64_t N, int64_t K, int x_dtype) {
   const int64_t max_nt = pl.planes == 2 ? 128 : 256;
   const int64_t per_tile = std::min<int64_t>(M, max_nt);
   pl.NT = (int)(cdiv(per_tile, 16) * 16);
+  // above 256 tokens a CTA takes 512 (two 128 x 256 accumulators = all of TMEM): every expanded stage
+  // then feeds twice the tensor work, and the expansion is what bounds the kernel at large M
+  if (pl.planes == 1 && M > 256) pl.NT = 512;
   pl.mtiles = (int)cdiv(M, pl.NT);
   pl.ncg = (int)cdiv(N, U_COLS);
-  pl.tmem_cols = pl.NT <= 32 ? 32 : pl.NT <= 64 ? 64 : pl.NT <= 128 ? 128 : 256;
+  pl.tmem_cols = pl.NT <= 32 ? 32 : pl.NT <= 64 ? 64 : pl.NT <= 128 ? 128 : pl.NT <= 256 ? 256 : 512;
   const size_t x_stage = (size_t)pl.NT * 128 * pl.planes;
   // ring depths (<= 224 KB in all): raw and expanded-A rings hold one stage per active expansion warp
   // (8, or 4 when the activation tiles are large and the tensor pipe is the bound anyway)
-  if (x_stage <= (8u << 10))       { pl.raw_stages = 8; pl.a_stages = 8; pl.x_stages = 8; }
-  else if (x_stage <= (16u << 10)) { pl.raw_stages = 8; pl.a_stages = 8; pl.x_stages = 4; }
-  else                             { pl.raw_stages = 4; pl.a_stages = 4; pl.x_stages = 4; }
+  // Ring depths.  What bounds the kernel below a few hundred tokens is the activation ring: a slot is
+  // free again only when the MMAs that read it have completed and is full again one L2 round trip later,
+  // so the ring gets all the shared memory that the other two do not need: four expanded stages
+  // (four expansion warps active; a slot belongs to one warp) and eight raw stages.
+  pl.raw_stages = 8; pl.a_stages = 4;
+  {
+    const size_t budget = (size_t)(224u << 10) - (size_t)pl.raw_stages * U_RAW_BYTES - (size_t)pl.a_stages * U_A_BYTES;
+    pl.x_stages = (int)std::max<size_t>(2, std::min<size_t>(U_MAX_ST, budget / x_stage));
+  }
   pl.smem_bytes = (size_t)pl.raw_stages * U_RAW_BYTES + (size_t)pl.a_stages * U_A_BYTES + pl.x_stages * x_stage +
-                  1024 + 512;
+                  1024 /*alignment*/ + 1024 /*barriers*/;
   const int64_t total_stages = cdiv(K, U_STAGE_K);
   const int64_t base = (int64_t)pl.ncg * pl.mtiles;
   const int sms = sm_count();
   int64_t kmax = std::max<int64_t>(1, total_stages / 8);          // at least 8 stages per CTA
   if (base > (int64_t)(U_TICKET_BYTES / sizeof(int))) kmax = 1;
-  // Split-K only when the tiles alone cannot occupy the SMs: the slice reduction costs
-  // ksplit x tokens reads per epilogue thread, which is only cheap for few tokens.
+  // Split-K only when the tiles alone cannot occupy the SMs.  A CTA costs about 13 us around its
+  // stages (TMEM allocation, first loads, epilogue, slice exchange), so short CTAs lose more than
+  // a partly empty last wave does: measured at 8192 x 28672, M = 128, one wave and a half of long
+  // CTAs takes 233 us, five slices per tile 313 us.
   if (2 * base >= sms) kmax = 1;
   if (pl.NT > 64) kmax = std::min<int64_t>(kmax, 4);
   kmax = std::min<int64_t>(kmax, 64);
@@ -430,20 +493,24 @@ int launch_w4_umma(const UmmaPlan& pl, const void* x, int x_dtype, const uint8_t
     plane0 = P0; plane1 = P1;
   }
   p.partials = (float*)w;
-  if (x_dtype == JGQ_F32)      xsum_kernel<float><<<(unsigned)M, 256, 0, s>>>((const float*)x, xsum, K);
+  if (x_dtype == JGQ_F32)
+    xsum_planes_kernel<<<(unsigned)M, 256, 0, s>>>((const __nv_bfloat16*)plane0, (const __nv_bfloat16*)plane1, xsum, K);
   else if (x_dtype == JGQ_F16) xsum_kernel<__half><<<(unsigned)M, 256, 0, s>>>((const __half*)x, xsum, K);
   else                         xsum_kernel<__nv_bfloat16><<<(unsigned)M, 256, 0, s>>>((const __nv_bfloat16*)x, xsum, K);
   JGQ_LAUNCHED();
   CUtensorMap wmap, x0, x1;
   int rc = encode_tmap_2d_u8(&wmap, packed, (uint64_t)N, (uint64_t)(K / 2), (uint64_t)N, U_COLS, 32, 0);
   if (rc) return rc;
-  rc = encode_tmap_2d_b16(&x0, plane0, (uint64_t)K, (uint64_t)M, (uint64_t)K * 2, 64, (uint32_t)pl.NT);
+  const uint32_t box_rows = (uint32_t)std::min(pl.NT, 256);
+  rc = encode_tmap_2d_b16(&x0, plane0, (uint64_t)K, (uint64_t)M, (uint64_t)K * 2, 64, box_rows);
   if (rc) return rc;
-  rc = encode_tmap_2d_b16(&x1, plane1, (uint64_t)K, (uint64_t)M, (uint64_t)K * 2, 64, (uint32_t)pl.NT);
+  rc = encode_tmap_2d_b16(&x1, plane1, (uint64_t)K, (uint64_t)M, (uint64_t)K * 2, 64, box_rows);
   if (rc) return rc;
   p.packed = packed; p.zero = zero; p.scale = scale; p.out = out; p.xsum = xsum;
   p.M = M; p.N = N; p.K = K; p.NT = pl.NT; p.planes = pl.planes;
   p.fmt = (x_dtype == JGQ_F16) ? 0 : 1;
+  p.emask_lo = 0x000F000Fu; p.emask_hi = 0x00F000F0u;
+  p.emagic = p.fmt == 0 ? 0x64006400u : 0x43004300u;
   p.raw_stages = pl.raw_stages; p.a_stages = pl.a_stages; p.x_stages = pl.x_stages; p.stages_per_split = pl.stages_per_split; p.ksplit = pl.ksplit;
   p.ncg = pl.ncg; p.mtiles = pl.mtiles; p.tmem_cols = pl.tmem_cols;
   const bool zf32 = zs_dtype == JGQ_F32;

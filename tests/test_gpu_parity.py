@@ -333,7 +333,8 @@ def _check_mm(G, qm, x, transpose, tol=1e-2):
 
 
 @pytest.mark.parametrize('transpose', [False, True])
-@pytest.mark.parametrize('M,N,K', [(137, 909, 256), (32, 1024, 2048), (37, 32000, 5120)])
+@pytest.mark.parametrize('M,N,K', [(137, 909, 256), (32, 1024, 2048), (37, 32000, 5120), (300, 1024, 1024),
+                                   (700, 384, 4096)])
 def test_matmul_reference_kernel_shapes(G, M, N, K, transpose):
     # reference test_kernel.py:8-41, fp32 activations
     rng = np.random.default_rng(60 + M)
@@ -342,7 +343,7 @@ def test_matmul_reference_kernel_shapes(G, M, N, K, transpose):
     _check_mm(G, qm, x, transpose)
 
 
-@pytest.mark.parametrize('M', [1, 2, 8, 16, 17, 40])
+@pytest.mark.parametrize('M', [1, 2, 8, 16, 17, 40, 300, 600])
 @pytest.mark.parametrize('x_dtype', ['float16', 'bfloat16', 'float32'])
 def test_matmul_decode_sizes(G, M, x_dtype):
     rng = np.random.default_rng(70 + M)
