@@ -154,26 +154,31 @@ hessian_umma_kernel(const __grid_constant__ CUtensorMap map0, const __grid_const
 
   if (warp == 0) {
     // ===================== TMA producer =====================
-    if (lane == 0) {
+    {
       const uint32_t stage_tx = (uint32_t)(p.planes * (groups_a + groups_b) * HT_BOX_BYTES);
       int issued = 0;
+      int st = 0;                 // ring slot and phase parity, stepped by hand: the depth is a run-time
+      uint32_t ph = 0;            // value and a division per stage would sit on this lane's critical path
       for (int kc = 0; kc < nchunks; ++kc) {
-        const int st = kc % nst;
-        if (kc >= nst && !mbar_wait(&empty_bar[st], ((kc / nst) & 1) ^ 1, abort_flag)) break;
-        mbar_expect_tx(&full_bar[st], stage_tx);
-        const int tok = tok0 + kc * HT_BK;
-        uint8_t* sb = smem + st * stage_bytes;
-        for (int pl = 0; pl < p.planes; ++pl) {
-          const CUtensorMap* m = pl == 0 ? &map0 : &map1;
-          uint8_t* pb = sb + pl * plane_bytes;
-          for (int g = 0; g < groups_a; ++g)
-            tma_load_2d(pb + g * HT_BOX_BYTES, m, row0 + 64 * g, tok, &full_bar[st]);
-          for (int g = 0; g < groups_b; ++g)
-            tma_load_2d(pb + (a_boxes + g) * HT_BOX_BYTES, m, col0 + 64 * g, tok, &full_bar[st]);
+        if (kc >= nst && !__all_sync(0xffffffffu, mbar_wait(&empty_bar[st], ph ^ 1, abort_flag))) break;
+        if (elect_one()) {
+          mbar_expect_tx(&full_bar[st], stage_tx);
+          const int tok = tok0 + kc * HT_BK;
+          uint8_t* sb = smem + st * stage_bytes;
+          for (int pl = 0; pl < p.planes; ++pl) {
+            const CUtensorMap* m = pl == 0 ? &map0 : &map1;
+            uint8_t* pb = sb + pl * plane_bytes;
+            for (int g = 0; g < groups_a; ++g)
+              tma_load_2d(pb + g * HT_BOX_BYTES, m, row0 + 64 * g, tok, &full_bar[st]);
+            for (int g = 0; g < groups_b; ++g)
+              tma_load_2d(pb + (a_boxes + g) * HT_BOX_BYTES, m, col0 + 64 * g, tok, &full_bar[st]);
+          }
         }
+        __syncwarp();
         issued = kc + 1;
+        if (++st == nst) { st = 0; ph ^= 1; }
       }
-      if (*abort_flag) {
+      if (*abort_flag && lane == 0) {
         // let copies that are still in flight land before the CTA gives its shared memory back
         for (int kc = max(0, issued - nst); kc < issued; ++kc) {
           const long long t0 = clock64();
@@ -183,37 +188,49 @@ hessian_umma_kernel(const __grid_constant__ CUtensorMap map0, const __grid_const
     }
   } else if (warp == 1) {
     // ===================== MMA issuer =====================
-    if (lane == 0) {
+    {
       const uint32_t idesc0 = make_idesc_f16(p.fmt, 1, 1, HT_M, nb0);
       const uint32_t idesc1 = make_idesc_f16(p.fmt, 1, 1, HT_M, nb);
       const int nterms = p.planes > 1 ? 3 : 1;
       const int b_box = diag ? 0 : a_boxes;       // first box of the B operand inside a plane
+      // A shared-memory descriptor is a constant plus the start address / 16 in its low bits, so the
+      // descriptors of a stage are one addition away from the stage's base: the issuing lane runs a
+      // dependent instruction chain, and every instruction saved here is tensor time gained.
+      const uint64_t desc0 = make_desc_sw128(0, HT_BOX_BYTES, 1024);
+      const uint32_t smem0 = smem_u32(smem);
+      const uint32_t off_b = (uint32_t)(b_box * HT_BOX_BYTES) >> 4, off_a1 = (uint32_t)(2 * HT_BOX_BYTES) >> 4;
+      const uint32_t off_plane = (uint32_t)plane_bytes >> 4;
       bool ok = true;
+      int st = 0;
+      uint32_t ph = 0;
+      uint32_t sb16 = smem0 >> 4;                   // stage base / 16
+      const uint32_t stage16 = (uint32_t)stage_bytes >> 4;
       for (int kc = 0; kc < nchunks && ok; ++kc) {
-        const int st = kc % nst;
-        ok = mbar_wait(&full_bar[st], (kc / nst) & 1, abort_flag);
+        ok = __all_sync(0xffffffffu, mbar_wait(&full_bar[st], ph, abort_flag));
         if (!ok) break;
         tc_fence_after();
-        const uint32_t sb = smem_u32(smem + st * stage_bytes);
+        if (elect_one()) {
 #pragma unroll
         for (int k16 = 0; k16 < HT_BK / 16; ++k16) {
-          for (int t = 0; t < nterms; ++t) {
-            const int pa = (t == 2) ? 1 : 0, pbn = (t == 1) ? 1 : 0;     // (0,0) (0,1) (1,0)
-            const uint32_t acc_on = (kc > 0 || k16 > 0 || t > 0) ? 1u : 0u;
-            const uint64_t db = make_desc_sw128(sb + pbn * plane_bytes + b_box * HT_BOX_BYTES + k16 * 2048,
-                                                HT_BOX_BYTES, 1024);
-            const uint64_t da0 = make_desc_sw128(sb + pa * plane_bytes + k16 * 2048, HT_BOX_BYTES, 1024);
-            mma_f16_ss(tmem_acc, da0, db, idesc0, acc_on);
-            if (two) {
-              const uint64_t da1 = make_desc_sw128(sb + pa * plane_bytes + 2 * HT_BOX_BYTES + k16 * 2048,
-                                                   HT_BOX_BYTES, 1024);
-              mma_f16_ss(tmem_acc + HT_N, da1, db, idesc1, acc_on);
+#pragma unroll
+          for (int t = 0; t < 3; ++t) {
+            if (t < nterms) {
+              const uint32_t pa = (t == 2) ? off_plane : 0u, pbn = (t == 1) ? off_plane : 0u;   // (0,0) (0,1) (1,0)
+              const uint32_t acc_on = (kc > 0 || k16 > 0 || t > 0) ? 1u : 0u;
+              const uint64_t db = desc0 + (sb16 + pbn + off_b + (uint32_t)(k16 * 2048 >> 4));
+              const uint64_t da0 = desc0 + (sb16 + pa + (uint32_t)(k16 * 2048 >> 4));
+              mma_f16_ss(tmem_acc, da0, db, idesc0, acc_on);
+              if (two) mma_f16_ss(tmem_acc + HT_N, da0 + off_a1, db, idesc1, acc_on);
             }
           }
         }
         mma_commit(&empty_bar[st]);     // frees the stage once these MMAs have read it
+        }
+        __syncwarp();
+        if (++st == nst) { st = 0; ph ^= 1; sb16 = smem0 >> 4; } else { sb16 += stage16; }
       }
-      if (ok) mma_commit(acc_bar);
+      if (ok && elect_one()) mma_commit(acc_bar);
+      __syncwarp();
     }
   } else {
     // ===================== epilogue: TMEM -> global =====================

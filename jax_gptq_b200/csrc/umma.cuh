@@ -40,6 +40,16 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 
 constexpr long long kWaitBudgetCycles = 4000000000LL;   // ~2 s at 2 GHz
 
+// One lane of a converged warp.  The pipeline roles run their loops with the whole warp (waits included) and
+// put only the TMA / tcgen05 instructions under this: in code that the compiler knows to be executed by a
+// full warp the descriptors live in uniform registers; behind `if (lane == 0)` every such instruction is
+// wrapped in a scalarisation sequence that costs about 200 cycles.
+__device__ __forceinline__ bool elect_one() {
+  uint32_t pred;
+  asm volatile("{\n\t.reg .pred p;\n\telect.sync _|p, 0xffffffff;\n\tselp.u32 %0, 1, 0, p;\n\t}" : "=r"(pred));
+  return pred != 0;
+}
+
 // Waits for the phase with the given parity.  Returns false (and raises *abort) when the
 // budget runs out or another role already aborted.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort) {

@@ -324,7 +324,7 @@ static int launch_tb(const void* x, const uint8_t* packed, const void* zero, con
 }
 
 constexpr int64_t kStreamRows = 16;          // token rows of one pass of the streaming kernel
-constexpr int64_t kStreamPassesMaxM = 48;    // up to three passes before the tensor-path kernel takes over
+constexpr int64_t kStreamPassesMaxM = 32;    // two passes (120 us at 8192 x 28672) still beat the tensor-path kernel (128 us at M = 64)
 
 static int w4_path_override() {        // JGQ_W4_PATH=direct: direct-load decode kernel; =mma: no tcgen05 either
   static int v = -1;
@@ -392,8 +392,8 @@ extern "C" int jgq_w4_matmul(const void* x, int x_dtype, const uint8_t* packed,
     const StreamPlan sp = plan_w4_stream(M, N, K);
     if (sp.use && aligned(packed, 16)) return launch_w4_stream(sp, x, x_dtype, packed, zero, scale, zs_dtype, out, M, N, K, ws, s);
     // A few more tokens than one pass of the streaming kernel takes: one pass per 16 token rows (60 us
-    // each at 8192 x 28672) still beats the tensor-path kernel, which needs about 250 us for any M
-    // up to 256 on that shape.  The passes run one after the other on the stream and share the workspace.
+    // each at 8192 x 28672) still beats the tensor-path kernel there.  The passes run one after the other
+    // on the stream and share the workspace.
     if (M > kStreamRows && M <= kStreamPassesMaxM && aligned(packed, 16)) {
       const size_t elt = x_dtype == JGQ_F32 ? 4 : 2;
       bool ok = true;

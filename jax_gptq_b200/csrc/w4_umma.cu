@@ -133,6 +133,16 @@ __device__ __forceinline__ void expand_word(uint32_t w, uint32_t mask_lo, uint32
   }
 }
 
+#ifdef JGQ_UMMA_TRACE
+// per-stage timestamps of CTA (0, 0, 0): [kind][stage], kinds: 0 raw issued, 1 x issued, 2 raw landed (expansion
+// warp), 3 expanded tile published, 4 MMA thread has both operands, 5 MMAs issued
+__device__ unsigned long long g_utrace[10 * 256];
+__device__ __forceinline__ unsigned long long ugtime() { return (unsigned long long)clock64(); }   // SM cycles: cheap to read, one SM only
+#define UTRACE(kind, i) do { if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && (i) < 256) g_utrace[(kind) * 256 + (i)] = ugtime(); } while (0)
+#else
+#define UTRACE(kind, i) do {} while (0)
+#endif
+
 template <typename XT, typename ZST, int FMT>
 __global__ void __launch_bounds__(U_THREADS, 1)
 w4_umma_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__ CUtensorMap xmap0,
@@ -169,8 +179,9 @@ w4_umma_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__
 
   if (threadIdx.x == 0) {
     for (int i = 0; i < U_MAX_ST; ++i) {
-      mbar_init(&raw_full[i], 1); mbar_init(&raw_empty[i], 1);     // a stage belongs to one expansion warp
-      mbar_init(&a_full[i], 1); mbar_init(&a_empty[i], 1);
+      // a stage belongs to one expansion warp, or to a pair of them when the A ring has four slots
+      mbar_init(&raw_full[i], 1); mbar_init(&raw_empty[i], U_DQ_WARPS / A_ST);
+      mbar_init(&a_full[i], U_DQ_WARPS / A_ST); mbar_init(&a_empty[i], 1);
       mbar_init(&x_full[i], 1); mbar_init(&x_empty[i], 1);
     }
     mbar_init(acc_bar, 1);
@@ -194,17 +205,24 @@ w4_umma_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__
     // ===================== TMA producer, packed weights =====================
     // Runs ahead of everything else by the whole raw ring (up to 64 KB per SM), independent of the
     // activation ring: at small M the kernel lives on the weight bytes it has in flight.
-    if (lane == 0) {
+    // The whole warp walks the ring; one elected lane issues (see elect_one).
+    {
       int issued = 0;
+      int rs = 0;                 // ring slot and phase parity are stepped by hand in every role: the depths
+      uint32_t rph = 0;           // are run-time values, and a division per stage costs hundreds of cycles
       for (int i = 0; i < nst; ++i) {
-        const int rs = i % RAW_ST;
         const int64_t stage = st_begin + i;
-        if (i >= RAW_ST && !mbar_wait(&raw_empty[rs], ((i / RAW_ST) & 1) ^ 1, abort_flag)) break;
-        mbar_expect_tx(&raw_full[rs], U_RAW_BYTES);
-        tma_load_2d(raw_ring + rs * U_RAW_BYTES, &wmap, (int)cbase, (int)(stage * 32), &raw_full[rs]);
+        if (i >= RAW_ST && !__all_sync(0xffffffffu, mbar_wait(&raw_empty[rs], rph ^ 1, abort_flag))) break;
+        if (elect_one()) {
+          mbar_expect_tx(&raw_full[rs], U_RAW_BYTES);
+          tma_load_2d(raw_ring + rs * U_RAW_BYTES, &wmap, (int)cbase, (int)(stage * 32), &raw_full[rs]);
+          UTRACE(0, i);
+        }
+        __syncwarp();
         issued = i + 1;
+        if (++rs == RAW_ST) { rs = 0; rph ^= 1; }
       }
-      if (*abort_flag) {
+      if (*abort_flag && lane == 0) {
         for (int i = max(0, issued - RAW_ST); i < issued; ++i) {
           const long long t0 = clock64();
           while (!mbar_try_wait(&raw_full[i % RAW_ST], (i / RAW_ST) & 1) && clock64() - t0 < 20000000LL) {}
@@ -213,21 +231,27 @@ w4_umma_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__
     }
   } else if (warp == U_XWARP) {
     // ===================== TMA producer, activation tiles =====================
-    if (lane == 0) {
+    {
       int issued = 0;
+      int xs = 0;
+      uint32_t xph = 0;
       for (int i = 0; i < nst; ++i) {
-        const int xs = i % p.x_stages;
         const int64_t stage = st_begin + i;
-        if (i >= p.x_stages && !mbar_wait(&x_empty[xs], ((i / p.x_stages) & 1) ^ 1, abort_flag)) break;
-        mbar_expect_tx(&x_full[xs], (uint32_t)x_stage_bytes);
-        tma_load_2d(x_ring + xs * x_stage_bytes, &xmap0, (int)(stage * U_STAGE_K), (int)m0, &x_full[xs]);
-        if (nt1 > 0)     // second box of 256 token rows (one plane only at this size)
-          tma_load_2d(x_ring + xs * x_stage_bytes + 256 * 128, &xmap0, (int)(stage * U_STAGE_K), (int)m0 + 256, &x_full[xs]);
-        if (p.planes > 1)
-          tma_load_2d(x_ring + xs * x_stage_bytes + x_plane_bytes, &xmap1, (int)(stage * U_STAGE_K), (int)m0, &x_full[xs]);
+        if (i >= p.x_stages && !__all_sync(0xffffffffu, mbar_wait(&x_empty[xs], xph ^ 1, abort_flag))) break;
+        if (elect_one()) {
+          mbar_expect_tx(&x_full[xs], (uint32_t)x_stage_bytes);
+          tma_load_2d(x_ring + xs * x_stage_bytes, &xmap0, (int)(stage * U_STAGE_K), (int)m0, &x_full[xs]);
+          if (nt1 > 0)     // second box of 256 token rows (one plane only at this size)
+            tma_load_2d(x_ring + xs * x_stage_bytes + 256 * 128, &xmap0, (int)(stage * U_STAGE_K), (int)m0 + 256, &x_full[xs]);
+          if (p.planes > 1)
+            tma_load_2d(x_ring + xs * x_stage_bytes + x_plane_bytes, &xmap1, (int)(stage * U_STAGE_K), (int)m0, &x_full[xs]);
+          UTRACE(1, i);
+        }
+        __syncwarp();
         issued = i + 1;
+        if (++xs == p.x_stages) { xs = 0; xph ^= 1; }
       }
-      if (*abort_flag) {
+      if (*abort_flag && lane == 0) {
         for (int i = max(0, issued - p.x_stages); i < issued; ++i) {
           const long long t0 = clock64();
           while (!mbar_try_wait(&x_full[i % p.x_stages], (i / p.x_stages) & 1) && clock64() - t0 < 20000000LL) {}
@@ -236,34 +260,45 @@ w4_umma_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__
     }
   } else if (warp == 1) {
     // ===================== MMA issuer =====================
-    if (lane == 0) {
+    {
       const uint32_t idesc = make_idesc_f16(p.fmt, /*a M-major*/ 1, /*b K-major*/ 0, U_COLS, nt0);
       const uint32_t idesc1 = make_idesc_f16(p.fmt, 1, 0, U_COLS, nt1 > 0 ? nt1 : 16);
+      // Descriptors are a constant plus (start address / 16) in the low bits: one addition per MMA.
+      const uint64_t desc_a0 = make_desc_sw128(0, 8192, 1024), desc_b0 = make_desc_sw128(0, 16, 1024);
+      const uint32_t a_ring16 = smem_u32(a_ring) >> 4, x_ring16 = smem_u32(x_ring) >> 4;
+      const uint32_t a_stage16 = (uint32_t)U_A_BYTES >> 4, x_stage16 = (uint32_t)x_stage_bytes >> 4;
+      const uint32_t x_plane16 = (uint32_t)x_plane_bytes >> 4;
       bool ok = true;
+      int as = 0, xs = 0;
+      uint32_t aph = 0, xph = 0;
+      uint32_t a16 = a_ring16, x16 = x_ring16;
       for (int i = 0; i < nst && ok; ++i) {
-        const int as = i % A_ST, xs = i % p.x_stages;
-        ok = mbar_wait(&a_full[as], (i / A_ST) & 1, abort_flag) &&
-             mbar_wait(&x_full[xs], (i / p.x_stages) & 1, abort_flag);
+        ok = __all_sync(0xffffffffu, mbar_wait(&a_full[as], aph, abort_flag) && mbar_wait(&x_full[xs], xph, abort_flag));
         if (!ok) break;
         tc_fence_after();
-        const uint32_t a_base = smem_u32(a_ring + as * U_A_BYTES);
-        const uint32_t x_base = smem_u32(x_ring + xs * x_stage_bytes);
+        if (elect_one()) {
+        UTRACE(4, i);
+        UTRACE(6, i);
 #pragma unroll
         for (int k16 = 0; k16 < U_STAGE_K / 16; ++k16) {
-          const uint64_t da = make_desc_sw128(a_base + k16 * 2048, 8192, 1024);
-          for (int pl = 0; pl < p.planes; ++pl) {
-            const uint64_t db = make_desc_sw128(x_base + pl * x_plane_bytes + k16 * 32, 16, 1024);
-            mma_f16_ss(tmem_acc, da, db, idesc, (i > 0 || k16 > 0 || pl > 0) ? 1u : 0u);
-          }
-          if (nt1 > 0) {
-            const uint64_t db1 = make_desc_sw128(x_base + 256 * 128 + k16 * 32, 16, 1024);
-            mma_f16_ss(tmem_acc + 256, da, db1, idesc1, (i > 0 || k16 > 0) ? 1u : 0u);
-          }
+          const uint64_t da = desc_a0 + (a16 + (uint32_t)(k16 * 2048 >> 4));
+          const uint64_t db = desc_b0 + (x16 + (uint32_t)(k16 * 32 >> 4));
+          mma_f16_ss(tmem_acc, da, db, idesc, (i > 0 || k16 > 0) ? 1u : 0u);
+          if (p.planes > 1) mma_f16_ss(tmem_acc, da, db + x_plane16, idesc, 1u);
+          if (nt1 > 0) mma_f16_ss(tmem_acc + 256, da, db + (uint32_t)(256 * 128 >> 4), idesc1, (i > 0 || k16 > 0) ? 1u : 0u);
         }
+        UTRACE(7, i);
         mma_commit(&a_empty[as]);
+        UTRACE(8, i);
         mma_commit(&x_empty[xs]);
+        UTRACE(5, i);
+        }
+        __syncwarp();
+        if (++as == A_ST) { as = 0; aph ^= 1; a16 = a_ring16; } else { a16 += a_stage16; }
+        if (++xs == p.x_stages) { xs = 0; xph ^= 1; x16 = x_ring16; } else { x16 += x_stage16; }
       }
-      if (ok) mma_commit(acc_bar);
+      if (ok && elect_one()) mma_commit(acc_bar);
+      __syncwarp();
     }
   } else {
     // ===================== nibble expansion (warps 2..9) =====================
@@ -277,24 +312,31 @@ w4_umma_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__
     // A warp always works on the same ring slot (slot = warp index), so it sees every phase of
     // that slot's barriers in order; the ring depths equal the number of active expansion warps.
     const int ndq = A_ST;
-    for (int i = dw; i < nst && dw < ndq; i += ndq) {
-      const int rs = i % RAW_ST, as = i % A_ST;
-      ok = __all_sync(0xffffffffu, mbar_wait(&raw_full[rs], (i / RAW_ST) & 1, abort_flag));
+    const int wps = U_DQ_WARPS / A_ST;   // warps per stage: 1, or 2 (each expands 16 of the 32 byte rows)
+    const int as = dw / wps;             // the warp's A slot never changes
+    const int u_lo = (dw % wps) * (8 / wps), u_hi = u_lo + 8 / wps;
+    int rs = as;                         // raw slot of this warp's next stage (RAW_ST is a multiple of ndq)
+    uint32_t rph = 0, aph = 0;           // phase parities of the raw slot and of the warp's A slot
+    for (int i = as; i < nst; i += ndq) {
+      ok = __all_sync(0xffffffffu, mbar_wait(&raw_full[rs], rph, abort_flag));
       if (!ok) break;
+      if (lane == 0) UTRACE(2, i);
       uint4 v[8];
       const uint8_t* rawp = raw_ring + rs * U_RAW_BYTES + cgp * 16;
 #pragma unroll
-      for (int u = 0; u < 8; ++u) v[u] = *reinterpret_cast<const uint4*>(rawp + (4 * u + rsub) * U_COLS);
+      for (int u = 0; u < 8; ++u)
+        if (u >= u_lo && u < u_hi) v[u] = *reinterpret_cast<const uint4*>(rawp + (4 * u + rsub) * U_COLS);
       __syncwarp();
       if (lane == 0) mbar_arrive(&raw_empty[rs]);
       if (i >= A_ST) {
-        ok = __all_sync(0xffffffffu, mbar_wait(&a_empty[as], ((i / A_ST) & 1) ^ 1, abort_flag));
+        ok = __all_sync(0xffffffffu, mbar_wait(&a_empty[as], aph ^ 1, abort_flag));
         if (!ok) break;
         tc_fence_after();
       }
       uint8_t* grp = a_ring + as * U_A_BYTES + ngroup * 8192;
 #pragma unroll
       for (int u = 0; u < 8; ++u) {
+        if (u < u_lo || u >= u_hi) continue;
         uint32_t e[8], o[8];     // k even / k odd: 16 channels each, in expanded order
         expand_word<FMT>(v[u].x, p.emask_lo, p.emask_hi, p.emagic, e[0], e[1], o[0], o[1]);
         expand_word<FMT>(v[u].y, p.emask_lo, p.emask_hi, p.emagic, e[2], e[3], o[2], o[3]);
@@ -308,7 +350,10 @@ w4_umma_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__
       }
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
       __syncwarp();
-      if (lane == 0) mbar_arrive(&a_full[as]);
+      if (lane == 0) { mbar_arrive(&a_full[as]); UTRACE(3, i); }
+      aph ^= 1;
+      rs += ndq;
+      if (rs >= RAW_ST) { rs -= RAW_ST; rph ^= 1; }
     }
 
     // ===================== epilogue (warps 2..5) =====================
@@ -410,11 +455,11 @@ UmmaPlan plan_w4_umma(int64_t M, int64_t N, int64_t K, int x_dtype) {
   const size_t x_stage = (size_t)pl.NT * 128 * pl.planes;
   // ring depths (<= 224 KB in all): raw and expanded-A rings hold one stage per active expansion warp
   // (8, or 4 when the activation tiles are large and the tensor pipe is the bound anyway)
-  // Ring depths.  What bounds the kernel below a few hundred tokens is the activation ring: a slot is
-  // free again only when the MMAs that read it have completed and is full again one L2 round trip later,
-  // so the ring gets all the shared memory that the other two do not need: four expanded stages
-  // (four expansion warps active; a slot belongs to one warp) and eight raw stages.
-  pl.raw_stages = 8; pl.a_stages = 4;
+  // Ring depths: eight raw stages; eight expanded stages (one per expansion warp) while the activation
+  // ring still gets two stages of what is left, else four (two warps share a stage); the activation
+  // ring takes the rest.
+  pl.raw_stages = 8;
+  pl.a_stages = ((size_t)(224u << 10) - 8 * U_RAW_BYTES - 8 * U_A_BYTES) / x_stage >= 2 ? 8 : 4;
   {
     const size_t budget = (size_t)(224u << 10) - (size_t)pl.raw_stages * U_RAW_BYTES - (size_t)pl.a_stages * U_A_BYTES;
     pl.x_stages = (int)std::max<size_t>(2, std::min<size_t>(U_MAX_ST, budget / x_stage));
@@ -521,5 +566,11 @@ int launch_w4_umma(const UmmaPlan& pl, const void* x, int x_dtype, const uint8_t
                 : launch_inst<__nv_bfloat16, __half, 1>(pl, p, wmap, x0, x1, s);
   return zf32 ? launch_inst<float, float, 1>(pl, p, wmap, x0, x1, s) : launch_inst<float, __half, 1>(pl, p, wmap, x0, x1, s);
 }
+
+#ifdef JGQ_UMMA_TRACE
+extern "C" int jgq_dbg_utrace(unsigned long long* host) {
+  return (int)cudaMemcpyFromSymbol(host, g_utrace, sizeof(unsigned long long) * 10 * 256);
+}
+#endif
 
 }  // namespace jgq
