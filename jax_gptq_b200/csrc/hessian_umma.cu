@@ -161,7 +161,7 @@ hessian_umma_kernel(const __grid_constant__ CUtensorMap map0, const __grid_const
       uint32_t ph = 0;            // value and a division per stage would sit on this lane's critical path
       for (int kc = 0; kc < nchunks; ++kc) {
         if (kc >= nst && !__all_sync(0xffffffffu, mbar_wait(&empty_bar[st], ph ^ 1, abort_flag))) break;
-        if (elect_one()) {
+        if (lane == 0) {      // a fixed lane: with an elected one the matmul kernel's producers gave wrong sums now and then
           mbar_expect_tx(&full_bar[st], stage_tx);
           const int tok = tok0 + kc * HT_BK;
           uint8_t* sb = smem + st * stage_bytes;

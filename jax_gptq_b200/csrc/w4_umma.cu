@@ -23,6 +23,8 @@
 #include "w4_common.cuh"
 #include "w4_plans.cuh"
 #include <algorithm>
+#include <cstdio>
+#include <cstdlib>
 #include <cstring>
 
 namespace jgq {
@@ -133,6 +135,12 @@ __device__ __forceinline__ void expand_word(uint32_t w, uint32_t mask_lo, uint32
   }
 }
 
+// Who issues inside a converged role warp: the MMA warp elects (that is what makes the issue cheap, see
+// elect_one); the TMA producers use a fixed lane - with an elected one, single CTAs produced wrong sums
+// now and then (1-3 of 250 CTAs per launch at 32000 x 5120), for a reason that was not found.
+#define U_LEADER_PROD (lane == 0)
+#define U_LEADER_MMA elect_one()
+
 #ifdef JGQ_UMMA_TRACE
 // per-stage timestamps of CTA (0, 0, 0): [kind][stage], kinds: 0 raw issued, 1 x issued, 2 raw landed (expansion
 // warp), 3 expanded tile published, 4 MMA thread has both operands, 5 MMAs issued
@@ -179,9 +187,8 @@ w4_umma_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__
 
   if (threadIdx.x == 0) {
     for (int i = 0; i < U_MAX_ST; ++i) {
-      // a stage belongs to one expansion warp, or to a pair of them when the A ring has four slots
-      mbar_init(&raw_full[i], 1); mbar_init(&raw_empty[i], U_DQ_WARPS / A_ST);
-      mbar_init(&a_full[i], U_DQ_WARPS / A_ST); mbar_init(&a_empty[i], 1);
+      mbar_init(&raw_full[i], 1); mbar_init(&raw_empty[i], 1);     // a stage belongs to one expansion warp
+      mbar_init(&a_full[i], 1); mbar_init(&a_empty[i], 1);
       mbar_init(&x_full[i], 1); mbar_init(&x_empty[i], 1);
     }
     mbar_init(acc_bar, 1);
@@ -213,7 +220,7 @@ w4_umma_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__
       for (int i = 0; i < nst; ++i) {
         const int64_t stage = st_begin + i;
         if (i >= RAW_ST && !__all_sync(0xffffffffu, mbar_wait(&raw_empty[rs], rph ^ 1, abort_flag))) break;
-        if (elect_one()) {
+        if (U_LEADER_PROD) {
           mbar_expect_tx(&raw_full[rs], U_RAW_BYTES);
           tma_load_2d(raw_ring + rs * U_RAW_BYTES, &wmap, (int)cbase, (int)(stage * 32), &raw_full[rs]);
           UTRACE(0, i);
@@ -238,7 +245,7 @@ w4_umma_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__
       for (int i = 0; i < nst; ++i) {
         const int64_t stage = st_begin + i;
         if (i >= p.x_stages && !__all_sync(0xffffffffu, mbar_wait(&x_empty[xs], xph ^ 1, abort_flag))) break;
-        if (elect_one()) {
+        if (U_LEADER_PROD) {
           mbar_expect_tx(&x_full[xs], (uint32_t)x_stage_bytes);
           tma_load_2d(x_ring + xs * x_stage_bytes, &xmap0, (int)(stage * U_STAGE_K), (int)m0, &x_full[xs]);
           if (nt1 > 0)     // second box of 256 token rows (one plane only at this size)
@@ -276,7 +283,7 @@ w4_umma_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__
         ok = __all_sync(0xffffffffu, mbar_wait(&a_full[as], aph, abort_flag) && mbar_wait(&x_full[xs], xph, abort_flag));
         if (!ok) break;
         tc_fence_after();
-        if (elect_one()) {
+        if (U_LEADER_MMA) {
         UTRACE(4, i);
         UTRACE(6, i);
 #pragma unroll
@@ -293,11 +300,12 @@ w4_umma_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__
         mma_commit(&x_empty[xs]);
         UTRACE(5, i);
         }
+        tc_fence_before();      // the next stage's MMAs follow these whichever lane issues them
         __syncwarp();
         if (++as == A_ST) { as = 0; aph ^= 1; a16 = a_ring16; } else { a16 += a_stage16; }
         if (++xs == p.x_stages) { xs = 0; xph ^= 1; x16 = x_ring16; } else { x16 += x_stage16; }
       }
-      if (ok && elect_one()) mma_commit(acc_bar);
+      if (ok && U_LEADER_MMA) mma_commit(acc_bar);
       __syncwarp();
     }
   } else {
@@ -311,23 +319,22 @@ w4_umma_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__
     bool ok = true;
     // A warp always works on the same ring slot (slot = warp index), so it sees every phase of
     // that slot's barriers in order; the ring depths equal the number of active expansion warps.
-    const int ndq = A_ST;
-    const int wps = U_DQ_WARPS / A_ST;   // warps per stage: 1, or 2 (each expands 16 of the 32 byte rows)
-    const int as = dw / wps;             // the warp's A slot never changes
-    const int u_lo = (dw % wps) * (8 / wps), u_hi = u_lo + 8 / wps;
-    int rs = as;                         // raw slot of this warp's next stage (RAW_ST is a multiple of ndq)
+    const int ndq = A_ST;                // active expansion warps (the others only take part in the epilogue)
+    const int as = dw;                   // the warp's A slot never changes
+    int rs = dw;                         // raw slot of this warp's next stage (RAW_ST is a multiple of ndq)
     uint32_t rph = 0, aph = 0;           // phase parities of the raw slot and of the warp's A slot
-    for (int i = as; i < nst; i += ndq) {
+    for (int i = dw; i < nst && dw < ndq; i += ndq) {
       ok = __all_sync(0xffffffffu, mbar_wait(&raw_full[rs], rph, abort_flag));
       if (!ok) break;
       if (lane == 0) UTRACE(2, i);
       uint4 v[8];
-      const uint8_t* rawp = raw_ring + rs * U_RAW_BYTES + cgp * 16;
+      const uint32_t rawp = smem_u32(raw_ring + rs * U_RAW_BYTES + cgp * 16);
 #pragma unroll
       for (int u = 0; u < 8; ++u)
-        if (u >= u_lo && u < u_hi) v[u] = *reinterpret_cast<const uint4*>(rawp + (4 * u + rsub) * U_COLS);
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&raw_empty[rs]);
+        asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];"
+                     : "=r"(v[u].x), "=r"(v[u].y), "=r"(v[u].z), "=r"(v[u].w)
+                     : "r"(rawp + (uint32_t)((4 * u + rsub) * U_COLS))
+                     : "memory");
       if (i >= A_ST) {
         ok = __all_sync(0xffffffffu, mbar_wait(&a_empty[as], aph ^ 1, abort_flag));
         if (!ok) break;
@@ -336,7 +343,6 @@ w4_umma_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__
       uint8_t* grp = a_ring + as * U_A_BYTES + ngroup * 8192;
 #pragma unroll
       for (int u = 0; u < 8; ++u) {
-        if (u < u_lo || u >= u_hi) continue;
         uint32_t e[8], o[8];     // k even / k odd: 16 channels each, in expanded order
         expand_word<FMT>(v[u].x, p.emask_lo, p.emask_hi, p.emagic, e[0], e[1], o[0], o[1]);
         expand_word<FMT>(v[u].y, p.emask_lo, p.emask_hi, p.emagic, e[2], e[3], o[2], o[3]);
@@ -350,7 +356,10 @@ w4_umma_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__
       }
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
       __syncwarp();
-      if (lane == 0) { mbar_arrive(&a_full[as]); UTRACE(3, i); }
+      // The raw slot goes back to the producer only now.  Releasing it right after the loads looked
+      // safe and was not: with the producer a full ring ahead, single CTAs produced wrong sums now and
+      // then.  The ring is twice as deep as the number of expanding warps instead.
+      if (lane == 0) { mbar_arrive(&a_full[as]); mbar_arrive(&raw_empty[rs]); UTRACE(3, i); }
       aph ^= 1;
       rs += ndq;
       if (rs >= RAW_ST) { rs -= RAW_ST; rph ^= 1; }
@@ -455,14 +464,22 @@ UmmaPlan plan_w4_umma(int64_t M, int64_t N, int64_t K, int x_dtype) {
   const size_t x_stage = (size_t)pl.NT * 128 * pl.planes;
   // ring depths (<= 224 KB in all): raw and expanded-A rings hold one stage per active expansion warp
   // (8, or 4 when the activation tiles are large and the tensor pipe is the bound anyway)
-  // Ring depths: eight raw stages; eight expanded stages (one per expansion warp) while the activation
-  // ring still gets two stages of what is left, else four (two warps share a stage); the activation
-  // ring takes the rest.
-  pl.raw_stages = 8;
-  pl.a_stages = ((size_t)(224u << 10) - 8 * U_RAW_BYTES - 8 * U_A_BYTES) / x_stage >= 2 ? 8 : 4;
+  // Ring depths: eight expanded stages (one per expansion warp) while the activation ring still gets four
+  // stages of what is left, else four (four warps expand); twice as many raw stages; the activation ring
+  // takes the rest.  A slot of the activation ring
+  // is free again only when the MMAs that read it have completed and full again one L2 round trip
+  // later (about 2 us in all), so at 128 tokens four 16 KB slots hold the kernel to 0.5 us per stage.
+  pl.a_stages = ((size_t)(224u << 10) - 16 * U_RAW_BYTES - 8 * U_A_BYTES) / x_stage >= 4 ? 8 : 4;
+  pl.raw_stages = 2 * pl.a_stages;      // a raw slot is held while its stage is expanded: half the ring is in flight
   {
     const size_t budget = (size_t)(224u << 10) - (size_t)pl.raw_stages * U_RAW_BYTES - (size_t)pl.a_stages * U_A_BYTES;
-    pl.x_stages = (int)std::max<size_t>(2, std::min<size_t>(U_MAX_ST, budget / x_stage));
+    pl.x_stages = (int)std::max<size_t>(1, std::min<size_t>(U_MAX_ST, budget / x_stage));
+  }
+  if (const char* e = getenv("JGQ_UMMA_RINGS")) {       // debugging aid: "raw,a,x" ring depths
+    int r = 0, a = 0, x = 0;
+    if (sscanf(e, "%d,%d,%d", &r, &a, &x) == 3 && r >= a && r % a == 0 && (a == 4 || a == 8) && r <= U_MAX_ST && x >= 1 && x <= U_MAX_ST) {
+      pl.raw_stages = r; pl.a_stages = a; pl.x_stages = x;
+    }
   }
   pl.smem_bytes = (size_t)pl.raw_stages * U_RAW_BYTES + (size_t)pl.a_stages * U_A_BYTES + pl.x_stages * x_stage +
                   1024 /*alignment*/ + 1024 /*barriers*/;

@@ -361,6 +361,24 @@ def test_matmul_decode_sizes(G, M, x_dtype):
     assert rel <= 1e-2, f'{x_dtype} M={M}: relative error {rel:.3e}'
 
 
+@pytest.mark.parametrize('M,x_dtype', [(64, 'float16'), (128, 'float16'), (100, 'float32'), (24, 'bfloat16')])
+def test_matmul_many_ctas_repeatable(G, M, x_dtype):
+    """250 CTAs of 80 stages each (more CTAs than SMs, rings wrapping many times): ten launches must agree
+    bit for bit and match the dequantized product."""
+    torch.manual_seed(5)
+    N, K = 32000, 5120
+    packed = torch.randint(0, 256, (K // 2, N), dtype=torch.uint8, device='cuda')
+    qm = G.QuantizedMatrix(packed, torch.rand(1, N, device='cuda') * 15, torch.rand(1, N, device='cuda') * 0.02)
+    x = torch.randn(M, K, device='cuda').to(getattr(torch, x_dtype))
+    outs = [G.quantized_matmul(x, qm).float() for _ in range(10)]
+    for o in outs[1:]:
+        assert torch.equal(o, outs[0]), 'repeated launches must agree bit for bit'
+    ref = x.float() @ G.unpack_matrix(qm).float()
+    rel = float((outs[0] - ref).norm() / ref.norm())
+    assert rel <= (2e-5 if x_dtype == 'float32' else 5e-3), f'relative error {rel:.3e}'
+    assert float((outs[0] - ref).abs().max()) <= 0.02 * float(ref.abs().max())
+
+
 def test_matmul_sweep_shape_small_m(G):
     from jax_gptq_b200 import workloads
     codes, scale, zero, x = workloads.w4_case(3003, 4096, 4096, 16)
