@@ -187,8 +187,9 @@ w4_umma_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__
 
   if (threadIdx.x == 0) {
     for (int i = 0; i < U_MAX_ST; ++i) {
-      mbar_init(&raw_full[i], 1); mbar_init(&raw_empty[i], 1);     // a stage belongs to one expansion warp
-      mbar_init(&a_full[i], 1); mbar_init(&a_empty[i], 1);
+      // a stage belongs to one expansion warp, or to a pair of them when the A ring has four slots
+      mbar_init(&raw_full[i], 1); mbar_init(&raw_empty[i], U_DQ_WARPS / A_ST);
+      mbar_init(&a_full[i], U_DQ_WARPS / A_ST); mbar_init(&a_empty[i], 1);
       mbar_init(&x_full[i], 1); mbar_init(&x_empty[i], 1);
     }
     mbar_init(acc_bar, 1);
@@ -319,11 +320,13 @@ w4_umma_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__
     bool ok = true;
     // A warp always works on the same ring slot (slot = warp index), so it sees every phase of
     // that slot's barriers in order; the ring depths equal the number of active expansion warps.
-    const int ndq = A_ST;                // active expansion warps (the others only take part in the epilogue)
-    const int as = dw;                   // the warp's A slot never changes
-    int rs = dw;                         // raw slot of this warp's next stage (RAW_ST is a multiple of ndq)
+    const int ndq = A_ST;                // stages in expansion at a time
+    const int wps = U_DQ_WARPS / A_ST;   // warps per stage: 1, or 2 (each expands 16 of the 32 byte rows)
+    const int as = dw / wps;             // the warp's A slot never changes
+    const int u_lo = (dw % wps) * (8 / wps), u_hi = u_lo + 8 / wps;
+    int rs = as;                         // raw slot of this warp's next stage (RAW_ST is a multiple of ndq)
     uint32_t rph = 0, aph = 0;           // phase parities of the raw slot and of the warp's A slot
-    for (int i = dw; i < nst && dw < ndq; i += ndq) {
+    for (int i = as; i < nst; i += ndq) {
       ok = __all_sync(0xffffffffu, mbar_wait(&raw_full[rs], rph, abort_flag));
       if (!ok) break;
       if (lane == 0) UTRACE(2, i);
@@ -331,6 +334,7 @@ w4_umma_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__
       const uint32_t rawp = smem_u32(raw_ring + rs * U_RAW_BYTES + cgp * 16);
 #pragma unroll
       for (int u = 0; u < 8; ++u)
+        if (u >= u_lo && u < u_hi)
         asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];"
                      : "=r"(v[u].x), "=r"(v[u].y), "=r"(v[u].z), "=r"(v[u].w)
                      : "r"(rawp + (uint32_t)((4 * u + rsub) * U_COLS))
@@ -343,6 +347,7 @@ w4_umma_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__
       uint8_t* grp = a_ring + as * U_A_BYTES + ngroup * 8192;
 #pragma unroll
       for (int u = 0; u < 8; ++u) {
+        if (u < u_lo || u >= u_hi) continue;
         uint32_t e[8], o[8];     // k even / k odd: 16 channels each, in expanded order
         expand_word<FMT>(v[u].x, p.emask_lo, p.emask_hi, p.emagic, e[0], e[1], o[0], o[1]);
         expand_word<FMT>(v[u].y, p.emask_lo, p.emask_hi, p.emagic, e[2], e[3], o[2], o[3]);
@@ -465,7 +470,7 @@ UmmaPlan plan_w4_umma(int64_t M, int64_t N, int64_t K, int x_dtype) {
   // ring depths (<= 224 KB in all): raw and expanded-A rings hold one stage per active expansion warp
   // (8, or 4 when the activation tiles are large and the tensor pipe is the bound anyway)
   // Ring depths: eight expanded stages (one per expansion warp) while the activation ring still gets four
-  // stages of what is left, else four (four warps expand); twice as many raw stages; the activation ring
+  // stages of what is left, else four (two warps share a stage); twice as many raw stages; the activation ring
   // takes the rest.  A slot of the activation ring
   // is free again only when the MMAs that read it have completed and full again one L2 round trip
   // later (about 2 us in all), so at 128 tokens four 16 KB slots hold the kernel to 0.5 us per stage.
