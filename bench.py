@@ -293,7 +293,7 @@ def run_ours(args):
                 'peak_source': 'MEASURED_PEAKS.json bf16_tflops_sustained' if peaks else 'fallback 1.4 PFLOP/s sustained',
                 'launches_per_hessian': h_launches, 'ms_per_hessian': h_ms,
                 'note': 'time covers the bf16 split, the tcgen05 kernel and the slice reduction of one Hessian',
-                'traffic': 1.231e9,
+                'traffic': 1.254e9,
                 'traffic_source': 'ncu dram__bytes_read+write of the hessian_umma_kernel launch for K=3072, n=65536 '
                                   '(profiles/hessian_umma_k3072_gpt2_block.md)'}
 
