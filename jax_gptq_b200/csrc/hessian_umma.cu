@@ -293,9 +293,13 @@ HessPlan plan_hessian_umma(int64_t n, int64_t K, int x_dtype) {
   if (ov != 2 && (K < 256 || n < 512)) return pl;     // tiny problems: the FFMA path is already launch-bound
   pl.use = 1;
   pl.planes = (x_dtype == JGQ_F32) ? 2 : 1;
-  // 256-row tiles need a third fewer operand bytes per flop; with few tiles (small K) the
-  // 128-row tiles balance better over the SMs and need fewer token slices
-  pl.panel = K >= 1536 ? HT_PANEL : HT_M;
+  // 256-row tiles need a third fewer operand bytes per flop (measured: K = 768 0.31 against 0.33 ms per
+  // Hessian stage, K = 3072 1.75 against 2.2 ms); below six tiles the 128-row tiles spread better over the SMs
+  pl.panel = K >= 768 ? HT_PANEL : HT_M;
+  if (const char* e = getenv("JGQ_HESSIAN_PANEL")) {      // measurement aid: force the tile height
+    if (!strcmp(e, "256")) pl.panel = HT_PANEL;
+    if (!strcmp(e, "128")) pl.panel = HT_M;
+  }
   int64_t nseg = 0;
   if (pl.panel == HT_PANEL) {
     const int64_t T = cdiv(K, HT_PANEL);

@@ -422,11 +422,11 @@ def test_config1_matmul_after_gptq(G):
 
 
 # ------------------------------------------------- Hessian on the tensor path ----
-@pytest.mark.parametrize('n,K', [(1024, 256), (4096, 768), (2000, 320), (8192, 1024), (777, 512),
+@pytest.mark.parametrize('n,K', [(1024, 256), (4096, 768), (2000, 320), (8192, 1024), (777, 512), (1500, 712), (2048, 776),
                                  (4096, 1536), (3000, 1800), (2048, 1928), (16384, 3072)])
 def test_hessian_tensor_path_fp32(G, n, K):
     """fp32 batches go through the bf16-split tcgen05 kernel (K % 8 == 0, K >= 256, n >= 512):
-    128-row tiles below K = 1536, 256-row tiles with two accumulators from there on, ragged edges included."""
+    128-row tiles below K = 768, 256-row tiles with two accumulators from there on, ragged edges included."""
     rng = np.random.default_rng(90 + K)
     X = (rng.standard_normal((n, K)) * rng.uniform(0.1, 3.0, size=K) + rng.uniform(-0.5, 0.5, size=K)).astype(np.float32)
     ref = (X.astype(np.float64).T @ X.astype(np.float64)) / n
