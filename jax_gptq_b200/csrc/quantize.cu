@@ -31,8 +31,8 @@ static int tail_on_tensor_cores() {
   return v;
 }
 
-template <typename QT, int TPB>
-__global__ void __launch_bounds__(TPB)
+template <typename QT, int TPB, int R>
+__global__ void __launch_bounds__(TPB * R)
 gptq_block_kernel(const float* __restrict__ W, const float* __restrict__ L,
                   const float* __restrict__ scale, const float* __restrict__ zero,
                   int K, int64_t N, int start, int bs, float maxq,
@@ -41,7 +41,12 @@ gptq_block_kernel(const float* __restrict__ W, const float* __restrict__ L,
   float* Ld = smem;                    // [bs][bs_pad]
   const int bs_pad = (bs + 3) & ~3;
   float* Wb = smem + bs * bs_pad;      // [bs][TPB]
-  const int tid = threadIdx.x;
+  float* Eb = Wb + bs * TPB;           // [SUB][TPB]: the errors of the current sub-block, for the helper roles
+  // TPB channels per CTA, R roles per channel: role 0 walks the rows of a sub-block one after the other,
+  // then all R roles bring disjoint groups of the later rows up to date (same operations per element, in
+  // the same order, whoever executes them).
+  constexpr int NT = TPB * R;
+  const int tid = threadIdx.x % TPB, role = threadIdx.x / TPB, lin = threadIdx.x;
   const int64_t col = (int64_t)blockIdx.x * TPB + tid;
   const bool live = col < N;
 
@@ -51,11 +56,11 @@ gptq_block_kernel(const float* __restrict__ W, const float* __restrict__ L,
   if ((bs & 3) == 0 && (K & 3) == 0 && ((reinterpret_cast<uintptr_t>(L) & 15) == 0)) {
     const int q = bs >> 2;                       // float4 per row
     const int total = bs * q;
-    for (int base = 0; base < total; base += 8 * TPB) {
+    for (int base = 0; base < total; base += 8 * NT) {
       float4 v[8];
 #pragma unroll
       for (int u = 0; u < 8; ++u) {
-        const int idx = base + u * TPB + tid;
+        const int idx = base + u * NT + lin;
         if (idx < total) {
           const int j = idx / q, i4 = idx - j * q;
           v[u] = __ldg(reinterpret_cast<const float4*>(L + (int64_t)(start + j) * K + start) + i4);
@@ -63,7 +68,7 @@ gptq_block_kernel(const float* __restrict__ W, const float* __restrict__ L,
       }
 #pragma unroll
       for (int u = 0; u < 8; ++u) {
-        const int idx = base + u * TPB + tid;
+        const int idx = base + u * NT + lin;
         if (idx < total) {
           const int j = idx / q, i4 = idx - j * q;
           *reinterpret_cast<float4*>(&Ld[j * bs_pad + 4 * i4]) = v[u];
@@ -71,12 +76,12 @@ gptq_block_kernel(const float* __restrict__ W, const float* __restrict__ L,
       }
     }
   } else {
-    for (int idx = tid; idx < bs * bs; idx += TPB) {
+    for (int idx = lin; idx < bs * bs; idx += NT) {
       const int j = idx / bs, i = idx % bs;
       Ld[j * bs_pad + i] = L[(int64_t)(start + j) * K + start + i];
     }
   }
-  for (int j0 = 0; j0 < bs; j0 += 16) {
+  for (int j0 = 16 * role; j0 < bs; j0 += 16 * R) {
     float v[16];
 #pragma unroll
     for (int u = 0; u < 16; ++u)
@@ -92,6 +97,7 @@ gptq_block_kernel(const float* __restrict__ W, const float* __restrict__ L,
   for (int s0 = 0; s0 < bs; s0 += SUB) {
     const int sn = min(SUB, bs - s0);
     float w[SUB], e[SUB];
+    if (role == 0) {
 #pragma unroll
     for (int i = 0; i < SUB; ++i) w[i] = (i < sn) ? Wb[(s0 + i) * TPB + tid] : 0.f;
 #pragma unroll
@@ -117,11 +123,24 @@ gptq_block_kernel(const float* __restrict__ W, const float* __restrict__ L,
           if (ii < sn) w[ii] = __fsub_rn(w[ii], __fmul_rn(Ld[(s0 + ii) * bs_pad + r], err));
       }
     }
+    if (R > 1) {
+#pragma unroll
+      for (int i = 0; i < SUB; ++i) Eb[i * TPB + tid] = e[i];
+    }
+    }  // role 0
+    if (R > 1) {
+      __syncthreads();
+      if (role != 0) {
+#pragma unroll
+        for (int i = 0; i < SUB; ++i) e[i] = Eb[i * TPB + tid];
+      }
+    }
     // bring the later rows of this block up to date (only reached when sn == SUB).
     // Four rows at a time: each row is its own dependent chain of 16 multiply/subtract pairs,
-    // so interleaving four of them hides the arithmetic latency of the single resident warp.
-    int j = s0 + SUB;
-    for (; j + 3 < bs; j += 4) {
+    // so interleaving four of them hides the arithmetic latency of a warp; the groups of four
+    // are dealt to the R roles in turn.
+    int j = s0 + SUB + 4 * role;
+    for (; j + 3 < bs; j += 4 * R) {
       float wj[4];
       const float4* lrow[4];
 #pragma unroll
@@ -146,7 +165,9 @@ gptq_block_kernel(const float* __restrict__ W, const float* __restrict__ L,
 #pragma unroll
       for (int r = 0; r < 4; ++r) Wb[(j + r) * TPB + tid] = wj[r];
     }
-    for (; j < bs; ++j) {
+    // rows left over when the block is not a multiple of four past the sub-block: role 0
+    j = s0 + SUB + ((bs - s0 - SUB) > 0 ? ((bs - s0 - SUB) / 4) * 4 : 0);
+    for (; role == 0 && j < bs; ++j) {
       float wj = Wb[j * TPB + tid];
       const float4* lrow = reinterpret_cast<const float4*>(&Ld[j * bs_pad + s0]);
 #pragma unroll
@@ -159,6 +180,7 @@ gptq_block_kernel(const float* __restrict__ W, const float* __restrict__ L,
       }
       Wb[j * TPB + tid] = wj;
     }
+    if (R > 1) __syncthreads();      // the next sub-block reads rows the helpers wrote, and reuses Eb
   }
 }
 
@@ -167,19 +189,20 @@ static int launch_block(const float* W, const float* L, const float* scale, cons
                         int K, int64_t N, int start, int bs, float maxq, QT* Q, uint8_t* codes,
                         float* E, cudaStream_t s) {
   const int bs_pad = (bs + 3) & ~3;
-  const size_t smem = ((size_t)bs * bs_pad + (size_t)bs * TPB) * sizeof(float);
+  constexpr int R = 128 / TPB;        // 128 threads per CTA: 4 roles for 32 channels, 2 for 64, 1 for 128
+  const size_t smem = ((size_t)bs * bs_pad + (size_t)bs * TPB + (size_t)SUB * TPB) * sizeof(float);
   static std::once_flag flags[64];
   int dev = 0;
   cudaGetDevice(&dev);
   if (dev >= 0 && dev < 64) {
     std::call_once(flags[dev], []() {
-      cudaFuncSetAttribute(gptq_block_kernel<QT, TPB>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                           (128 * 128 + 128 * TPB) * (int)sizeof(float));
-      cudaFuncSetAttribute(gptq_block_kernel<QT, TPB>, cudaFuncAttributePreferredSharedMemoryCarveout,
+      cudaFuncSetAttribute(gptq_block_kernel<QT, TPB, 128 / TPB>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                           (128 * 128 + 128 * TPB + SUB * TPB) * (int)sizeof(float));
+      cudaFuncSetAttribute(gptq_block_kernel<QT, TPB, 128 / TPB>, cudaFuncAttributePreferredSharedMemoryCarveout,
                            cudaSharedmemCarveoutMaxShared);
     });
   }
-  gptq_block_kernel<QT, TPB><<<(unsigned)cdiv(N, TPB), TPB, smem, s>>>(
+  gptq_block_kernel<QT, TPB, R><<<(unsigned)cdiv(N, TPB), TPB * R, smem, s>>>(
       W, L, scale, zero, K, N, start, bs, maxq, Q, codes, E);
   return check_launch("gptq_block");
 }
