@@ -451,6 +451,24 @@ def test_hessian_tensor_path_half(G, dtype, K):
     assert np.allclose(got, ref, atol=5e-6, rtol=1e-5)
 
 
+def test_gptq_many_actorder_and_bits(G):
+    """The options of gptq reach every job of gptq_many unchanged, with and without the Hessian stream."""
+    rng = np.random.default_rng(124)
+    jobs = []
+    for K, N in [(256, 96), (128, 160), (384, 64)]:
+        W = (0.02 * rng.standard_normal((K, N))).astype(np.float32)
+        xs = [(rng.standard_normal((256, K)) * np.linspace(0.3, 2.5, K)).astype(np.float32) for _ in range(2)]
+        jobs.append((dev(W), [dev(x) for x in xs]))
+    for kw in ({'actorder': True}, {'bits': 3}, {'actorder': True, 'damping': 0.05}):
+        seq = [G.pack_matrix(*G.gptq(W, xs, block_size=64, **kw)) for W, xs in jobs]
+        for hs in (True, False):
+            got = G.gptq_many(jobs, block_size=64, streams=2, hessian_stream=hs, **kw)
+            torch.cuda.synchronize()
+            for a, b in zip(got, seq):
+                assert torch.equal(a.int_weight, b.int_weight)
+                assert torch.equal(a.scale, b.scale) and torch.equal(a.zero, b.zero)
+
+
 def test_gptq_many_matches_sequential(G):
     """Jobs issued on several streams with host- and device-resident inputs give exactly the
     results of one-at-a-time calls; a bad job still raises."""
