@@ -498,8 +498,8 @@ def gptq_many(jobs, block_size=128, actorder=False, damping=0.01, bits=4, pack=T
     main = torch.cuda.current_stream()
     start = main.record_event()
     copier.wait_event(start)
-    for w in workers:
-        w.wait_event(start)
+    for w in workers + ([hstream] if hstream is not None else []):
+        w.wait_event(start)          # inputs produced on the caller's stream are complete for every stream used here
     done = [None] * nw               # completion event of the last job issued on each worker
 
     def stage(job, wi):
