@@ -245,5 +245,7 @@ def main(ref_root, out_path):
 
 
 if __name__ == '__main__':
-    root = sys.argv[1] if len(sys.argv) > 1 else '/root/reference'
+    if len(sys.argv) < 2:
+        sys.exit('usage: python make_golden.py <path of a checkout of davisyoshida/jax-gptq>')
+    root = sys.argv[1]
     main(root, os.path.join(os.path.dirname(os.path.abspath(__file__)), 'gptq_golden.npz'))
