@@ -6,6 +6,7 @@
 #include <stdint.h>
 #include <stdio.h>
 #include <stdarg.h>
+#include <mutex>
 #include "../../include/jgq.h"
 
 namespace jgq {
@@ -39,15 +40,29 @@ inline int check_launch(const char* what) {
 // Asks for the largest shared-memory carve-out for a kernel (once per device).  The kernels of the
 // latency-bound stages are meant to share SMs with the Hessian kernel, which needs that carve-out;
 // CTAs of kernels that prefer different L1 / shared-memory splits do not run on one SM together.
+// Runs `fn` exactly once per device (the current one) per distinct `Tag` type, whatever host thread
+// asks first; later calls return the first call's result.  Host frameworks may call into the library
+// from one thread per device, so per-device set-up never goes through a plain mutable static.
+template <typename Tag, typename F>
+inline int once_per_device(F&& fn) {
+  static std::once_flag flags[64];
+  static int rc[64];
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return fn();
+  std::call_once(flags[dev], [&]() { rc[dev] = fn(); });
+  return rc[dev];
+}
+
+template <auto Kern> struct KernelTag {};
+
 template <auto Kern>
 inline void prefer_shared_carveout() {
-  static bool done[64] = {false};
-  int dev = 0;
-  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64 || done[dev]) return;
-  cudaFuncSetAttribute(reinterpret_cast<const void*>(Kern), cudaFuncAttributePreferredSharedMemoryCarveout,
-                       cudaSharedmemCarveoutMaxShared);
-  cudaGetLastError();      // a hint: a refusal is not an error
-  done[dev] = true;
+  once_per_device<KernelTag<Kern>>([]() {
+    cudaFuncSetAttribute(reinterpret_cast<const void*>(Kern), cudaFuncAttributePreferredSharedMemoryCarveout,
+                         cudaSharedmemCarveoutMaxShared);
+    cudaGetLastError();      // a hint: a refusal is not an error
+    return 0;
+  });
 }
 
 inline bool aligned(const void* p, size_t a) { return (reinterpret_cast<uintptr_t>(p) % a) == 0; }

@@ -76,11 +76,13 @@ static size_t simt_workspace_bytes(int64_t n, int64_t K, int x_dtype);
 
 using namespace jgq;
 
+// The tensor-core kernel is what a batch takes whenever its plan allows it, and then only that kernel's
+// scratch is charged (two bf16 planes for fp32 batches, token-slice buffers).  The FFMA kernel is the route
+// of small or odd shapes; it is not kept as an alternative for large ones (see jgq_hessian_accum).
 extern "C" size_t jgq_hessian_workspace_bytes(int64_t n, int64_t K, int x_dtype) {
   if (n <= 0 || K <= 0) return 0;
   const HessPlan pl = plan_hessian_umma(n, K, x_dtype);
-  const size_t simt = simt_workspace_bytes(n, K, x_dtype);
-  return pl.use ? std::max(simt, 2 * pl.plane_bytes + pl.part_bytes) : simt;
+  return pl.use ? 2 * pl.plane_bytes + pl.part_bytes : simt_workspace_bytes(n, K, x_dtype);
 }
 
 static size_t jgq::simt_workspace_bytes(int64_t n, int64_t K, int x_dtype) {
@@ -105,7 +107,10 @@ extern "C" int jgq_hessian_accum(const void* X, int x_dtype, int64_t n, int64_t 
   JGQ_REQUIRE(need == 0 || aligned(ws, 256), JGQ_ERR_ALIGN, "hessian_accum: workspace must be 256-byte aligned");
   cudaStream_t s = (cudaStream_t)stream;
   const HessPlan pl = plan_hessian_umma(n, K, x_dtype);
-  if (pl.use && aligned(X, 16) && aligned(H, 16)) {
+  // TMA reads X and the epilogue writes H in 16-byte pieces
+  JGQ_REQUIRE(!pl.use || (aligned(X, 16) && aligned(H, 16)), JGQ_ERR_ALIGN,
+              "hessian_accum: X and H must be 16-byte aligned for n=%lld K=%lld", (long long)n, (long long)K);
+  if (pl.use) {
     int rc = launch_hessian_umma(pl, X, x_dtype, n, K, H, ws, dev_status, s);
     if (rc) return rc;
     if (pl.S > 1) {

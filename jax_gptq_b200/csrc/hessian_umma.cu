@@ -277,11 +277,10 @@ hessian_umma_kernel(const __grid_constant__ CUtensorMap map0, const __grid_const
 
 // ------------------------------------------------------------------ host ----
 static int hessian_path_override() {      // 0 = automatic, 1 = FFMA only, 2 = tensor path whenever legal
-  static int v = -1;
-  if (v < 0) {
+  static const int v = []() {        // initialised once, thread-safe
     const char* e = getenv("JGQ_HESSIAN_PATH");
-    v = (e && !strcmp(e, "simt")) ? 1 : (e && !strcmp(e, "umma")) ? 2 : 0;
-  }
+    return (e && !strcmp(e, "simt")) ? 1 : (e && !strcmp(e, "umma")) ? 2 : 0;
+  }();
   return v;
 }
 
@@ -362,14 +361,11 @@ int launch_hessian_umma(const HessPlan& pl, const void* X, int x_dtype, int64_t 
   p.out = pl.S > 1 ? part : H;
   p.slice_stride = pl.S > 1 ? K * K : 0;
   p.status = status;
-  static bool attr_set[64] = {false};
-  int dev = 0;
-  cudaGetDevice(&dev);
-  if (dev >= 0 && dev < 64 && !attr_set[dev]) {
-    cudaFuncSetAttribute(hessian_umma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                         HT_RING_BYTES_MAX + HT_BAR_BYTES);
-    attr_set[dev] = true;
-  }
+  struct SmemAttrTag {};
+  once_per_device<SmemAttrTag>([]() {
+    return (int)cudaFuncSetAttribute(hessian_umma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                     HT_RING_BYTES_MAX + HT_BAR_BYTES);
+  });
   hessian_umma_kernel<<<(unsigned)(pl.nseg * pl.S), HT_THREADS, smem_bytes, s>>>(m0, m1, p);
   return check_launch("hessian_umma");
 }

@@ -26,8 +26,7 @@ constexpr int SUB = 16;
 
 // JGQ_TAIL_GEMM=ffma keeps the lazy-batch tail update on the FFMA body (for comparisons).
 static int tail_on_tensor_cores() {
-  static int v = -1;
-  if (v < 0) { const char* e = getenv("JGQ_TAIL_GEMM"); v = (e && !strcmp(e, "ffma")) ? 0 : 1; }
+  static const int v = []() { const char* e = getenv("JGQ_TAIL_GEMM"); return (e && !strcmp(e, "ffma")) ? 0 : 1; }();
   return v;
 }
 

@@ -327,13 +327,14 @@ constexpr int64_t kStreamRows = 16;          // token rows of one pass of the st
 constexpr int64_t kStreamPassesMaxM = 32;    // two passes (120 us at 8192 x 28672) still beat the tensor-path kernel (128 us at M = 64)
 
 static int w4_path_override() {        // JGQ_W4_PATH=direct: direct-load decode kernel; =mma: no tcgen05 either
-  static int v = -1;
-  if (v < 0) { const char* e = getenv("JGQ_W4_PATH"); v = !e ? 0 : !strcmp(e, "direct") ? 1 : !strcmp(e, "mma") ? 2 : 0; }
+  static const int v = []() {
+    const char* e = getenv("JGQ_W4_PATH");
+    return !e ? 0 : !strcmp(e, "direct") ? 1 : !strcmp(e, "mma") ? 2 : 0;
+  }();
   return v;
 }
 
 static bool w4_force_mma_sync() {      // JGQ_W4_PATH=mma sends every M to the mma.sync kernel (for comparisons)
-  static int v = -1;
   return w4_path_override() == 2;
 }
 
@@ -341,30 +342,32 @@ static bool w4_force_mma_sync() {      // JGQ_W4_PATH=mma sends every M to the m
 
 using namespace jgq;
 
-// Workspace layout (forward): 4096 bytes of int32 tickets, one per (row tile,
-// channel group), then [ksplit][M][channel groups][132] fp32 slices.  The ticket
-// bytes must be zero before the first launch that uses a workspace; every launch
-// leaves them zero again.  The slices need no initialisation.
-extern "C" size_t jgq_w4_matmul_workspace_bytes(int64_t M, int64_t N, int64_t K, int transpose_b) {
-  if (transpose_b || M <= 0 || N <= 0 || K <= 0) return 0;
+namespace jgq {
+
+// Scratch bytes of the forward matmul for one activation dtype (x_dtype < 0: the largest over all dtypes).
+static size_t w4_forward_need(int64_t M, int64_t N, int64_t K, int x_dtype) {
+  if (M <= 0 || N <= 0 || K <= 0) return 0;
   const FwdPlan p = plan_fwd(M, N, K);
   size_t bytes = kTicketBytes;
   if (p.ksplit > 1) bytes += align_up((size_t)p.ksplit * M * p.ncg * PSTRIDE * sizeof(float), 256);
   // the tensor-path kernel is chosen at call time (it also needs aligned pointers); size for either.
   // fp32 activations are the worst case for its staging planes.
-  const UmmaPlan up = plan_w4_umma(M, N, K, JGQ_F32);
-  if (up.use) bytes = std::max(bytes, w4_umma_workspace_bytes(up));
-  const UmmaPlan up16 = plan_w4_umma(M, N, K, JGQ_F16);
-  if (up16.use) bytes = std::max(bytes, w4_umma_workspace_bytes(up16));
+  if (x_dtype < 0 || x_dtype == JGQ_F32) {
+    const UmmaPlan up = plan_w4_umma(M, N, K, JGQ_F32);
+    if (up.use) bytes = std::max(bytes, w4_umma_workspace_bytes(up));
+  }
+  if (x_dtype < 0 || x_dtype != JGQ_F32) {
+    const UmmaPlan up16 = plan_w4_umma(M, N, K, JGQ_F16);
+    if (up16.use) bytes = std::max(bytes, w4_umma_workspace_bytes(up16));
+  }
   const StreamPlan sp = plan_w4_stream(std::min<int64_t>(M, kStreamPassesMaxM) > kStreamRows ? kStreamRows : M, N, K);
   if (sp.use && M <= kStreamPassesMaxM) bytes = std::max(bytes, kTicketBytes + sp.part_bytes);
   return bytes;
 }
 
-extern "C" int jgq_w4_matmul(const void* x, int x_dtype, const uint8_t* packed,
-                             const void* zero, const void* scale, int zs_dtype,
-                             void* out, int64_t M, int64_t N, int64_t K, int transpose_b,
-                             void* ws, size_t ws_bytes, void* stream) {
+// Host-side argument checks shared by the two forward entry points.  Nothing is enqueued here.
+static int w4_validate(const void* x, int x_dtype, const uint8_t* packed, const void* zero, const void* scale,
+                       int zs_dtype, void* out, int64_t M, int64_t N, int64_t K) {
   JGQ_REQUIRE(x_dtype == JGQ_F32 || x_dtype == JGQ_F16 || x_dtype == JGQ_BF16, JGQ_ERR_ARG,
               "w4_matmul: activation dtype must be f32/f16/bf16");
   JGQ_REQUIRE(zs_dtype == JGQ_F32 || zs_dtype == JGQ_F16, JGQ_ERR_ARG, "w4_matmul: zero/scale dtype must be f32/f16");
@@ -374,6 +377,28 @@ extern "C" int jgq_w4_matmul(const void* x, int x_dtype, const uint8_t* packed,
   JGQ_REQUIRE(M <= 2147483647LL / 2 && N <= 2147483647LL && K <= 2147483647LL, JGQ_ERR_LIMIT, "w4_matmul: shape too large");
   if (M == 0) return JGQ_OK;
   JGQ_REQUIRE(x && packed && zero && scale && out, JGQ_ERR_ARG, "w4_matmul: null pointer");
+  return JGQ_OK;
+}
+
+}  // namespace jgq
+
+// Workspace layout (forward): 4096 bytes of int32 tickets, one per (row tile,
+// channel group), then [ksplit][M][channel groups][132] fp32 slices.  The ticket
+// bytes must be zero before the first launch that uses a workspace; every launch
+// leaves them zero again.  The slices need no initialisation.
+// The size returned covers every activation dtype; a call is accepted with the
+// (possibly smaller) amount its own dtype needs.
+extern "C" size_t jgq_w4_matmul_workspace_bytes(int64_t M, int64_t N, int64_t K, int transpose_b) {
+  if (transpose_b) return 0;
+  return w4_forward_need(M, N, K, -1);
+}
+
+extern "C" int jgq_w4_matmul(const void* x, int x_dtype, const uint8_t* packed,
+                             const void* zero, const void* scale, int zs_dtype,
+                             void* out, int64_t M, int64_t N, int64_t K, int transpose_b,
+                             void* ws, size_t ws_bytes, void* stream) {
+  if (const int rc = w4_validate(x, x_dtype, packed, zero, scale, zs_dtype, out, M, N, K)) return rc;
+  if (M == 0) return JGQ_OK;
   cudaStream_t s = (cudaStream_t)stream;
   if (transpose_b) {
 #define JGQ_TB(XT)                                                                                       \
@@ -385,7 +410,7 @@ extern "C" int jgq_w4_matmul(const void* x, int x_dtype, const uint8_t* packed,
 #undef JGQ_TB
   }
   JGQ_REQUIRE(aligned(x, 8), JGQ_ERR_ALIGN, "w4_matmul: x must be 8-byte aligned");
-  const size_t need = jgq_w4_matmul_workspace_bytes(M, N, K, 0);
+  const size_t need = w4_forward_need(M, N, K, x_dtype);
   JGQ_REQUIRE(ws && ws_bytes >= need, JGQ_ERR_WORKSPACE, "w4_matmul: workspace %zu < %zu bytes", ws_bytes, need);
   JGQ_REQUIRE(aligned(ws, 256), JGQ_ERR_ALIGN, "w4_matmul: workspace must be 256-byte aligned");
   if (w4_path_override() == 0) {
@@ -477,10 +502,11 @@ extern "C" size_t jgq_w4_matmul_noalloc_max_bytes(void) { return jgq::kNoAllocSc
 extern "C" int jgq_w4_matmul_noalloc(const void* x, int x_dtype, const uint8_t* packed,
                                      const void* zero, const void* scale, int zs_dtype,
                                      void* out, int64_t M, int64_t N, int64_t K, void* stream) {
-  JGQ_REQUIRE(M >= 0 && N > 0 && K > 0, JGQ_ERR_ARG, "w4_matmul_noalloc: bad shape M=%lld N=%lld K=%lld",
-              (long long)M, (long long)N, (long long)K);
+  // every argument check comes before the first thing that is enqueued
+  if (const int rc = w4_validate(x, x_dtype, packed, zero, scale, zs_dtype, out, M, N, K)) return rc;
   if (M == 0) return JGQ_OK;
-  const size_t need = jgq_w4_matmul_workspace_bytes(M, N, K, 0);
+  JGQ_REQUIRE(aligned(x, 8), JGQ_ERR_ALIGN, "w4_matmul_noalloc: x must be 8-byte aligned");
+  const size_t need = w4_forward_need(M, N, K, x_dtype);     // what this call's dtype needs, not the dtype-blind bound
   JGQ_REQUIRE(need <= kNoAllocScratchBytes, JGQ_ERR_LIMIT,
               "w4_matmul_noalloc: M=%lld N=%lld K=%lld needs %zu bytes of scratch, the built-in array holds %zu; "
               "use jgq_w4_matmul with a caller-provided workspace",

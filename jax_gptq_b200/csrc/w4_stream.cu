@@ -431,15 +431,15 @@ StreamPlan plan_w4_stream(int64_t M, int64_t N, int64_t K) {
 template <typename XT, typename CT, int NTOK, typename ZST>
 static int launch_stream_inst(const StreamPlan& pl, const StreamParams& p, const CUtensorMap& wmap, cudaStream_t s) {
   auto kern = w4_stream_kernel<XT, CT, NTOK, ZST>;
-  static bool attr_set[64] = {false};
-  int dev = 0;
-  cudaGetDevice(&dev);
-  if (dev >= 0 && dev < 64 && !attr_set[dev]) {
-    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, S_RING_BYTES + WWARPS * 8 * NTOK * PSTRIDE * (int)sizeof(float)) != cudaSuccess)
-      return fail(JGQ_ERR_CUDA, "w4_matmul: cannot raise the dynamic shared memory limit");
+  struct AttrTag {};       // one flag set per instantiation: the tag is local to this template
+  const int arc = once_per_device<AttrTag>([&]() {
+    const cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                               S_RING_BYTES + WWARPS * 8 * NTOK * PSTRIDE * (int)sizeof(float));
     cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout, 100);   // a hint: all of it as shared memory
-    attr_set[dev] = true;
-  }
+    cudaGetLastError();
+    return (int)e;
+  });
+  if (arc != 0) return fail(JGQ_ERR_CUDA, "w4_matmul: cannot raise the dynamic shared memory limit");
   kern<<<(unsigned)pl.G, S_THREADS, pl.smem_bytes, s>>>(wmap, p);
   return check_launch("w4_stream");
 }

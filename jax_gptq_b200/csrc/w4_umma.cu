@@ -526,14 +526,11 @@ template <typename XT, typename ZST, int FMT>
 static int launch_inst(const UmmaPlan& pl, const UmmaParams& p, const CUtensorMap& wmap, const CUtensorMap& x0,
                        const CUtensorMap& x1, cudaStream_t s) {
   auto kern = w4_umma_kernel<XT, ZST, FMT>;
-  static size_t attr_bytes[64] = {0};
-  int dev = 0;
-  cudaGetDevice(&dev);
-  if (dev >= 0 && dev < 64 && attr_bytes[dev] < pl.smem_bytes) {
-    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(227 << 10) - 1024) != cudaSuccess)
-      return fail(JGQ_ERR_CUDA, "w4_matmul: cannot raise the dynamic shared memory limit");
-    attr_bytes[dev] = (size_t)(227 << 10);
-  }
+  struct AttrTag {};       // local to this template: one flag set per instantiation
+  const int arc = once_per_device<AttrTag>([&]() {
+    return (int)cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(227 << 10) - 1024);
+  });
+  if (arc != 0) return fail(JGQ_ERR_CUDA, "w4_matmul: cannot raise the dynamic shared memory limit");
   dim3 grid((unsigned)pl.ncg, (unsigned)pl.ksplit, (unsigned)pl.mtiles);
   kern<<<grid, U_THREADS, pl.smem_bytes, s>>>(wmap, x0, x1, p);
   return check_launch("w4_umma");

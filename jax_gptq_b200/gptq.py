@@ -16,7 +16,7 @@ from . import _lib
 from ._lib import lib, check
 
 _DT = {torch.float32: _lib.F32, torch.float16: _lib.F16, torch.bfloat16: _lib.BF16}
-_MAX_CONVERT_BYTES = 1 << 30     # fp32 staging cap for non-fp32 calibration batches
+_MAX_HESSIAN_SCRATCH = 1 << 30   # calibration batches are fed in row chunks whose scratch stays below this
 
 
 # --------------------------------------------------------------------------
@@ -188,6 +188,16 @@ def _merge_adjacent(xs):
     return out
 
 
+def _chunk_rows(n, K, dt):
+    """Rows per kernel call: the whole batch if its scratch (bf16 planes of an fp32 batch, token-slice
+    buffers, the fp32 copy of a small 16-bit batch) stays under _MAX_HESSIAN_SCRATCH, else the largest
+    multiple of 1024 rows that does."""
+    rows = n
+    while rows > 1024 and lib.jgq_hessian_workspace_bytes(rows, K, dt) > _MAX_HESSIAN_SCRATCH:
+        rows = max(1024, (rows // 2 + 1023) // 1024 * 1024)
+    return max(1, rows)
+
+
 def _accumulate_raw(xs, H=None, status=None):
     """H (K x K fp32, lower triangle) += sum over batches of X^T X; returns (H, n)."""
     n_total = 0
@@ -202,9 +212,7 @@ def _accumulate_raw(xs, H=None, status=None):
         if H is None:
             H = _tmp('H', (K, K), torch.float32, zero=True)
         n = b.shape[0]
-        rows = n
-        if b.dtype != torch.float32:
-            rows = max(1, min(n, _MAX_CONVERT_BYTES // (4 * K)))
+        rows = _chunk_rows(n, K, _DT[b.dtype])
         for r0 in range(0, n, rows):
             chunk = b[r0:r0 + rows]
             m = chunk.shape[0]
@@ -509,9 +517,10 @@ def gptq_many(jobs, block_size=128, actorder=False, damping=0.01, bits=4, pack=T
         arena = arenas[wi]
         xs = list(xs)
         w_host = not (isinstance(W, torch.Tensor) and W.is_cuda)
-        x_host = bool(xs) and all(not (isinstance(x, torch.Tensor) and x.is_cuda) for x in xs)
-        if not w_host and not x_host:
-            return W, [_to_dev(x) for x in xs], None
+        on_host = [not (isinstance(x, torch.Tensor) and x.is_cuda) for x in xs]
+        x_host = bool(xs) and all(on_host)
+        if not w_host and not any(on_host):
+            return W, xs, None
         with torch.cuda.stream(copier):
             if done[wi] is not None:
                 copier.wait_event(done[wi])
@@ -537,8 +546,16 @@ def gptq_many(jobs, block_size=128, actorder=False, damping=0.01, bits=4, pack=T
                     xd = [arena.get(f'Xstage{j}', tuple(t.shape), t.dtype) for j, t in enumerate(ts)]
                     for v, t in zip(xd, ts):
                         v.copy_(t, non_blocking=True)
-            else:
-                xd = [_to_dev(x) for x in xs]
+            elif any(on_host):
+                # a mix of device- and host-resident batches: the host ones are staged like the rest, so that
+                # both consumer streams wait for their copies through the event recorded below
+                xd = list(xs)
+                for j, x in enumerate(xs):
+                    if on_host[j]:
+                        t = x if isinstance(x, torch.Tensor) else torch.from_numpy(np.ascontiguousarray(x))
+                        v = arena.get(f'Xstage{j}', tuple(t.shape), t.dtype)
+                        v.copy_(t, non_blocking=True)
+                        xd[j] = v
             ev = copier.record_event()
         return Wd, xd, ev
 
@@ -627,7 +644,10 @@ def gptq_many(jobs, block_size=128, actorder=False, damping=0.01, bits=4, pack=T
     main.wait_event(copier.record_event())
     if _issued_hook is not None:
         _issued_hook()                   # every launch of the call has been issued; nothing has been waited for
-    st = int(torch.stack(deferred).max().item()) if deferred else 0      # synchronises with every worker
+    st = 0
+    if deferred:                         # the words are bit sets: OR them (synchronises with every worker)
+        for w in torch.stack(deferred).reshape(-1).tolist():
+            st |= int(w)
     for a in arenas:
         a.release()
     harena.release()

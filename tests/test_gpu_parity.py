@@ -3,7 +3,12 @@
 Bars: bit-exact for packing, codes and per-channel parameters; >= 99.9 % identical
 quantized codes and reconstruction error within 1e-3 relative for whole-layer GPTQ;
 1e-2 relative for the packed-int4 matmul (the reference's own kernel test asserts a
-mean absolute gap below 3e-2, test_kernel.py:39-41)."""
+mean absolute gap below 3e-2, test_kernel.py:39-41).
+
+The 99.9 % bar is loosened in one measured case only: when the oracle, run against
+itself with a Hessian that differs by nothing but fp32 rounding (accumulated in fp64,
+then cast), already changes more than 0.05 % of the codes, the bar becomes twice that
+measured fraction (`bench.parity_bar`).  The measured floor is printed with the result."""
 import numpy as np
 import pytest
 import torch
@@ -139,7 +144,7 @@ def test_accumulate_H_large_split(G):
 
 
 # ------------------------------------------------------- damp + Cholesky inverse ----
-@pytest.mark.parametrize('K', [32, 64, 100, 256, 768, 840, 1536])      # 840: ragged last panel inside an outer block
+@pytest.mark.parametrize('K', [32, 64, 100, 256, 768, 840, 1536, 3072])      # 840: ragged last panel inside an outer block; 3072: the benchmark's largest
 def test_damp_invert_matches_oracle(G, K):
     import importlib; gg = importlib.import_module('jax_gptq_b200.gptq')
     rng = np.random.default_rng(30 + K)
@@ -215,7 +220,10 @@ def test_single_block_bit_exact(G, K, N, bs):
         assert (host(codes) == codes_ref).mean() >= 0.999
 
 
-def _gptq_parity(G, W, xs, bs, min_same=0.999, actorder=False):
+def _gptq_parity(G, W, xs, bs, floor=False, actorder=False):
+    """Whole-layer parity.  With `floor` the accepted fraction of differing codes is
+    max(1e-3, 2 x the oracle's own fp32-rounding floor on this input)."""
+    import bench
     Q_ref, p_ref, it = R.gptq(W, xs, block_size=bs, actorder=actorder, return_internals=True)
     Q, p, codes = G.gptq(dev(W), [dev(x) for x in xs], block_size=bs, actorder=actorder, return_codes=True)
     assert Q.dtype == torch.float32 and tuple(Q.shape) == W.shape
@@ -227,7 +235,14 @@ def _gptq_parity(G, W, xs, bs, min_same=0.999, actorder=False):
     e_ref = R.reconstruction_error(W, Q_ref, xs)
     e_got = R.reconstruction_error(W, Qh, xs)
     rel = abs(e_got - e_ref) / e_ref
-    assert same >= min_same, f'identical codes {same:.5f}'
+    bar = 1e-3
+    if floor:
+        H64 = R.accumulate_H_direct(xs, use_fp64=True)
+        _, _, it_f = R.gptq(W, xs, block_size=bs, actorder=actorder, H=H64.astype(np.float32), return_internals=True)
+        floor_mismatch = 1.0 - (it_f['codes'] == it['codes']).mean()
+        bar = bench.parity_bar(floor_mismatch)
+        print(f'oracle fp64-H vs fp32-H differ in {floor_mismatch:.5f} of the codes; bar {bar:.5f}; GPU vs oracle {1 - same:.5f}')
+    assert 1.0 - same <= bar, f'identical codes {same:.5f} (bar {1 - bar:.5f})'
     assert rel <= 1e-3, f'reconstruction error differs by {rel:.2e}'
     return same, rel
 
@@ -259,14 +274,14 @@ def test_gptq_large_k(G):
     mix = (rng.standard_normal((K, K)) / np.sqrt(K)).astype(np.float32)
     xs = [(rng.standard_normal((1024, K)).astype(np.float32) @ mix + 0.3 * rng.standard_normal((1024, K)).astype(np.float32))
           for _ in range(4)]
-    same, rel = _gptq_parity(G, W, xs, 128, min_same=0.995)
+    same, rel = _gptq_parity(G, W, xs, 128, floor=True)
     print(f'K=1536: identical codes {same:.6f}, recon rel diff {rel:.2e}')
 
 
 def test_gptq_correlated_activations(G):
     from jax_gptq_b200 import workloads
     W, xs = workloads.correlated_layer(51, 512, 640, 4096)
-    same, rel = _gptq_parity(G, W, xs, 128, min_same=0.995)
+    same, rel = _gptq_parity(G, W, xs, 128, floor=True)
     print(f'correlated: identical codes {same:.6f}, recon rel diff {rel:.2e}')
 
 
@@ -385,6 +400,39 @@ def test_matmul_sweep_shape_small_m(G):
     qm = R.QuantizedMatrix(R.pack_colwise(codes), zero, scale)
     _check_mm(G, qm, x, False)
     _check_mm(G, qm, x[:1], False)
+
+
+def _sweep_case_device(K, N, M, seed):
+    """Config-3 inputs generated on the device (uniform codes, fp16 scale ~U(0.001,0.02), integer fp16
+    zeros, fp16 x ~ N(0,1)); returned with host copies for the oracle."""
+    g = torch.Generator(device='cuda').manual_seed(seed)
+    packed = torch.randint(0, 256, (K // 2, N), generator=g, device='cuda', dtype=torch.uint8)
+    scale = (0.001 + 0.019 * torch.rand(N, generator=g, device='cuda')).half()
+    zero = torch.randint(0, 16, (N,), generator=g, device='cuda').half()
+    x = torch.randn((M, K), generator=g, device='cuda').half()
+    return packed, scale, zero, x
+
+
+@pytest.mark.parametrize('K,N,cols', [(4096, 4096, None), (4096, 11008, None), (11008, 4096, None), (8192, 28672, 512)])
+@pytest.mark.parametrize('M', [1, 16, 128, 2048])
+def test_matmul_sweep_shapes_against_oracle(G, K, N, M, cols):
+    """Every shape and M of the benchmark's matmul sweep against the oracle's fp32 dequant product;
+    the largest weight is checked on a random sample of 512 output channels so the CPU product stays small."""
+    packed, scale, zero, x = _sweep_case_device(K, N, M, 3003 + M)
+    qm = G.QuantizedMatrix(packed, zero, scale)
+    y = G.quantized_matmul(x, qm)
+    y2 = G.quantized_matmul(x, qm)
+    assert torch.equal(y, y2), 'repeated launches must agree bit for bit'
+    rng = np.random.default_rng(K + N + M)
+    sel = np.arange(N) if cols is None else np.sort(rng.choice(N, size=cols, replace=False))
+    sel_t = torch.from_numpy(sel).cuda()
+    qm_ref = R.QuantizedMatrix(host(packed[:, sel_t]), host(zero[sel_t]), host(scale[sel_t]))
+    ref = R.quantized_matmul(host(x), qm_ref).astype(np.float64)
+    got = host(y[:, sel_t]).astype(np.float64)
+    rel = np.linalg.norm(got - ref) / np.linalg.norm(ref)
+    assert rel <= 1e-2, f'relative error {rel:.3e}'
+    assert np.mean(np.abs(got - ref)) < 3e-2
+    assert np.abs(got - ref).max() <= 2e-2 * np.abs(ref).max()
 
 
 def test_matmul_leading_dims_grad_and_errors(G):
