@@ -535,7 +535,7 @@ def run_ours(args):
         dist.destroy_process_group()
 
 
-def bench_w4(torch, G, dev, peaks, cases=None):
+def bench_w4(torch, G, dev, peaks, cases=None, no_settled=False):
     """Config-3 sweep on one GPU: fp16 activations, fp16 scale/zero; weights rotated over
     enough distinct buffers to exceed L2 between launches."""
     hbm = float(peaks.get('hbm_gbs', 6650.0))
@@ -563,8 +563,10 @@ def bench_w4(torch, G, dev, peaks, cases=None):
             ws = torch.zeros(max(need, 1), dtype=torch.uint8, device=dev)
             out = torch.empty((M, N), dtype=torch.float16, device=dev)
             def launch(i, st):
+                # the weights were generated long before these launches: JGQ_W4_WEIGHTS_SETTLED holds
                 _lib.check(_lib.lib.jgq_w4_matmul(x.data_ptr(), _lib.F16, packed[i % nbuf].data_ptr(), zero.data_ptr(),
-                                                  scale.data_ptr(), _lib.F16, out.data_ptr(), M, N, K, 0,
+                                                  scale.data_ptr(), _lib.F16, out.data_ptr(), M, N, K,
+                                                  0 if no_settled else _lib.W4_WEIGHTS_SETTLED,
                                                   ws.data_ptr(), need, st))
             st = torch.cuda.current_stream().cuda_stream
             for i in range(3):
@@ -618,6 +620,8 @@ def main():
                     help='issue every Hessian GEMM on its linear\'s own stream instead of one lower-priority stream')
     ap.add_argument('--only-matmul', action='store_true', help='run only the packed-int4 matmul sweep')
     ap.add_argument('--matmul-shapes', default='', help='comma list of KxNxM cases for --only-matmul')
+    ap.add_argument('--no-settled', action='store_true',
+                    help='matmul sweep without JGQ_W4_WEIGHTS_SETTLED (no weight fetch ahead of the previous kernel\'s end)')
     ap.add_argument('--skip-cpu', action='store_true')
     ap.add_argument('--skip-parity', action='store_true', help='do not run the oracle comparison of block 0')
     args = ap.parse_args()
@@ -631,7 +635,8 @@ def main():
         except (OSError, ValueError):
             pass
         cases = [tuple(int(v) for v in c.split('x')) for c in args.matmul_shapes.split(',') if c]
-        print(json.dumps({'w4_matmul': bench_w4(torch, G, torch.device('cuda', 0), peaks, cases or None)}), flush=True)
+        print(json.dumps({'w4_matmul': bench_w4(torch, G, torch.device('cuda', 0), peaks, cases or None,
+                                                no_settled=args.no_settled)}), flush=True)
     elif args.impl == 'reference':
         run_reference(args)
     else:

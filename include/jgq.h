@@ -113,11 +113,20 @@ int jgq_gptq_quantize(float* W, const float* L, const float* scale, const float*
  * forward:      out[M, N]  = x[M, K]  @ dequant(packed[K/2, N])
  * transpose_b:  out[M, K]  = x[M, N]  @ dequant(packed[K/2, N])^T
  * x and out share x_dtype (F32/F16/BF16); zero/scale have zs_dtype (F32/F16),
- * one entry per output channel n.  Accumulation is fp32. */
+ * one entry per output channel n.  Accumulation is fp32.
+ * `flags`: JGQ_W4_TRANSPOSE_B (= 1, so the reference's transpose_b boolean can be
+ * passed as is) selects the transposed product.  JGQ_W4_WEIGHTS_SETTLED is a
+ * promise by the caller that packed, zero and scale were complete before the work
+ * enqueued just ahead of this call on `stream` started (weights loaded at start-up,
+ * say): the decode kernel then fetches its first weight tiles while the stream's
+ * previous kernel is still finishing.  Without the flag nothing is read early.
+ * The first 16384 bytes of the forward workspace must be zero before its first use
+ * (the kernels leave them zero); the rest needs no initialisation. */
+enum { JGQ_W4_TRANSPOSE_B = 1, JGQ_W4_WEIGHTS_SETTLED = 2 };
 size_t jgq_w4_matmul_workspace_bytes(int64_t M, int64_t N, int64_t K, int transpose_b);
 int jgq_w4_matmul(const void* x, int x_dtype, const uint8_t* packed,
                   const void* zero, const void* scale, int zs_dtype,
-                  void* out, int64_t M, int64_t N, int64_t K, int transpose_b,
+                  void* out, int64_t M, int64_t N, int64_t K, int flags,
                   void* ws, size_t ws_bytes, void* stream);
 
 /* ---- forward matmul without a caller workspace ----------------------------

@@ -13,6 +13,7 @@ LIB_PATH = os.path.join(HERE, 'libjgq.so')
 
 F32, F16, BF16, U8, I32 = 0, 1, 2, 3, 4
 STATUS_NOT_PD, STATUS_NAN, STATUS_TIMEOUT = 1, 2, 4
+W4_TRANSPOSE_B, W4_WEIGHTS_SETTLED = 1, 2
 
 _i64, _int, _vp, _sz = C.c_int64, C.c_int, C.c_void_p, C.c_size_t
 

@@ -37,6 +37,8 @@ def build(verbose=False, force=False):
     os.makedirs(OBJ, exist_ok=True)
     headers = [os.path.join(CSRC, f) for f in os.listdir(CSRC) if f.endswith(('.cuh', '.h'))]
     headers.append(os.path.join(HERE, '..', 'include', 'jgq.h'))
+    # measurement builds: JGQ_BUILD_DEFINES="-DJGQ_TRACE" adds the in-kernel timestamps of trace.cuh
+    extra = os.environ.get('JGQ_BUILD_DEFINES', '').split()
     jobs = []
     objs = []
     for src in sources():
@@ -44,7 +46,7 @@ def build(verbose=False, force=False):
         objs.append(obj)
         path = os.path.join(CSRC, src)
         if force or _stale(obj, [path] + headers):
-            cmd = [nvcc] + NVCC_FLAGS + (['-Xptxas', '-v'] if verbose else []) + ['-c', path, '-o', obj]
+            cmd = [nvcc] + NVCC_FLAGS + extra + (['-Xptxas', '-v'] if verbose else []) + ['-c', path, '-o', obj]
             jobs.append(cmd)
 
     def run(cmd):

@@ -277,6 +277,7 @@ w4_tb_kernel(const XT* __restrict__ x, const uint8_t* __restrict__ packed,
 }
 
 constexpr size_t kTicketBytes = 4096;   // 1024 tickets; split-K is only planned below 4 * #SM CTAs
+constexpr size_t kTicketRegionBytes = 16384;   // the largest ticket region of any forward kernel (f16 decode kernel)
 
 struct FwdPlan { int ntok; int mtiles; int ncg; int ksplit; int steps_per_split; };
 
@@ -326,10 +327,10 @@ static int launch_tb(const void* x, const uint8_t* packed, const void* zero, con
 constexpr int64_t kStreamRows = 16;          // token rows of one pass of the streaming kernel
 constexpr int64_t kStreamPassesMaxM = 32;    // two passes (120 us at 8192 x 28672) still beat the tensor-path kernel (128 us at M = 64)
 
-static int w4_path_override() {        // JGQ_W4_PATH=direct: direct-load decode kernel; =mma: no tcgen05 either
+static int w4_path_override() {        // JGQ_W4_PATH=direct: direct-load decode kernel; =mma: no tcgen05 either; =stream: no f16 decode kernel
   static const int v = []() {
     const char* e = getenv("JGQ_W4_PATH");
-    return !e ? 0 : !strcmp(e, "direct") ? 1 : !strcmp(e, "mma") ? 2 : 0;
+    return !e ? 0 : !strcmp(e, "direct") ? 1 : !strcmp(e, "mma") ? 2 : !strcmp(e, "stream") ? 3 : 0;
   }();
   return v;
 }
@@ -362,6 +363,10 @@ static size_t w4_forward_need(int64_t M, int64_t N, int64_t K, int x_dtype) {
   }
   const StreamPlan sp = plan_w4_stream(std::min<int64_t>(M, kStreamPassesMaxM) > kStreamRows ? kStreamRows : M, N, K);
   if (sp.use && M <= kStreamPassesMaxM) bytes = std::max(bytes, kTicketBytes + sp.part_bytes);
+  if (x_dtype < 0 || x_dtype == JGQ_F16) {
+    const GemvPlan gp = plan_w4_gemv(M, N, K);
+    if (gp.use) bytes = std::max(bytes, gp.ws_bytes);
+  }
   return bytes;
 }
 
@@ -382,10 +387,10 @@ static int w4_validate(const void* x, int x_dtype, const uint8_t* packed, const 
 
 }  // namespace jgq
 
-// Workspace layout (forward): 4096 bytes of int32 tickets, one per (row tile,
-// channel group), then [ksplit][M][channel groups][132] fp32 slices.  The ticket
-// bytes must be zero before the first launch that uses a workspace; every launch
-// leaves them zero again.  The slices need no initialisation.
+// Workspace layout (forward): int32 tickets first (4096 bytes, 16384 for the f16
+// decode kernel), then the kernels' fp32 slices.  The first 16384 bytes must be zero
+// before the first launch that uses a workspace; every launch leaves them zero
+// again.  The slices need no initialisation.
 // The size returned covers every activation dtype; a call is accepted with the
 // (possibly smaller) amount its own dtype needs.
 extern "C" size_t jgq_w4_matmul_workspace_bytes(int64_t M, int64_t N, int64_t K, int transpose_b) {
@@ -395,8 +400,11 @@ extern "C" size_t jgq_w4_matmul_workspace_bytes(int64_t M, int64_t N, int64_t K,
 
 extern "C" int jgq_w4_matmul(const void* x, int x_dtype, const uint8_t* packed,
                              const void* zero, const void* scale, int zs_dtype,
-                             void* out, int64_t M, int64_t N, int64_t K, int transpose_b,
+                             void* out, int64_t M, int64_t N, int64_t K, int flags,
                              void* ws, size_t ws_bytes, void* stream) {
+  JGQ_REQUIRE((flags & ~(JGQ_W4_TRANSPOSE_B | JGQ_W4_WEIGHTS_SETTLED)) == 0, JGQ_ERR_ARG, "w4_matmul: unknown flag bits %d", flags);
+  const int transpose_b = flags & JGQ_W4_TRANSPOSE_B;
+  const int settled = (flags & JGQ_W4_WEIGHTS_SETTLED) ? 1 : 0;
   if (const int rc = w4_validate(x, x_dtype, packed, zero, scale, zs_dtype, out, M, N, K)) return rc;
   if (M == 0) return JGQ_OK;
   cudaStream_t s = (cudaStream_t)stream;
@@ -413,7 +421,12 @@ extern "C" int jgq_w4_matmul(const void* x, int x_dtype, const uint8_t* packed,
   const size_t need = w4_forward_need(M, N, K, x_dtype);
   JGQ_REQUIRE(ws && ws_bytes >= need, JGQ_ERR_WORKSPACE, "w4_matmul: workspace %zu < %zu bytes", ws_bytes, need);
   JGQ_REQUIRE(aligned(ws, 256), JGQ_ERR_ALIGN, "w4_matmul: workspace must be 256-byte aligned");
-  if (w4_path_override() == 0) {
+  if (w4_path_override() == 0 && x_dtype == JGQ_F16) {
+    const GemvPlan gp = plan_w4_gemv(M, N, K);
+    if (gp.use && aligned(packed, 16) && aligned(x, 16) && aligned(out, 8))
+      return launch_w4_gemv(gp, x, packed, zero, scale, zs_dtype, out, M, N, K, ws, settled, s);
+  }
+  if (w4_path_override() == 0 || w4_path_override() == 3) {
     const StreamPlan sp = plan_w4_stream(M, N, K);
     if (sp.use && aligned(packed, 16)) return launch_w4_stream(sp, x, x_dtype, packed, zero, scale, zs_dtype, out, M, N, K, ws, s);
     // A few more tokens than one pass of the streaming kernel takes: one pass per 16 token rows (60 us
@@ -515,7 +528,7 @@ extern "C" int jgq_w4_matmul_noalloc(const void* x, int x_dtype, const uint8_t* 
   const int rc = w4_scratch_address(&ws);
   if (rc) return rc;
   // tickets must read zero when the kernel starts, whatever an earlier call left behind
-  cudaError_t e = cudaMemsetAsync(ws, 0, kTicketBytes, (cudaStream_t)stream);
+  cudaError_t e = cudaMemsetAsync(ws, 0, kTicketRegionBytes, (cudaStream_t)stream);
   if (e != cudaSuccess) return fail(JGQ_ERR_CUDA, "w4_matmul_noalloc: cudaMemsetAsync: %s", cudaGetErrorString(e));
   return jgq_w4_matmul(x, x_dtype, packed, zero, scale, zs_dtype, out, M, N, K, 0, ws, kNoAllocScratchBytes, stream);
 }

@@ -28,4 +28,15 @@ int launch_w4_stream(const StreamPlan& pl, const void* x, int x_dtype, const uin
                      const void* scale, int zs_dtype, void* out, int64_t M, int64_t N, int64_t K, void* ws,
                      cudaStream_t s);
 
+// f16 decode kernel for M <= 8 (w4_gemv.cu)
+struct GemvPlan {
+  int use; int nt; int rows; int ncg; int spc; int64_t S; int G; int maxc;
+  size_t part_bytes;     // slices in the workspace (after the ticket region)
+  size_t ws_bytes;       // tickets + slices
+  int smem_bytes;        // dynamic shared memory per CTA
+};
+GemvPlan plan_w4_gemv(int64_t M, int64_t N, int64_t K);
+int launch_w4_gemv(const GemvPlan& pl, const void* x, const uint8_t* packed, const void* zero, const void* scale,
+                   int zs_dtype, void* out, int64_t M, int64_t N, int64_t K, void* ws, int settled, cudaStream_t s);
+
 }  // namespace jgq

@@ -27,24 +27,19 @@
 // 16g..16g+15 and byte rows q, q+4 of a step; the swizzle spreads the byte rows a quarter
 // warp reads over different banks.
 //
-// Building with -DJGQ_SV_TRACE adds per-CTA timestamps (entry, first box, last stage, exit)
-// and an extra exported function that copies them out; the library proper never defines it.
+// A measurement build (-DJGQ_TRACE, trace.cuh) adds per-CTA timestamps (entry, first box, last stage, exit).
 #include "w4_common.cuh"
 #include "w4_plans.cuh"
 #include "umma.cuh"
+#include "trace.cuh"
 #include <algorithm>
 #include <cstring>
 
 
 namespace jgq {
 
-#ifdef JGQ_SV_TRACE
-__device__ unsigned long long g_trace[8 * 1024];
-__device__ __forceinline__ unsigned long long gtime() { unsigned long long t; asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t)); return t; }
-#define TRACE(i) do { if (threadIdx.x == 0 && blockIdx.x < 1024) { g_trace[8 * blockIdx.x + (i)] = gtime(); if ((i) == 0) { unsigned sm; asm volatile("mov.u32 %0, %smid;" : "=r"(sm)); g_trace[8 * blockIdx.x + 4] = sm; } } } while (0)
-#else
-#define TRACE(i) do {} while (0)
-#endif
+JGQ_TRACE_DEFINE(stream, 8 * 1024)
+#define TRACE(i) JGQ_TRACE_CTA(stream, i, 1024)
 
 constexpr int S_NST = 3;                      // stages in flight per CTA
 constexpr int S_STEPS = 16;                   // contraction steps (8 byte rows each) per stage
@@ -469,11 +464,5 @@ int launch_w4_stream(const StreamPlan& pl, const void* x, int x_dtype, const uin
   JGQ_STREAM(__nv_bfloat16, __nv_bfloat16);
 #undef JGQ_STREAM
 }
-
-#ifdef JGQ_SV_TRACE
-extern "C" int jgq_dbg_trace(unsigned long long* host) {
-  return (int)cudaMemcpyFromSymbol(host, g_trace, sizeof(unsigned long long) * 8 * 1024);
-}
-#endif
 
 }  // namespace jgq

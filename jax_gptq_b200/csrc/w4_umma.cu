@@ -20,6 +20,7 @@
 // At small M the kernel is HBM-bound (one pass over K*N/2 bytes, ~1.3 instructions per code
 // for the expansion, everything else on the tensor pipe); at large M it is tensor-bound.
 #include "umma.cuh"
+#include "trace.cuh"
 #include "w4_common.cuh"
 #include "w4_plans.cuh"
 #include <algorithm>
@@ -141,15 +142,10 @@ __device__ __forceinline__ void expand_word(uint32_t w, uint32_t mask_lo, uint32
 #define U_LEADER_PROD (lane == 0)
 #define U_LEADER_MMA elect_one()
 
-#ifdef JGQ_UMMA_TRACE
-// per-stage timestamps of CTA (0, 0, 0): [kind][stage], kinds: 0 raw issued, 1 x issued, 2 raw landed (expansion
-// warp), 3 expanded tile published, 4 MMA thread has both operands, 5 MMAs issued
-__device__ unsigned long long g_utrace[10 * 256];
-__device__ __forceinline__ unsigned long long ugtime() { return (unsigned long long)clock64(); }   // SM cycles: cheap to read, one SM only
-#define UTRACE(kind, i) do { if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && (i) < 256) g_utrace[(kind) * 256 + (i)] = ugtime(); } while (0)
-#else
-#define UTRACE(kind, i) do {} while (0)
-#endif
+// per-stage timestamps of CTA (0, 0, 0) in measurement builds: [kind][stage], kinds: 0 raw issued, 1 x issued,
+// 2 raw landed (expansion warp), 3 expanded tile published, 4 MMA thread has both operands, 5 MMAs issued
+JGQ_TRACE_DEFINE(umma, 10 * 256)
+#define UTRACE(kind, i) JGQ_TRACE_STAGE(umma, kind, i, 256)
 
 template <typename XT, typename ZST, int FMT>
 __global__ void __launch_bounds__(U_THREADS, 1)
@@ -586,10 +582,5 @@ int launch_w4_umma(const UmmaPlan& pl, const void* x, int x_dtype, const uint8_t
   return zf32 ? launch_inst<float, float, 1>(pl, p, wmap, x0, x1, s) : launch_inst<float, __half, 1>(pl, p, wmap, x0, x1, s);
 }
 
-#ifdef JGQ_UMMA_TRACE
-extern "C" int jgq_dbg_utrace(unsigned long long* host) {
-  return (int)cudaMemcpyFromSymbol(host, g_utrace, sizeof(unsigned long long) * 10 * 256);
-}
-#endif
 
 }  // namespace jgq

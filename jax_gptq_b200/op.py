@@ -19,6 +19,16 @@ from .gptq import _to_dev, _out, _is_np, _stream, _workspace, _DT
 _ZS = {torch.float32: _lib.F32, torch.float16: _lib.F16}
 
 
+def _settled(w):
+    """True from the second matmul on an unchanged packed-weight tensor: the weights were then complete
+    before the kernel enqueued just ahead of this call (at the latest, the previous matmul on them)
+    started, which is what JGQ_W4_WEIGHTS_SETTLED promises.  An in-place update through torch bumps the
+    tensor's version counter and makes the next call an ordinary one again."""
+    seen = getattr(w, '_jgq_seen_version', None)
+    w._jgq_seen_version = w._version
+    return seen == w._version
+
+
 def _launch(x, w, zero, scale, transpose_b):
     lead = None
     if x.dim() > 2:                                   # op.py:21-24
@@ -37,8 +47,9 @@ def _launch(x, w, zero, scale, transpose_b):
     out = torch.empty((M, out_n), dtype=x.dtype, device=x.device)
     need = lib.jgq_w4_matmul_workspace_bytes(M, Nw, Kw, int(transpose_b))
     ws = _workspace(need, zeroed=True, tag='w4') if need else None
+    flags = (_lib.W4_TRANSPOSE_B if transpose_b else 0) | (_lib.W4_WEIGHTS_SETTLED if _settled(w) else 0)
     check(lib.jgq_w4_matmul(x.data_ptr(), _DT[x.dtype], w.data_ptr(), zero.data_ptr(), scale.data_ptr(),
-                            _ZS[zero.dtype], out.data_ptr(), M, Nw, Kw, int(transpose_b),
+                            _ZS[zero.dtype], out.data_ptr(), M, Nw, Kw, flags,
                             0 if ws is None else ws.data_ptr(), need, _stream()))
     if lead is not None:
         out = out.reshape(tuple(lead) + (out_n,))
