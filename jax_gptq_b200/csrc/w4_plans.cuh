@@ -31,6 +31,7 @@ int launch_w4_stream(const StreamPlan& pl, const void* x, int x_dtype, const uin
 // f16 decode kernel for M <= 8 (w4_gemv.cu)
 struct GemvPlan {
   int use; int nt; int rows; int ncg; int spc; int64_t S; int G; int maxc;
+  int cb, nbig, cs, nsmall, nunits;      // chunks of a group's contraction range (big ones first, short ones last)
   size_t part_bytes;     // slices in the workspace (after the ticket region)
   size_t ws_bytes;       // tickets + slices
   int smem_bytes;        // dynamic shared memory per CTA
