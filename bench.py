@@ -16,8 +16,12 @@ weight as soon as it exists (the reference's default calibration mode).
 
 `--impl reference` times the CPU oracle (NumPy/SciPy restatement of the reference,
 all host cores) on a bounded sample of the same workload: one block (4 linears).
-Multi-GPU (`torchrun`, one rank per GPU): ranks quantize independent models
-(layer-parallel, no data-path collective): weak scaling.
+Multi-GPU (`torchrun`, one rank per GPU): ONE model, strong scaling.  The calibration
+tokens of every linear are sharded over the ranks; per linear the local Hessian sums
+are all-reduced over NCCL (lower triangle only, overlapped with the next Hessian
+GEMM), the quantize loop is sharded over output channels, and the packed column slabs
+are all-gathered.  The line also carries the layer-parallel form (one independent
+model per rank, no collective) under `replicas`, and the packed matmul sharded over N.
 """
 from __future__ import annotations
 
@@ -288,6 +292,112 @@ def run_reference(args):
     print(json.dumps(line), flush=True)
 
 
+
+def e2e_single(torch, gg, args, dev, model, acts, layers, total_weights, barrier):
+    """End to end on one GPU: weights and calibration inputs in pinned host memory, every step copies them to
+    the device (overlapped with compute by gptq_many) and the packed result back."""
+    world = 1
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    free_host = 0
+    try:
+        for ln in open('/proc/meminfo'):
+            if ln.startswith('MemAvailable'):
+                free_host = int(ln.split()[1]) * 1024
+    except OSError:
+        pass
+    per_layer = sum(a.numel() * 4 for a in acts[0].values())
+    budget = min(free_host // (2 * max(world, 1)), 24 << 30) if free_host else 4 << 30
+    distinct = max(1, min(layers, budget // per_layer))
+    host_acts = [{k: v.cpu().pin_memory() for k, v in acts[i].items()} for i in range(distinct)]
+    host_w = [{k: v.cpu().pin_memory() for k, v in m.items()} for m in model]
+    host_out = [{name: (torch.empty((k // 2, n), dtype=torch.uint8).pin_memory(),
+                        torch.empty(n, dtype=torch.float32).pin_memory(),
+                        torch.empty(n, dtype=torch.float32).pin_memory()) for name, k, n in LINEARS}
+                for _ in range(layers)]
+    acts_dev_bytes = sum(v.numel() * 4 for a in acts for v in a.values())
+    torch.cuda.empty_cache()
+    h2d = sum(host_acts[i % distinct][name].numel() * 4 + host_w[i][name].numel() * 4
+              for i in range(layers) for name, _, _ in LINEARS)
+    d2h = sum(sum(t.numel() * t.element_size() for t in host_out[i][name])
+              for i in range(layers) for name, _, _ in LINEARS)
+
+    def step_e2e():
+        jobs = [(host_w[i][name], list(host_acts[i % distinct][name].chunk(CALIB_BATCHES)))
+                for i in range(layers) for name, _, _ in LINEARS]
+        outs = [host_out[i][name] for i in range(layers) for name, _, _ in LINEARS]
+        gg.gptq_many(jobs, block_size=BLOCK_SIZE, damping=DAMP, pack=True, out_host=outs, streams=args.streams,
+                     hessian_stream=not args.no_hessian_stream)
+        torch.cuda.synchronize()
+
+    for _ in range(min(args.warmup, 3)):
+        step_e2e()
+    barrier()
+    e0.record()
+    for _ in range(args.steps):
+        step_e2e()
+    e1.record()
+    torch.cuda.synchronize()
+    t = torch.tensor([e0.elapsed_time(e1) / args.steps], device=dev, dtype=torch.float64)
+    e2e_ms = float(t.item())
+    e2e = {'value': world * total_weights / (e2e_ms * 1e-3), 'unit': UNIT, 'ms_per_step': e2e_ms,
+           'h2d_bytes_per_step': h2d, 'd2h_bytes_per_step': d2h,
+           'distinct_activation_sets_in_pinned_memory': distinct}
+    del host_acts, host_w, host_out
+    return e2e, acts_dev_bytes
+
+
+def e2e_sharded(torch, dist, args, dev, rank, world, model, acts, pipe, shard, total_weights, barrier):
+    """End to end on N GPUs: every rank holds ITS token shard of every calibration input and the weights in
+    pinned host memory; a step copies them to the device (copy stream, one event per linear), runs the
+    sharded pipeline on them and rank 0 reads the packed model back."""
+    b, e = shard
+    layers = len(model)
+    host_acts = [{k: v[b:e].cpu().pin_memory() for k, v in a.items()} for a in acts]
+    host_w = [{k: v.cpu().pin_memory() for k, v in m.items()} for m in model]
+    dev_acts = [{k: torch.empty_like(v, device=dev) for k, v in a.items()} for a in host_acts]
+    dev_w = [{k: torch.empty_like(v, device=dev) for k, v in m.items()} for m in host_w]
+    host_out = [{name: torch.empty((k // 2, n), dtype=torch.uint8).pin_memory() for name, k, n in LINEARS} for _ in range(layers)]
+    copier = torch.cuda.Stream()
+    h2d = sum(v.numel() * 4 for a in host_acts for v in a.values()) + sum(v.numel() * 4 for m in host_w for v in m.values())
+    d2h = sum(t.numel() for o in host_out for t in o.values())
+    nb = max(1, CALIB_BATCHES // world)
+
+    def step():
+        jobs = []
+        copier.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(copier):
+            for i in range(layers):
+                for name, _, _ in LINEARS:
+                    dev_w[i][name].copy_(host_w[i][name], non_blocking=True)
+                    dev_acts[i][name].copy_(host_acts[i][name], non_blocking=True)
+                    jobs.append((dev_w[i][name], list(dev_acts[i][name].chunk(nb)), copier.record_event()))
+        res = pipe.run(jobs, N_SEQ * SEQ, block_size=BLOCK_SIZE, damping=DAMP)
+        if rank == 0:
+            j = 0
+            for i in range(layers):
+                for name, _, _ in LINEARS:
+                    host_out[i][name].copy_(res[j][0], non_blocking=True)
+                    j += 1
+        torch.cuda.synchronize()
+
+    for _ in range(min(args.warmup, 3)):
+        step()
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        step()
+    e1.record()
+    torch.cuda.synchronize()
+    t = torch.tensor([e0.elapsed_time(e1) / args.steps], device=dev, dtype=torch.float64)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms = float(t.item())
+    return {'value': total_weights / (ms * 1e-3), 'unit': UNIT, 'ms_per_step': ms,
+            'h2d_bytes_per_step': h2d * world, 'd2h_bytes_per_step': d2h,
+            'h2d_bytes_per_step_per_rank': h2d, 'h2d_GBps_per_rank': h2d / (ms * 1e-3) / 1e9,
+            'what': 'one model on all ranks: each rank copies its token shard of every calibration input and the weights '
+                    'host->device, rank 0 reads the packed model back'}
+
 # --------------------------------------------------------------------------
 # our arm
 # --------------------------------------------------------------------------
@@ -313,7 +423,7 @@ def run_ours(args):
         torch.cuda.synchronize()
 
     layers = args.layers
-    gen = torch.Generator(device=dev).manual_seed(2002 + rank)
+    gen = torch.Generator(device=dev).manual_seed(2002)       # the same model on every rank
 
     # ---- untimed set-up: weights, and calibration inputs captured with quantized weights in place ----
     h = embed(torch, gen, dev)
@@ -363,6 +473,66 @@ def run_ours(args):
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
     ms_max = float(t.item())
     value = world * total_weights / (ms_max * 1e-3)
+
+    # ---- N > 1: one model, tokens sharded over the ranks (strong scaling) ----
+    replicas = None
+    sharded = None
+    if world > 1:
+        from jax_gptq_b200 import dist as D
+        replicas = {'value': value, 'unit': UNIT, 'ms_per_step': ms_max, 'scaling': 'weak',
+                    'what': f'{world} independent models, one per GPU, no data-path collective'}
+        n_tok = N_SEQ * SEQ
+        b, e = D.shard_range(n_tok, rank, world, 64)
+        pipe = D.ShardedPipeline(streams=min(args.streams, 8))
+
+        def sharded_jobs():
+            return [(weights[name], list(captured[name][b:e].chunk(max(1, CALIB_BATCHES // world))))
+                    for weights, captured in zip(model, acts) for name, _, _ in LINEARS]
+
+        def step_sharded():
+            return pipe.run(sharded_jobs(), n_tok, block_size=BLOCK_SIZE, damping=DAMP)
+        for _ in range(args.warmup):
+            out_sh = step_sharded()
+        barrier()
+        launches0 = lib.jgq_launch_count()
+        e0.record()
+        for _ in range(args.steps):
+            out_sh = step_sharded()
+        e1.record()
+        torch.cuda.synchronize()
+        launches = lib.jgq_launch_count() - launches0
+        t = torch.tensor([e0.elapsed_time(e1) / args.steps], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms_max = float(t.item())
+        value = total_weights / (ms_max * 1e-3)           # ONE model: strong scaling
+        # collective alone: the all-reduces of one step, back to back
+        bufs = [torch.zeros(lib.jgq_hessian_lower_elems(k), dtype=torch.float32, device=dev) for _, k, _ in LINEARS]
+        for _ in range(2):
+            for bf in bufs:
+                dist.all_reduce(bf)
+        barrier()
+        e0.record()
+        for _ in range(layers):
+            for bf in bufs:
+                dist.all_reduce(bf)
+        e1.record()
+        torch.cuda.synchronize()
+        ar_ms = e0.elapsed_time(e1)
+        # check: the sharded result of block 0 against the single-GPU path on the same data
+        same = []
+        for j, (name, _, _) in enumerate(LINEARS):
+            Q1, p1 = gg.gptq(model[0][name], list(acts[0][name].chunk(CALIB_BATCHES)), block_size=BLOCK_SIZE, damping=DAMP)
+            ref_packed = G.pack_matrix(Q1, p1).int_weight
+            got = out_sh[j][0]
+            lo = ((got & 15) == (ref_packed & 15)).float().mean()
+            hi = ((got >> 4) == (ref_packed >> 4)).float().mean()
+            same.append(float((lo + hi) / 2))
+        sharded = {'collective': 'NCCL all-reduce (sum, fp32) of the lower block triangle of every Hessian, one per linear; '
+                                 'all-gather of the packed column slabs on a second communicator',
+                   'allreduce_bytes_per_step': pipe.stats['allreduce_bytes'], 'allgather_bytes_per_step': pipe.stats['allgather_bytes'],
+                   'allreduce_ms_alone_per_step': ar_ms, 'allreduce_share_of_step': ar_ms / ms_max,
+                   'tokens_per_rank': e - b,
+                   'check_same_codes_block0_vs_single_gpu': same, 'check_ok': bool(min(same) >= 0.999)}
 
     # ---- the same work issued one linear at a time, in the order the calibration forward needs the
     # quantized weights (layer l+1's input depends on layer l's result): nothing overlaps ----
@@ -442,59 +612,25 @@ def run_ours(args):
     stages = {k2: round(v, 4) for k2, v in stages.items()}
 
     # ---- e2e: pinned host buffers in, packed result out, all copies inside the timed region ----
-    free_host = 0
-    try:
-        for ln in open('/proc/meminfo'):
-            if ln.startswith('MemAvailable'):
-                free_host = int(ln.split()[1]) * 1024
-    except OSError:
-        pass
-    per_layer = sum(a.numel() * 4 for a in acts[0].values())
-    budget = min(free_host // (2 * max(world, 1)), 24 << 30) if free_host else 4 << 30
-    distinct = max(1, min(layers, budget // per_layer))
-    host_acts = [{k: v.cpu().pin_memory() for k, v in acts[i].items()} for i in range(distinct)]
-    host_w = [{k: v.cpu().pin_memory() for k, v in m.items()} for m in model]
-    host_out = [{name: (torch.empty((k // 2, n), dtype=torch.uint8).pin_memory(),
-                        torch.empty(n, dtype=torch.float32).pin_memory(),
-                        torch.empty(n, dtype=torch.float32).pin_memory()) for name, k, n in LINEARS}
-                for _ in range(layers)]
-    acts_dev_bytes = sum(v.numel() * 4 for a in acts for v in a.values())
-    del acts, model, x_big, batches
-    torch.cuda.empty_cache()
-    h2d = sum(host_acts[i % distinct][name].numel() * 4 + host_w[i][name].numel() * 4
-              for i in range(layers) for name, _, _ in LINEARS)
-    d2h = sum(sum(t.numel() * t.element_size() for t in host_out[i][name])
-              for i in range(layers) for name, _, _ in LINEARS)
-
-    def step_e2e():
-        jobs = [(host_w[i][name], list(host_acts[i % distinct][name].chunk(CALIB_BATCHES)))
-                for i in range(layers) for name, _, _ in LINEARS]
-        outs = [host_out[i][name] for i in range(layers) for name, _, _ in LINEARS]
-        gg.gptq_many(jobs, block_size=BLOCK_SIZE, damping=DAMP, pack=True, out_host=outs, streams=args.streams,
-                     hessian_stream=not args.no_hessian_stream)
-        torch.cuda.synchronize()
-
-    for _ in range(min(args.warmup, 3)):
-        step_e2e()
-    barrier()
-    e0.record()
-    for _ in range(args.steps):
-        step_e2e()
-    e1.record()
-    torch.cuda.synchronize()
-    t = torch.tensor([e0.elapsed_time(e1) / args.steps], device=dev, dtype=torch.float64)
     if world > 1:
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    e2e_ms = float(t.item())
-    e2e = {'value': world * total_weights / (e2e_ms * 1e-3), 'unit': UNIT, 'ms_per_step': e2e_ms,
-           'h2d_bytes_per_step': h2d, 'd2h_bytes_per_step': d2h,
-           'distinct_activation_sets_in_pinned_memory': distinct}
-    del host_acts, host_w, host_out
+        e2e = e2e_sharded(torch, dist, args, dev, rank, world, model, acts, pipe, (b, e), total_weights, barrier)
+        acts_dev_bytes = sum(v.numel() * 4 for a in acts for v in a.values())
+        del acts, model, x_big, batches
+        torch.cuda.empty_cache()
+    else:
+        model_h, acts_h = model, acts
+        del acts, model, x_big, batches
+        e2e, acts_dev_bytes = e2e_single(torch, gg, args, dev, model_h, acts_h, layers, total_weights, barrier)
+        del model_h, acts_h
 
     # ---- packed-int4 matmul: HBM GB/s at M=1, TFLOP/s at M=2048 (single rank numbers) ----
     w4 = []
     if rank == 0 and not args.skip_matmul:
         w4 = bench_w4(torch, G, dev, peaks)
+
+    w4_sharded = None
+    if world > 1 and not args.skip_matmul:
+        w4_sharded = bench_w4_sharded(torch, dist, dev, rank, world, peaks)
 
     cpu_baseline = None
     if rank == 0 and world == 1 and not args.skip_cpu:
@@ -516,11 +652,14 @@ def run_ours(args):
 
     if rank == 0:
         line = {'metric': METRIC, 'value': value, 'unit': UNIT, 'n_gpus': world, 'steps': args.steps,
-                'warmup': args.warmup, 'ms_per_step': ms_max, 'higher_is_better': True, 'scaling': 'weak',
+                'warmup': args.warmup, 'ms_per_step': ms_max, 'higher_is_better': True,
+                'scaling': 'strong' if world > 1 else 'weak',
                 'vs_baseline': None, 'dtype': 'f32', 'data': 'synthetic',
-                'config': {'workload': workload_name(layers), 'weights_per_step_per_gpu': total_weights,
+                'config': {'workload': workload_name(layers), 'weights_per_step': total_weights,
                            'l2': 'inputs larger than L2 (each linear reads 0.2-0.8 GB of activations)',
-                           'parallelism': f'{world} independent models, one per GPU, no data-path collective',
+                           'parallelism': (f'one model on {world} GPUs: calibration tokens sharded, Hessians all-reduced (NCCL), '
+                                           'quantize loop sharded over output channels, packed slabs all-gathered'
+                                           if world > 1 else 'one GPU'),
                            'linears_in_flight_per_gpu': args.streams,
                            'resident_activation_bytes_per_gpu': acts_dev_bytes, 'setup_seconds': setup_s},
                 'clocks': clocks, 'e2e': e2e, 'gpu_launches': int(launches), 'roofline': roofline,
@@ -529,10 +668,196 @@ def run_ours(args):
                 'value_note': 'the 48 linears are issued as independent jobs (calibration inputs captured beforehand); '
                               'ms_per_step_one_linear_at_a_time is the same work with nothing overlapped, the order a '
                               'calibration forward with quantized weights in place imposes',
-                'parity': parity}
+                'parity': parity, 'replicas': replicas, 'sharded': sharded, 'w4_matmul_sharded': w4_sharded}
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()
+
+
+
+# --------------------------------------------------------------------------
+# sized workloads: Llama-7B-shaped linears and one 70B-shaped block (bf16 weights and activations)
+# --------------------------------------------------------------------------
+SIZED = {
+    # name: (distinct linears (K, N, how many per block), calibration tokens, bits to run, blocks in the model)
+    'llama7b-linear': (((4096, 4096, 4), (4096, 11008, 2), (11008, 4096, 1)), 128 * 2048, (4,), 32),
+    'llama70b-block': (((8192, 8192, 2), (8192, 1024, 2), (8192, 28672, 2), (28672, 8192, 1)), 65536, (4, 3), 1),
+}
+ORACLE_MAX_K = 8192          # the CPU oracle is run up to this contraction size ...
+ORACLE_COLS = 512            # ... on this many output channels (channels are independent given the factor)
+
+
+def run_sized(args):
+    """One linear per distinct shape of the workload: bf16 W ~ 0.02 N(0,1), bf16 X ~ N(0,1) (the configuration's
+    calibration data is random by definition), GPTQ + pack, per-stage device time.  Checks: up to K = 8192 the
+    CPU oracle on a slice of the output channels (identical codes, reconstruction error); above that the
+    residual of the factor, the status word, and the reconstruction error against round-to-nearest."""
+    import importlib
+    import torch
+    import torch.distributed as dist
+    import jax_gptq_b200 as G
+    gg = importlib.import_module('jax_gptq_b200.gptq')
+    from jax_gptq_b200._lib import lib
+    world = int(os.environ.get('WORLD_SIZE', '1'))
+    rank = int(os.environ.get('RANK', '0'))
+    local = int(os.environ.get('LOCAL_RANK', '0'))
+    torch.cuda.set_device(local)
+    dev = torch.device('cuda', local)
+    pipe = None
+    if world > 1:
+        dist.init_process_group('nccl', device_id=dev)
+        from jax_gptq_b200 import dist as D
+        pipe = D.ShardedPipeline(streams=2)
+    shapes, n_tok, bit_list, blocks = SIZED[args.workload]
+    peaks = {}
+    try:
+        peaks = json.load(open(os.path.join(ROOT, 'MEASURED_PEAKS.json')))
+    except (OSError, ValueError):
+        pass
+    seed = 4004 if args.workload.startswith('llama7b') else 5005
+    rows, total_ms, total_weights = [], 0.0, 0
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    for (K, N, count) in shapes:
+        gen = torch.Generator(device=dev).manual_seed(seed + K + N)
+        W = (0.02 * torch.randn((K, N), generator=gen, device=dev)).bfloat16()
+        X = torch.empty((n_tok, K), dtype=torch.bfloat16, device=dev)
+        for r0 in range(0, n_tok, 16384):                   # generated in pieces: no fp32 copy of the whole batch
+            X[r0:r0 + 16384] = torch.randn((min(16384, n_tok - r0), K), generator=gen, device=dev).bfloat16()
+        b, e = (0, n_tok)
+        if world > 1:
+            b, e = D.shard_range(n_tok, rank, world, 64)
+        xs = list(X[b:e].chunk(max(1, 16 // world)))
+        for bits in bit_list:
+            def one():
+                if world > 1:
+                    return pipe.run([(W, xs)], n_tok, block_size=BLOCK_SIZE, damping=DAMP, bits=bits)[0]
+                Q, params = gg.gptq(W, xs, block_size=BLOCK_SIZE, damping=DAMP, bits=bits)
+                return G.pack_matrix(Q, params)
+            for _ in range(max(1, min(args.warmup, 2))):
+                one()
+            torch.cuda.synchronize()
+            if world > 1:
+                dist.barrier()
+            reps = max(1, min(args.steps, 3))
+            e0.record()
+            for _ in range(reps):
+                one()
+            e1.record()
+            torch.cuda.synchronize()
+            t = torch.tensor([e0.elapsed_time(e1) / reps], device=dev, dtype=torch.float64)
+            if world > 1:
+                dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+            row = {'K': K, 'N': N, 'bits': bits, 'per_block': count, 'ms': ms, 'weights_per_s': K * N / (ms * 1e-3)}
+            if rank == 0 and world == 1:
+                row.update(sized_stages(torch, gg, G, W, xs, bits))
+                if not args.skip_parity:
+                    # the CPU oracle runs for the first bit width of every shape and for the second one on the
+                    # smallest shape only (it takes about a minute per run at these sizes)
+                    with_oracle = bits == bit_list[0] or N <= 1024
+                    row['check'] = sized_check(torch, gg, W, xs, bits, K, N, with_oracle)
+            rows.append(row)
+            if bits == bit_list[0]:
+                total_ms += ms * count
+                total_weights += K * N * count
+        del W, X, xs
+        torch.cuda.empty_cache()
+    clocks = sampler.stop() if rank == 0 else None
+    if rank == 0:
+        big = max((r for r in rows if 'stage_ms' in r), key=lambda r: r['stage_ms']['hessian'], default=None)
+        roofline = None
+        if big is not None:
+            flops = 2.0 * n_tok * big['K'] * big['K']
+            peak = float(peaks.get('bf16_tflops', 1590.0))
+            ach = flops / (big['stage_ms']['hessian'] * 1e-3) / 1e12
+            roofline = {'kernel': f"hessian_accum (H += X^T X, K={big['K']}, n={n_tok}, bf16 activations)", 'bound': 'tensor',
+                        'achieved': ach, 'peak': peak, 'unit': 'TFLOP/s', 'frac': ach / peak,
+                        'peak_source': 'MEASURED_PEAKS.json bf16_tflops (burst: the stage is timed in isolation)' if peaks else 'fallback',
+                        'traffic': None}
+        line = {'metric': METRIC, 'value': total_weights / (total_ms * 1e-3), 'unit': UNIT, 'n_gpus': world,
+                'steps': max(1, min(args.steps, 3)), 'warmup': max(1, min(args.warmup, 2)), 'ms_per_step': total_ms,
+                'higher_is_better': True, 'scaling': 'strong' if world > 1 else 'weak', 'vs_baseline': None,
+                'dtype': 'f32 (bf16 weights and activations in, fp32 arithmetic)', 'data': 'synthetic',
+                'config': {'workload': f'{args.workload}: one linear per distinct shape, weighted by its count per block '
+                                       f'({blocks} block(s) in the model), {n_tok} calibration tokens, blocksize {BLOCK_SIZE}, damp {DAMP}',
+                           'l2': 'inputs larger than L2'},
+                'clocks': clocks, 'layers': rows, 'roofline': roofline,
+                'model_seconds_extrapolated': total_ms * 1e-3 * blocks,
+                'note': 'ms_per_step = one block (each distinct linear timed alone, times its count); the whole-model '
+                        'figure multiplies by the number of blocks (extrapolated, identical shapes)'}
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def sized_stages(torch, gg, G, W, xs, bits):
+    stages = {}
+
+    def timed(label, fn):
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        r = fn()
+        b.record()
+        torch.cuda.synchronize()
+        stages[label] = round(a.elapsed_time(b), 4)
+        return r
+    Wf = W.float()
+    p = timed('col_params', lambda: gg._col_params(Wf, bits))
+    Hn = timed('hessian', lambda: gg._accumulate_raw(xs))
+    Hf = timed('finalize', lambda: gg._finalize_H(*Hn))
+    Ls = timed('damp_invert', lambda: gg._damp_and_invert(Wf, Hf, DAMP))
+    Qc = timed('quantize', lambda: gg._quantize(Wf, Ls[0], p, BLOCK_SIZE, torch.bfloat16))
+    timed('pack', lambda: G.pack_matrix(Qc[0], p))
+    return {'stage_ms': stages, 'status': int(Ls[1].item())}
+
+
+def sized_check(torch, gg, W, xs, bits, K, N, with_oracle=True):
+    """Parity of one sized linear (see run_sized)."""
+    out = {}
+    n = sum(x.shape[0] for x in xs)
+    H, _ = gg._accumulate_raw(xs)
+    H = gg._finalize_H(H, n)
+    Hd = H.double()
+    Q, params, codes = gg.gptq(W, xs, block_size=BLOCK_SIZE, damping=DAMP, bits=bits, return_codes=True)
+    Wd, Qd = W.double(), Q.double()
+    D = Wd - Qd
+    err_gptq = float((D * (Hd @ D)).sum())
+    # round to nearest with the same grid
+    sc, z, maxq = params['scale'].double(), params['zero'].double(), params['maxq']
+    Qr = sc * (torch.clamp(torch.round(Wd / sc) + z, 0, maxq) - z)
+    Dr = Wd - Qr
+    out['recon_err_gptq_over_rtn'] = err_gptq / float((Dr * (Hd @ Dr)).sum())
+    # residual of the factor: L L^T (H + damp) = I
+    Wf = W.float()
+    L, status = gg._damp_and_invert(Wf, H.clone(), DAMP)
+    out['status'] = int(status.item())
+    Ld = L.double()
+    Hdamp = Hd + torch.eye(K, device=H.device, dtype=torch.float64) * (float(torch.diagonal(H).mean()) * DAMP)
+    R1 = Ld.T @ Hdamp
+    resid = Ld @ R1 - torch.eye(K, device=H.device, dtype=torch.float64)
+    out['factor_residual_max'] = float(resid.abs().max())
+    del R1, resid, Ld, Hdamp
+    if K <= ORACLE_MAX_K and with_oracle:
+        from oracle import ref_gptq as R
+        cols = min(N, ORACLE_COLS)
+        Wn = W[:, :cols].float().cpu().numpy()
+        xs_np = [x.float().cpu().numpy() for x in xs]
+        Q_ref, p_ref, it = R.gptq(Wn, xs_np, block_size=BLOCK_SIZE, damping=DAMP, bits=bits, return_internals=True)
+        # the GPU result for the same channels (channels are independent given the factor; scale / zero are per channel)
+        same = float((codes[:, :cols].cpu().numpy() == it['codes']).mean())
+        H64 = R.accumulate_H_direct(xs_np, use_fp64=True)
+        _, _, it_f = R.gptq(Wn, xs_np, block_size=BLOCK_SIZE, damping=DAMP, bits=bits, H=H64.astype(np.float32), return_internals=True)
+        floor_same = float((it_f['codes'] == it['codes']).mean())
+        e_ref = R.reconstruction_error(Wn, Q_ref, xs_np)
+        e_got = R.reconstruction_error(Wn, Q[:, :cols].float().cpu().numpy(), xs_np)
+        out.update({'oracle_channels': cols, 'same_codes': same, 'floor_same_codes_oracle_fp64H_vs_fp32H': floor_same,
+                    'bar_mismatch': parity_bar(1.0 - floor_same), 'recon_rel': abs(e_got - e_ref) / e_ref,
+                    'ok': bool(1.0 - same <= parity_bar(1.0 - floor_same) and abs(e_got - e_ref) / e_ref <= PARITY_RECON_REL)})
+    return out
 
 
 def bench_w4(torch, G, dev, peaks, cases=None, no_settled=False):
@@ -607,6 +932,60 @@ def bench_w4(torch, G, dev, peaks, cases=None, no_settled=False):
     return rows
 
 
+def bench_w4_sharded(torch, dist, dev, rank, world, peaks):
+    """Config-3's largest weight sharded over output channels: every rank multiplies the replicated
+    activations by its own (K/2, N/G) slab; with `gather` the (M, N/G) outputs are all-gathered."""
+    from jax_gptq_b200 import _lib
+    from jax_gptq_b200 import dist as D
+    K, N = 8192, 28672
+    c0, c1 = D.shard_range(N, rank, world, 128)
+    Nl = c1 - c0
+    gen = torch.Generator(device=dev).manual_seed(3003 + rank)
+    nbuf = max(2, -(-(300 << 20) // (K * Nl // 2)))
+    packed = [torch.randint(0, 256, (K // 2, Nl), generator=gen, device=dev, dtype=torch.uint8) for _ in range(nbuf)]
+    scale = (0.001 + 0.019 * torch.rand(Nl, generator=gen, device=dev)).half()
+    zero = torch.randint(0, 16, (Nl,), generator=gen, device=dev).half()
+    rows = []
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    for M in (1, 2048):
+        x = torch.randn((M, K), generator=torch.Generator(device=dev).manual_seed(5), device=dev).half()
+        need = _lib.lib.jgq_w4_matmul_workspace_bytes(M, Nl, K, 0)
+        ws = torch.zeros(max(need, 1), dtype=torch.uint8, device=dev)
+        out = torch.empty((M, Nl), dtype=torch.float16, device=dev)
+        full = torch.empty((world, M, Nl), dtype=torch.float16, device=dev)
+        st = torch.cuda.current_stream().cuda_stream
+        iters = 20 if M == 1 else 3
+
+        def launch(i):
+            _lib.check(_lib.lib.jgq_w4_matmul(x.data_ptr(), _lib.F16, packed[i % nbuf].data_ptr(), zero.data_ptr(),
+                                              scale.data_ptr(), _lib.F16, out.data_ptr(), M, Nl, K,
+                                              _lib.W4_WEIGHTS_SETTLED, ws.data_ptr(), need, st))
+        res = {}
+        for gather in (False, True):
+            for i in range(3):
+                launch(i)
+                if gather:
+                    dist.all_gather_into_tensor(full, out)
+            torch.cuda.synchronize()
+            dist.barrier()
+            e0.record()
+            for i in range(iters):
+                launch(i)
+                if gather:
+                    dist.all_gather_into_tensor(full, out)
+            e1.record()
+            torch.cuda.synchronize()
+            t = torch.tensor([e0.elapsed_time(e1) / iters], device=dev, dtype=torch.float64)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            res['us_with_gather' if gather else 'us_local'] = float(t.item()) * 1e3
+        bytes_alg = K * N // 2 + 4 * N + 2 * M * K + 2 * M * N
+        rows.append({'K': K, 'N': N, 'M': M, 'n_gpus': world, 'columns_per_rank': Nl, **res,
+                     'aggregate_GBps_local': bytes_alg / (res['us_local'] * 1e-6) / 1e9,
+                     'aggregate_TFLOPs_local': 2.0 * M * K * N / (res['us_local'] * 1e-6) / 1e12,
+                     'timing': 'host loop of launches (max over ranks); the gather is one NCCL all-gather per product'})
+    return rows
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument('--gpus', type=int, default=1)
@@ -622,6 +1001,8 @@ def main():
     ap.add_argument('--matmul-shapes', default='', help='comma list of KxNxM cases for --only-matmul')
     ap.add_argument('--no-settled', action='store_true',
                     help='matmul sweep without JGQ_W4_WEIGHTS_SETTLED (no weight fetch ahead of the previous kernel\'s end)')
+    ap.add_argument('--workload', default='gpt2-small', choices=['gpt2-small'] + sorted(SIZED),
+                    help='gpt2-small (the headline configuration) or one of the sized configurations')
     ap.add_argument('--skip-cpu', action='store_true')
     ap.add_argument('--skip-parity', action='store_true', help='do not run the oracle comparison of block 0')
     args = ap.parse_args()
@@ -639,6 +1020,8 @@ def main():
                                                 no_settled=args.no_settled)}), flush=True)
     elif args.impl == 'reference':
         run_reference(args)
+    elif args.workload != 'gpt2-small':
+        run_sized(args)
     else:
         run_ours(args)
 

@@ -9,8 +9,10 @@
  * Conventions shared by every entry point
  *   - all pointers are DEVICE pointers unless the name says "host";
  *   - `stream` is a cudaStream_t passed as void*; the call only enqueues work on
- *     it, never synchronises and never allocates.  Scratch memory is supplied by
- *     the caller (`ws`, `ws_bytes`; size from the matching *_workspace_bytes);
+ *     it, never synchronises and never allocates.  The device that owns the stream
+ *     must be the current device of the calling thread; calls may come from several
+ *     host threads (one per device).  Scratch memory is supplied by the caller
+ *     (`ws`, `ws_bytes`; size from the matching *_workspace_bytes);
  *   - return value 0 = enqueued, negative = host-side validation error, nothing
  *     was launched; jgq_last_error() returns the thread-local message;
  *   - device-side conditions (non-positive pivot / NaN in the Cholesky) are
@@ -72,6 +74,22 @@ int jgq_unpack_matrix(const uint8_t* packed, const float* zero, const float* sca
                       void* out, int out_dtype, int64_t outer, int64_t packed_len,
                       int64_t inner, void* stream);
 
+/* ---- 3-bit storage (no counterpart in the reference: its _pack/_unpack hard-code 4 bits,
+ * gptq.py:241,253, so a 3-bit result still takes a nibble per weight).  Eight codes along the packed
+ * axis -> three bytes, code i of a group in bits [3i, 3i+3) of the little-endian 24-bit word; axis_len
+ * must be a multiple of 8, the packed axis has axis_len * 3 / 8 bytes.  jgq_repack_int3_to_int4
+ * rewrites such a buffer in the two-codes-per-byte layout of gptq.py:246-247 that the matmul reads;
+ * jgq_unpack_matrix3 is unpack_matrix (gptq.py:230-235) for this format. */
+int jgq_pack_int3(const void* codes, int codes_dtype, uint8_t* packed,
+                  int64_t outer, int64_t axis_len, int64_t inner, void* stream);
+int jgq_unpack_int3(const uint8_t* packed, uint8_t* codes,
+                    int64_t outer, int64_t packed_len, int64_t inner, void* stream);
+int jgq_repack_int3_to_int4(const uint8_t* packed3, uint8_t* packed4,
+                            int64_t outer, int64_t packed_len, int64_t inner, void* stream);
+int jgq_unpack_matrix3(const uint8_t* packed, const float* zero, const float* scale,
+                       void* out, int out_dtype, int64_t outer, int64_t packed_len,
+                       int64_t inner, void* stream);
+
 /* ---- per-output-channel scale / zero (gptq.py:105-118) --------------------
  * W is (K, N) fp32; scale, zero are fp32[N]; maxq = 2^bits - 1. */
 int jgq_col_params(const float* W, int64_t K, int64_t N, int maxq,
@@ -89,6 +107,16 @@ int jgq_hessian_accum(const void* X, int x_dtype, int64_t n, int64_t K, float* H
                       void* ws, size_t ws_bytes, int32_t* dev_status, void* stream);
 int jgq_hessian_finalize(float* H, int64_t K, double n_total, void* stream);
 
+/* Token-sharded accumulation over several GPUs (no counterpart in the reference, which pins one GPU,
+ * quantize_interpreter.py:116-117): every rank accumulates its own tokens, the sums are added with one
+ * all-reduce, then every rank finalizes with the global sample count.  Only the tiles on or below the
+ * diagonal carry data before jgq_hessian_finalize, so only they need to travel: jgq_hessian_pack_lower
+ * copies them (row i: columns [0, 128 * (i / 128 + 1))) into a contiguous buffer of
+ * jgq_hessian_lower_elems(K) floats, jgq_hessian_unpack_lower writes a reduced buffer back.  K % 4 == 0. */
+size_t jgq_hessian_lower_elems(int64_t K);
+int jgq_hessian_pack_lower(const float* H, int64_t K, float* packed, void* stream);
+int jgq_hessian_unpack_lower(const float* packed, int64_t K, float* H, void* stream);
+
 /* ---- damping + Cholesky factor of the inverse (gptq.py:44-48, 155-168) ----
  * In: W (K x N fp32, rows of dead features are zeroed in place), H (K x K fp32,
  * destroyed).  Out: L (K x K fp32, lower, L L^T = (H + damp)^-1, upper = 0),
@@ -96,6 +124,15 @@ int jgq_hessian_finalize(float* H, int64_t K, double n_total, void* stream);
 size_t jgq_damp_invert_workspace_bytes(int64_t K);
 int jgq_damp_invert(float* W, int64_t N, float* H, int64_t K, float damping, float* L,
                     void* ws, size_t ws_bytes, int32_t* dev_status, void* stream);
+
+/* ---- use_fp64=True (gptq.py:87, 186-197): the Hessian and the factor of its inverse in double precision.
+ * Same contracts as the fp32 entry points above with H (K x K) in fp64; L comes out in fp32, which is
+ * what the quantize loop takes (gptq.py:197).  Plain FP64 kernels: an accuracy option, not a fast path. */
+int jgq_hessian_accum_f64(const void* X, int x_dtype, int64_t n, int64_t K, double* H, void* stream);
+int jgq_hessian_finalize_f64(double* H, int64_t K, double n_total, void* stream);
+size_t jgq_damp_invert_f64_workspace_bytes(int64_t K);
+int jgq_damp_invert_f64(float* W, int64_t N, double* H, int64_t K, double damping, float* L,
+                        void* ws, size_t ws_bytes, int32_t* dev_status, void* stream);
 
 /* ---- blocked quantize + error propagation (gptq.py:120-153, 199-208) ------
  * In: W (K x N fp32, destroyed), L from jgq_damp_invert, scale/zero fp32[N].
@@ -137,9 +174,13 @@ int jgq_w4_matmul(const void* x, int x_dtype, const uint8_t* packed,
  * Same result as jgq_w4_matmul(..., transpose_b = 0, ...).  The split-K scratch
  * is a fixed array of jgq_w4_matmul_noalloc_max_bytes() bytes inside the library,
  * resident on every GPU that loads it.  The call allocates nothing and frees
- * nothing.  Shapes whose scratch need (jgq_w4_matmul_workspace_bytes) exceeds the
- * array are refused with JGQ_ERR_LIMIT.  The first call on each device looks up
- * the array's device address; make that first call outside any stream capture.
+ * nothing.  Shapes whose scratch need for the call's own activation dtype exceeds
+ * the array are refused with JGQ_ERR_LIMIT (jgq_w4_matmul_workspace_bytes is an upper
+ * bound over all dtypes); every argument is checked before anything is enqueued.
+ * The device that owns `stream` must be current (as for every entry point here).
+ * The first call on each device looks up the array's device address, and the first
+ * use of each kernel variant (dtype, size class) sets its launch attributes: make
+ * those first calls outside any stream capture.
  * Every call on a device shares the array: calls that can overlap on the GPU
  * (different streams) race - keep them on one stream. */
 size_t jgq_w4_matmul_noalloc_max_bytes(void);

@@ -26,12 +26,23 @@ SIGNATURES = {
     'jgq_unpack_int4': (_int, [_vp, _vp, _i64, _i64, _i64, _vp]),
     'jgq_pack_matrix': (_int, [_vp, _int, _vp, _vp, _vp, _i64, _i64, _i64, _vp]),
     'jgq_unpack_matrix': (_int, [_vp, _vp, _vp, _vp, _int, _i64, _i64, _i64, _vp]),
+    'jgq_pack_int3': (_int, [_vp, _int, _vp, _i64, _i64, _i64, _vp]),
+    'jgq_unpack_int3': (_int, [_vp, _vp, _i64, _i64, _i64, _vp]),
+    'jgq_repack_int3_to_int4': (_int, [_vp, _vp, _i64, _i64, _i64, _vp]),
+    'jgq_unpack_matrix3': (_int, [_vp, _vp, _vp, _vp, _int, _i64, _i64, _i64, _vp]),
     'jgq_col_params': (_int, [_vp, _i64, _i64, _int, _vp, _vp, _vp]),
     'jgq_hessian_workspace_bytes': (_sz, [_i64, _i64, _int]),
     'jgq_hessian_accum': (_int, [_vp, _int, _i64, _i64, _vp, _vp, _sz, _vp, _vp]),
     'jgq_hessian_finalize': (_int, [_vp, _i64, C.c_double, _vp]),
+    'jgq_hessian_lower_elems': (_sz, [_i64]),
+    'jgq_hessian_pack_lower': (_int, [_vp, _i64, _vp, _vp]),
+    'jgq_hessian_unpack_lower': (_int, [_vp, _i64, _vp, _vp]),
     'jgq_damp_invert_workspace_bytes': (_sz, [_i64]),
     'jgq_damp_invert': (_int, [_vp, _i64, _vp, _i64, C.c_float, _vp, _vp, _sz, _vp, _vp]),
+    'jgq_hessian_accum_f64': (_int, [_vp, _int, _i64, _i64, _vp, _vp]),
+    'jgq_hessian_finalize_f64': (_int, [_vp, _i64, C.c_double, _vp]),
+    'jgq_damp_invert_f64_workspace_bytes': (_sz, [_i64]),
+    'jgq_damp_invert_f64': (_int, [_vp, _i64, _vp, _i64, C.c_double, _vp, _vp, _sz, _vp, _vp]),
     'jgq_gptq_quantize_workspace_bytes': (_sz, [_i64, _i64, _int]),
     'jgq_gptq_quantize': (_int, [_vp, _vp, _vp, _vp, _i64, _i64, _int, _int, _vp, _int, _vp, _vp, _sz, _vp]),
     'jgq_w4_matmul_workspace_bytes': (_sz, [_i64, _i64, _i64, _int]),

@@ -58,6 +58,26 @@ __global__ void finalize_kernel(float* __restrict__ H, int K, float n) {
   }
 }
 
+// ---- lower block triangle <-> contiguous buffer (what travels in a multi-GPU all-reduce) ----
+// Row i of the K x K sums is significant in columns [0, 128 * (i / 128 + 1)) (tiles on or below the
+// diagonal, 128-row panels); the packed buffer holds those row pieces back to back.
+__host__ __device__ inline int64_t tri_row_offset(int64_t i) {
+  const int64_t I = i / 128;
+  return 128 * 128 * (I * (I + 1) / 2) + (i % 128) * 128 * (I + 1);
+}
+
+template <bool kPack>
+__global__ void tri_copy_kernel(float* __restrict__ H, float* __restrict__ packed, int K) {
+  const int i = blockIdx.x;
+  const int len = min(K, 128 * (i / 128 + 1));
+  float* row = H + (int64_t)i * K;
+  float* dst = packed + tri_row_offset(i);
+  for (int c = 4 * threadIdx.x; c < len; c += 4 * blockDim.x) {      // K % 4 == 0 (checked by the caller)
+    if (kPack) *reinterpret_cast<float4*>(dst + c) = *reinterpret_cast<const float4*>(row + c);
+    else       *reinterpret_cast<float4*>(row + c) = *reinterpret_cast<const float4*>(dst + c);
+  }
+}
+
 static int hessian_splits(int64_t n, int64_t K) {
   const int64_t T = cdiv(K, GBM);
   const int64_t tiles = T * (T + 1) / 2;
@@ -143,6 +163,25 @@ extern "C" int jgq_hessian_accum(const void* X, int x_dtype, int64_t n, int64_t 
   dim3 blk(32, 8), grd((unsigned)cdiv(K, 32), (unsigned)cdiv(K, 8));
   reduce_splits_kernel<<<grd, blk, 0, s>>>(H, part, (int)K, splits);
   return check_launch("hessian_accum");
+}
+
+extern "C" size_t jgq_hessian_lower_elems(int64_t K) {
+  if (K <= 0) return 0;
+  return (size_t)tri_row_offset(K - 1) + (size_t)std::min<int64_t>(K, 128 * ((K - 1) / 128 + 1));
+}
+
+extern "C" int jgq_hessian_pack_lower(const float* H, int64_t K, float* packed, void* stream) {
+  JGQ_REQUIRE(K > 0 && K <= 46340 && K % 4 == 0, JGQ_ERR_ARG, "hessian_pack_lower: K=%lld must be a positive multiple of 4", (long long)K);
+  JGQ_REQUIRE(H && packed && aligned(H, 16) && aligned(packed, 16), JGQ_ERR_ARG, "hessian_pack_lower: null or unaligned pointer");
+  tri_copy_kernel<true><<<(unsigned)K, 256, 0, (cudaStream_t)stream>>>(const_cast<float*>(H), packed, (int)K);
+  return check_launch("hessian_pack_lower");
+}
+
+extern "C" int jgq_hessian_unpack_lower(const float* packed, int64_t K, float* H, void* stream) {
+  JGQ_REQUIRE(K > 0 && K <= 46340 && K % 4 == 0, JGQ_ERR_ARG, "hessian_unpack_lower: K=%lld must be a positive multiple of 4", (long long)K);
+  JGQ_REQUIRE(H && packed && aligned(H, 16) && aligned(packed, 16), JGQ_ERR_ARG, "hessian_unpack_lower: null or unaligned pointer");
+  tri_copy_kernel<false><<<(unsigned)K, 256, 0, (cudaStream_t)stream>>>(H, const_cast<float*>(packed), (int)K);
+  return check_launch("hessian_unpack_lower");
 }
 
 extern "C" int jgq_hessian_finalize(float* H, int64_t K, double n_total, void* stream) {

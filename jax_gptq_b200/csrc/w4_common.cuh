@@ -9,6 +9,10 @@ namespace jgq {
 constexpr int WCOLS = 128;          // channels per CTA
 constexpr int WWARPS = 4;
 constexpr int PSTRIDE = WCOLS + 4;  // floats per partial row: 128 sums + sum_k x (+pad)
+// Every forward kernel keeps its int32 tickets (and scheduling words) in the first W4_TICKET_REGION bytes of
+// the workspace and its fp32 slices behind them: the kernels share one workspace, and what one of them
+// writes as slices must never land on words another one expects to find zero.
+constexpr int W4_TICKET_REGION = 16384;
 
 template <typename XT> struct MmaType;
 template <> struct MmaType<__half> {

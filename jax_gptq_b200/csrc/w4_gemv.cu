@@ -46,22 +46,23 @@ namespace jgq {
 
 constexpr int GV_NST = 3;                      // boxes in flight per CTA
 constexpr int GV_THREADS = WWARPS * 32;
-constexpr int GV_TICKET_BYTES = 16384;         // one ticket per (channel group, warp): 1024 groups
+constexpr int GV_TICKET_BYTES = W4_TICKET_REGION;   // one ticket per (channel group, warp): 1024 groups
 constexpr int GV_XS_TOKENS = 8;                // sum_k x slots per slice
 
 struct GemvParams {
   const __half* x; const void* zero; const void* scale; __half* out;
-  float* partials; int* tickets; int* sched;     // sched[0]: next unit to hand out, sched[1]: CTAs that have finished
+  float* partials; int* tickets;
   int M, N, K;
   int ncg, spc;                // channel groups, stages per group
+  int64_t S;                   // total stages
   int G;                       // CTAs
-  // A group's contraction range is cut into nbig chunks of cb stages followed by nsmall chunks of cs stages.
-  // Units are handed out big ones first (all groups), then the small ones: the tail of the kernel is made of
-  // short units, so that the CTAs finish together whatever their individual speed was.
-  int cb, nbig, cs, nsmall;
-  int nunits;                  // ncg * (nbig + nsmall)
+  int maxc;                    // slice slots per group
   int early;                   // 1: weights may be fetched before the stream's previous kernel has finished
 };
+
+__device__ __forceinline__ int gemv_cta_of(int64_t idx, int64_t S, int G) {
+  return (int)(((idx + 1) * G + S - 1) / S) - 1;     // the c with c*S/G <= idx < (c+1)*S/G
+}
 
 __device__ __forceinline__ uint32_t lds32(uint32_t addr) {
   uint32_t v;
@@ -83,9 +84,6 @@ __device__ __forceinline__ void mma_f16(float (&d)[4], uint32_t a0, uint32_t a1,
                : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
-constexpr int GV_META = 8;          // descriptors of issued stages kept (a power of two >= 2 * GV_NST)
-constexpr int GV_LAST = 1, GV_TERM = 2;
-
 // NT: token rows staged per warp (1, 2, 4 or 8 >= M).  ROWS: byte rows per stage (64 or 128).
 template <int NT, int ROWS, typename ZST>
 __global__ void __launch_bounds__(GV_THREADS, NT <= 2 ? 4 : 3)
@@ -100,80 +98,32 @@ w4_gemv_kernel(const __grid_constant__ CUtensorMap wmap, const GemvParams p) {
   uint8_t* ring = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* xs_all = ring + GV_NST * STAGE_BYTES;   // [warp][token row][PAIRS] operand pairs, then one row of zeros
   __shared__ __align__(8) uint64_t full_bar[GV_NST];
+  __shared__ int issued[GV_NST];
   __shared__ int done[GV_NST];
   __shared__ int s_abort;
-  // the stage that was issued as number j of this CTA: its channel group, its position in the group, flags
-  // and the chunk it belongs to; `tag` is written last and tells that the other fields are those of stage j
-  __shared__ int m_tag[GV_META], m_group[GV_META], m_st[GV_META], m_flags[GV_META], m_chunk[GV_META];
-  // issue cursor (touched by one thread at a time: the one that refills a slot)
-  __shared__ int c_unit, c_pos, c_len, c_group, c_st0, c_chunk, c_seq, c_finished;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, t = lane & 3;
+  const int64_t idx_begin = ((int64_t)blockIdx.x * p.S) / p.G;
+  const int64_t idx_end = ((int64_t)(blockIdx.x + 1) * p.S) / p.G;
+  const int nstage = (int)(idx_end - idx_begin);
+  const int g_begin = (int)(idx_begin / p.spc);
+  const int st_begin = (int)(idx_begin - (int64_t)g_begin * p.spc);
   volatile int* abort_flag = &s_abort;
-  const int nchunks = p.nbig + p.nsmall;
 
-  auto decode_unit = [&](int u) {       // unit -> (group, first stage, stages, chunk index)
-    int grp, ch, st0, len;
-    const int ubig = p.ncg * p.nbig;
-    if (u < ubig) { grp = u / p.nbig; ch = u % p.nbig; st0 = ch * p.cb; len = p.cb; }
-    else { const int v = u - ubig; grp = v / p.nsmall; const int c2 = v % p.nsmall; ch = p.nbig + c2; st0 = p.nbig * p.cb + c2 * p.cs; len = p.cs; }
-    if (st0 + len > p.spc) len = p.spc - st0;
-    c_unit = u; c_pos = 0; c_len = len; c_group = grp; c_st0 = st0; c_chunk = ch;
-  };
-  // Issues stage number c_seq of this CTA into its ring slot: the next stage of the current unit, of a newly
-  // drawn unit when `may_draw`, or the end marker.  Returns false when nothing could be issued (a unit would
-  // have to be drawn and may not be yet).
-  auto issue_next = [&](bool may_draw) -> bool {
-    if (*(volatile int*)&c_finished) return true;
-    if (c_unit >= 0 && c_pos == c_len) {
-      if (!may_draw) return false;
-      const int u = atomicAdd(&p.sched[0], 1) + p.G;
-      if (u < p.nunits) decode_unit(u); else c_unit = -1;
-    }
-    const int j = c_seq, slot = j % GV_NST, ms = j & (GV_META - 1);
-    if (c_unit < 0) {                   // no work left: an end marker instead of a box
-      m_flags[ms] = GV_TERM;
-      __threadfence_block();
-      *(volatile int*)&m_tag[ms] = j;
-      c_finished = 1;
-      mbar_arrive(&full_bar[slot]);
-      __threadfence_block();
-      *(volatile int*)&c_seq = j + 1;
-      return true;
-    }
-    m_group[ms] = c_group; m_st[ms] = c_st0 + c_pos; m_chunk[ms] = c_chunk;
-    m_flags[ms] = (c_pos + 1 == c_len) ? GV_LAST : 0;
-    __threadfence_block();
-    *(volatile int*)&m_tag[ms] = j;
+  auto issue_stage = [&](int j) {
+    const int lin = st_begin + j;
+    const int gg = g_begin + lin / p.spc, ss = lin % p.spc;
+    const int slot = j % GV_NST;
+    issued[slot] = j;
     mbar_expect_tx(&full_bar[slot], STAGE_BYTES);
-    tma_load_2d(ring + slot * STAGE_BYTES, &wmap, c_group * WCOLS, (c_st0 + c_pos) * ROWS, &full_bar[slot]);
-    ++c_pos;
-    __threadfence_block();
-    *(volatile int*)&c_seq = j + 1;
-    return true;
-  };
-  // Refill after stage j was consumed: stage j + GV_NST goes into the same slot.  Slots are released in
-  // order, but the thread that refills one may still be drawing a unit when the next slot is released:
-  // the cursor is handed on in sequence order.
-  auto refill_after = [&](int j) {
-    const int q = j + GV_NST;
-    const long long t0 = clock64();
-    while (*(volatile int*)&c_seq != q) {
-      if (*(volatile int*)&c_finished) return;
-      if (clock64() - t0 > kWaitBudgetCycles) { *abort_flag = 1; return; }
-    }
-    __threadfence_block();
-    issue_next(true);
+    tma_load_2d(ring + slot * STAGE_BYTES, &wmap, gg * WCOLS, ss * ROWS, &full_bar[slot]);
   };
 
   GTRACE(0);
   if (threadIdx.x == 0) {
-    for (int i = 0; i < GV_NST; ++i) { mbar_init(&full_bar[i], 1); done[i] = 0; }
-    for (int i = 0; i < GV_META; ++i) m_tag[i] = -1;
+    for (int i = 0; i < GV_NST; ++i) { mbar_init(&full_bar[i], 1); done[i] = 0; issued[i] = -1; }
     s_abort = 0;
-    c_seq = 0; c_finished = 0; c_pos = 0; c_len = 0; c_unit = -1;
-    if ((int)blockIdx.x < p.nunits) decode_unit((int)blockIdx.x);     // the first unit is this CTA's own number
     fence_barrier_init();
     prefetch_tensormap(&wmap);
   }
@@ -182,16 +132,15 @@ w4_gemv_kernel(const __grid_constant__ CUtensorMap wmap, const GemvParams p) {
     reinterpret_cast<uint32_t*>(xs_all + WWARPS * XWARP)[i] = 0u;
   __syncthreads();
   if (p.early && threadIdx.x == 0)
-    while (c_seq < GV_NST && issue_next(false)) {}
+    for (int j = 0; j < GV_NST && j < nstage; ++j) issue_stage(j);
   // Wait until everything enqueued before this kernel has completed: activations, workspace and outputs
   // are only touched below this line.  Only then is the next kernel on the stream allowed to begin its
   // own set-up: whatever it reads early was therefore complete before THIS kernel's predecessor ended.
   asm volatile("griddepcontrol.wait;" ::: "memory");
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   GTRACE(1);
-  if (threadIdx.x == 0)
-    while (c_seq < GV_NST && !c_finished) issue_next(true);
-  __syncthreads();
+  if (!p.early && threadIdx.x == 0)
+    for (int j = 0; j < GV_NST && j < nstage; ++j) issue_stage(j);
 
   float acc[2][4], accx[4];
   auto clear_acc = [&]() {
@@ -212,41 +161,27 @@ w4_gemv_kernel(const __grid_constant__ CUtensorMap wmap, const GemvParams p) {
   const __half2 sixteenth = __float2half2_rn(0.0625f);
   const uint32_t ones_lo = 0x3C003C00u, ones_hi = 0x4C004C00u;      // (1, 1) and (16, 16)
 
-  uint2 xv[NT][ROWS / 64];
-  auto load_x = [&](int st) {       // activations of a stage: two 8-byte loads per token row and lane
-    const int k0 = st * (2 * ROWS);
-#pragma unroll
-    for (int r = 0; r < NT; ++r)
-#pragma unroll
-      for (int h = 0; h < ROWS / 64; ++h) {
-        const int k = k0 + 4 * (lane + 32 * h);
-        xv[r][h] = make_uint2(0u, 0u);
-        if (r < p.M && k < p.K)        // K % 8 == 0: the four values are inside the row together
-          xv[r][h] = __ldg(reinterpret_cast<const uint2*>(p.x + (int64_t)r * p.K + k));
-      }
-  };
-
+  int gid = g_begin, st = st_begin;
   bool alive = true;
-  bool traced = false;
-  for (int j = 0;; ++j) {
-    const int slot = j % GV_NST, ms = j & (GV_META - 1);
-    // The stage's descriptor is normally there long before its box (it was written when the box was asked
-    // for): then the activations are fetched before the wait.  A warp that runs ahead of the refill reads it
-    // after the wait instead.
-    int st = 0;
-    bool pre = (*(volatile int*)&m_tag[ms] == j);
-    if (pre) {
-      __threadfence_block();
-      pre = !(*(volatile int*)&m_flags[ms] & GV_TERM);
-      if (pre) { st = *(volatile int*)&m_st[ms]; load_x(st); }
+  for (int s = 0; s < nstage; ++s) {
+    const int cg = gid;
+    const int slot = s % GV_NST;
+    // ---- activations of this stage: two 8-byte loads per token row and lane, issued before the wait ----
+    uint2 xv[NT][ROWS / 64];
+    {
+      const int k0 = st * (2 * ROWS);
+#pragma unroll
+      for (int r = 0; r < NT; ++r)
+#pragma unroll
+        for (int h = 0; h < ROWS / 64; ++h) {
+          const int k = k0 + 4 * (lane + 32 * h);
+          xv[r][h] = make_uint2(0u, 0u);
+          if (r < p.M && k < p.K)        // K % 8 == 0: the four values are inside the row together
+            xv[r][h] = __ldg(reinterpret_cast<const uint2*>(p.x + (int64_t)r * p.K + k));
+        }
     }
-    alive = __all_sync(0xffffffffu, mbar_wait(&full_bar[slot], (j / GV_NST) & 1, abort_flag));
-    if (!alive) break;
-    const int flags = *(volatile int*)&m_flags[ms];
-    if (flags & GV_TERM) break;
-    const int cg = *(volatile int*)&m_group[ms], chunk_idx = *(volatile int*)&m_chunk[ms];
-    if (!pre) { st = *(volatile int*)&m_st[ms]; load_x(st); }
-    if (!traced) { GTRACE(2); traced = true; }
+    if (alive) alive = __all_sync(0xffffffffu, mbar_wait(&full_bar[slot], (s / GV_NST) & 1, abort_flag));
+    if (s == 0) GTRACE(2);
     __syncwarp();                          // the previous stage's operand pairs have been read by every lane
 #pragma unroll
     for (int r = 0; r < NT; ++r)
@@ -258,7 +193,7 @@ w4_gemv_kernel(const __grid_constant__ CUtensorMap wmap, const GemvParams p) {
         sts64(xs_warp + r * XROW + (lane + 32 * h) * 8, ev, *reinterpret_cast<uint32_t*>(&o2));
       }
     __syncwarp();
-    {
+    if (alive) {
       const uint32_t tile = ring_u32 + slot * STAGE_BYTES;
 #pragma unroll
       for (int sl = 0; sl < STEPS; ++sl) {
@@ -277,36 +212,40 @@ w4_gemv_kernel(const __grid_constant__ CUtensorMap wmap, const GemvParams p) {
         asm volatile("atom.acq_rel.cta.shared.add.u32 %0, [%1], 1;" : "=r"(old) : "r"(smem_u32(&done[slot])) : "memory");
         if (old == WWARPS - 1) {               // every warp has read the slot: refill it
           done[slot] = 0;
-          asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-          refill_after(j);
+          if (s + GV_NST < nstage) {
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            issue_stage(s + GV_NST);
+          }
         }
       }
     }
-    if (!(flags & GV_LAST)) continue;
+    const int st_now = st;
+    st = (st + 1 == p.spc) ? 0 : st + 1;
+    if (st == 0) ++gid;
+    const bool last_of_group = (st_now == p.spc - 1) || (s == nstage - 1);
+    if (!last_of_group) continue;
+    if (s == nstage - 1) GTRACE(3);
 
-    // ---- flush this warp's 32 channels of the unit (group cg, chunk chunk_idx) ----
+    // ---- flush this warp's 32 channels of group cg ----
     // lane (g, t): tokens 2t and 2t+1; channels n0 .. n0+3 = (tile 0 row g, tile 0 row g+8, tile 1 row g, tile 1 row g+8)
-    GTRACE(3);
     const float kUp = 16777216.f;             // 2^24: the codes entered as code * 2^-24
     const int n0 = cg * WCOLS + 32 * warp + 4 * g;
+    const int first_c = gemv_cta_of((int64_t)cg * p.spc, p.S, p.G);
+    const int last_c = gemv_cta_of((int64_t)(cg + 1) * p.spc - 1, p.S, p.G);
+    const int ncontrib = last_c - first_c + 1;
+    const float poison = (alive && !*abort_flag) ? 0.f : __int_as_float(0x7fc00000);
     float4 v[2];
     float xsum[2];
 #pragma unroll
     for (int e = 0; e < 2; ++e) {
-      v[e] = make_float4(acc[0][e], acc[0][2 + e], acc[1][e], acc[1][2 + e]);
+      v[e] = make_float4(acc[0][e] + poison, acc[0][2 + e] + poison, acc[1][e] + poison, acc[1][2 + e] + poison);
       xsum[e] = accx[e];
     }
-    // scale and zero are fetched before the ticket so that their latency overlaps the exchange
-    float sc[4] = {0.f, 0.f, 0.f, 0.f}, z[4] = {0.f, 0.f, 0.f, 0.f};
-    if (n0 < p.N) {                            // N % 16 == 0: the four channels are inside together
-#pragma unroll
-      for (int i = 0; i < 4; ++i) { sc[i] = zs_to_f32<ZST>(p.scale, n0 + i); z[i] = zs_to_f32<ZST>(p.zero, n0 + i); }
-    }
     bool write_out = true;
-    if (nchunks > 1) {
-      constexpr int SL = NT * 32 + GV_XS_TOKENS;        // floats per (chunk, warp): NT token rows x 32 channels, then sum_k x
-      float* base = p.partials + ((int64_t)cg * nchunks * WWARPS + warp) * SL;
-      float* mine = base + (int64_t)chunk_idx * WWARPS * SL;
+    if (ncontrib > 1) {
+      constexpr int SL = NT * 32 + GV_XS_TOKENS;        // floats per (slot, warp): NT token rows x 32 channels, then sum_k x
+      float* base = p.partials + ((int64_t)cg * p.maxc * WWARPS + warp) * SL;
+      float* mine = base + (int64_t)(blockIdx.x - first_c) * WWARPS * SL;
 #pragma unroll
       for (int e = 0; e < 2; ++e) {
         const int tok = 2 * t + e;
@@ -320,7 +259,7 @@ w4_gemv_kernel(const __grid_constant__ CUtensorMap wmap, const GemvParams p) {
       int last = 0;
       if (lane == 0) {
         const int old = atomicAdd(&p.tickets[cg * WWARPS + warp], 1);
-        last = (old == nchunks - 1);
+        last = (old == ncontrib - 1);
         if (last) p.tickets[cg * WWARPS + warp] = 0;           // ready for the next launch
       }
       last = __shfl_sync(0xffffffffu, last, 0);
@@ -333,7 +272,7 @@ w4_gemv_kernel(const __grid_constant__ CUtensorMap wmap, const GemvParams p) {
           v[e] = make_float4(0.f, 0.f, 0.f, 0.f);
           xsum[e] = 0.f;
           if (tok < p.M && tok < NT) {
-            for (int zc = 0; zc < nchunks; ++zc) {             // chunks are added in contraction order: deterministic
+            for (int zc = 0; zc < ncontrib; ++zc) {            // slices are added in CTA order: deterministic
               const float* src = base + (int64_t)zc * WWARPS * SL;
               const float4 a = __ldcg(reinterpret_cast<const float4*>(src + tok * 32 + 4 * g));
               v[e].x += a.x; v[e].y += a.y; v[e].z += a.z; v[e].w += a.w;
@@ -343,7 +282,10 @@ w4_gemv_kernel(const __grid_constant__ CUtensorMap wmap, const GemvParams p) {
         }
       }
     }
-    if (write_out && n0 < p.N) {
+    if (write_out && n0 < p.N) {               // N % 16 == 0: the four channels are inside together
+      float sc[4], z[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) { sc[i] = zs_to_f32<ZST>(p.scale, n0 + i); z[i] = zs_to_f32<ZST>(p.zero, n0 + i); }
 #pragma unroll
       for (int e = 0; e < 2; ++e) {
         const int tok = 2 * t + e;
@@ -362,23 +304,16 @@ w4_gemv_kernel(const __grid_constant__ CUtensorMap wmap, const GemvParams p) {
   }
 
   GTRACE(4);
+  // After a timed-out wait some boxes may still be in flight: give them a bounded time to land before
+  // the CTA's shared memory is released.
   __syncthreads();
-  if (threadIdx.x == 0) {
-    if (*abort_flag) {
-      // A wait ran out.  Boxes may still be in flight: give them a bounded time to land before the CTA's
-      // shared memory is released.  The units this CTA held are lost: mark the outputs of its current
-      // channel group as invalid so that the failure cannot pass for a result.
-      for (int i = 0; i < GV_NST; ++i) {
-        const long long t0 = clock64();
-        while (!mbar_try_wait(&full_bar[i], 0) && !mbar_try_wait(&full_bar[i], 1) && clock64() - t0 < 20000000LL) {}
-      }
-      if (c_unit >= 0)
-        for (int i = 0; i < WCOLS && c_group * WCOLS + i < p.N; ++i)
-          for (int m = 0; m < p.M; ++m) p.out[(int64_t)m * p.N + c_group * WCOLS + i] = __float2half_rn(__int_as_float(0x7fc00000));
+  if (threadIdx.x == 0 && *abort_flag) {
+    for (int i = 0; i < GV_NST; ++i) {
+      const int j = issued[i];
+      if (j < 0) continue;
+      const long long t0 = clock64();
+      while (!mbar_try_wait(&full_bar[i], (j / GV_NST) & 1) && clock64() - t0 < 20000000LL) {}
     }
-    // the CTA that leaves last puts the two scheduling words back to zero for the next launch
-    const int old = atomicAdd(&p.sched[1], 1);
-    if (old == p.G - 1) { p.sched[0] = 0; p.sched[1] = 0; }
   }
 }
 
@@ -392,17 +327,12 @@ static int gemv_rows_override() {       // JGQ_GEMV_ROWS=64|128: byte rows per s
   return v;
 }
 
-static int gemv_env_int(const char* name) {
-  const char* e = getenv(name);
-  return e ? atoi(e) : 0;
-}
-
 GemvPlan plan_w4_gemv(int64_t M, int64_t N, int64_t K) {
   GemvPlan pl;
   memset(&pl, 0, sizeof(pl));
   if (M < 1 || M > 8 || N % 16 != 0 || K % 8 != 0) return pl;
   pl.ncg = (int)cdiv(N, WCOLS);
-  if (pl.ncg * WWARPS + 2 > GV_TICKET_BYTES / (int)sizeof(int)) return pl;
+  if (pl.ncg * WWARPS > GV_TICKET_BYTES / (int)sizeof(int)) return pl;
   pl.use = 1;
   pl.nt = M <= 1 ? 1 : M <= 2 ? 2 : M <= 4 ? 4 : 8;
   pl.rows = gemv_rows_override() ? gemv_rows_override() : 128;
@@ -413,22 +343,8 @@ GemvPlan plan_w4_gemv(int64_t M, int64_t N, int64_t K) {
   const int by_smem = (227 * 1024) / (pl.smem_bytes + 1024 + 128);
   const int per_sm = std::max(1, std::min(pl.nt <= 2 ? 4 : 3, by_smem));
   pl.G = (int)std::min<int64_t>(per_sm * (int64_t)sm_count(), std::max<int64_t>(1, pl.S / 2));   // one resident wave
-  // Units.  About three quarters of a group's stages go into big chunks of roughly half a CTA's share of the
-  // work, the rest into short chunks that are handed out last.
-  static const int env_cb = gemv_env_int("JGQ_GEMV_CB"), env_cs = gemv_env_int("JGQ_GEMV_CS"), env_big = gemv_env_int("JGQ_GEMV_BIGPCT");
-  const double share = (double)pl.S / pl.G;           // stages per CTA
-  int cb = env_cb > 0 ? env_cb : (int)std::max<double>(2.0, std::min<double>(pl.spc, share * 0.5 + 0.5));
-  int cs = env_cs > 0 ? env_cs : std::max(1, std::min(2, cb / 2));
-  const int bigpct = env_big > 0 ? env_big : 75;
-  if (cb > pl.spc) cb = pl.spc;
-  int nbig = (int)((int64_t)pl.spc * bigpct / 100) / cb;
-  if (nbig * cb >= pl.spc) { nbig = pl.spc / cb; }
-  int rest = pl.spc - nbig * cb;
-  int nsmall = (int)cdiv(rest, cs);
-  if (nbig == 0 && nsmall == 0) { nbig = 1; cb = pl.spc; }
-  pl.cb = cb; pl.nbig = nbig; pl.cs = cs; pl.nsmall = nsmall;
-  pl.nunits = pl.ncg * (nbig + nsmall);
-  pl.maxc = nbig + nsmall;
+  const int64_t per = pl.S / pl.G;                    // every CTA streams per or per + 1 stages
+  pl.maxc = (int)cdiv(pl.spc, per) + 1;
   pl.part_bytes = align_up((size_t)pl.ncg * pl.maxc * WWARPS * (pl.nt * 32 + GV_XS_TOKENS) * sizeof(float), 256);
   pl.ws_bytes = GV_TICKET_BYTES + pl.part_bytes;
   return pl;
@@ -471,11 +387,9 @@ int launch_w4_gemv(const GemvPlan& pl, const void* x, const uint8_t* packed, con
   memset(&p, 0, sizeof(p));
   p.x = (const __half*)x; p.zero = zero; p.scale = scale; p.out = (__half*)out;
   p.tickets = (int*)ws;
-  p.sched = (int*)ws + (GV_TICKET_BYTES / (int)sizeof(int) - 2);      // the last two words of the ticket region
   p.partials = (float*)((char*)ws + GV_TICKET_BYTES);
   p.M = (int)M; p.N = (int)N; p.K = (int)K;
-  p.ncg = pl.ncg; p.spc = pl.spc; p.G = pl.G;
-  p.cb = pl.cb; p.nbig = pl.nbig; p.cs = pl.cs; p.nsmall = pl.nsmall; p.nunits = pl.nunits;
+  p.ncg = pl.ncg; p.spc = pl.spc; p.S = pl.S; p.G = pl.G; p.maxc = pl.maxc;
   p.early = settled ? 1 : 0;
   const bool zf = zs_dtype == JGQ_F32;
 #define JGQ_GEMV(NT_)                                                                                   \

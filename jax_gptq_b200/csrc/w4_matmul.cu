@@ -8,8 +8,8 @@
 // they leave the contraction loop:
 //     out[m, n] = scale[n] * ( sum_k x[m,k] code[k,n]  -  zero[n] * sum_k x[m,k] ).
 //
-// This file holds the decode-sized forward kernel (M <= 16 per CTA pass; larger M
-// goes to the tcgen05 kernel in w4_umma.cu) and the transposed kernel.
+// This file holds the dispatcher and the direct-load decode kernel (the fallback for shapes the
+// TMA-streamed kernels do not take); the transposed product is in w4_tb.cu.
 //
 // Decode kernel: HBM-bound, one pass over K*N/2 bytes.  Codes go from global
 // memory straight to registers (16-byte loads, a register ring keeps several
@@ -220,64 +220,8 @@ w4_decode_kernel(const XT* __restrict__ x, const uint8_t* __restrict__ packed,
     }
 }
 
-// ---- transpose_b: out[m, kk] = sum_n x[m, n] * (code[kk, n] - zero[n]) * scale[n] ------
-// fp32 FFMA tile kernel (64 x 64 outputs, 32-channel contraction slices); the
-// dequantised values are formed exactly as the reference kernel does
-// ((code - zero) * scale in fp32, kernel.py:216-217).
-template <typename XT, typename ZST>
-__global__ void __launch_bounds__(256)
-w4_tb_kernel(const XT* __restrict__ x, const uint8_t* __restrict__ packed,
-             const void* __restrict__ zero, const void* __restrict__ scale,
-             XT* __restrict__ out, int64_t M, int64_t N, int64_t K) {
-  __shared__ float xs[32][64 + 1];   // [n][m]
-  __shared__ float ws[32][64 + 1];   // [n][kk]
-  const int64_t m0 = (int64_t)blockIdx.y * 64, kk0 = (int64_t)blockIdx.x * 64;
-  const int tid = threadIdx.x;
-  const int tr = (tid >> 4) * 4, tc = (tid & 15) * 4;
-  float acc[4][4] = {};
-  for (int64_t n0 = 0; n0 < N; n0 += 32) {
-    for (int idx = tid; idx < 64 * 32; idx += 256) {
-      const int mm = idx >> 5, nn = idx & 31;
-      const int64_t m = m0 + mm, n = n0 + nn;
-      xs[nn][mm] = (m < M && n < N) ? to_f32<XT>(x[m * N + n]) : 0.f;
-    }
-    for (int idx = tid; idx < 32 * 32; idx += 256) {
-      const int jj = idx >> 5, nn = idx & 31;
-      const int64_t j = kk0 / 2 + jj, n = n0 + nn;
-      float lo = 0.f, hi = 0.f;
-      if (j < K / 2 && n < N) {
-        const uint32_t b = packed[j * N + n];
-        const float z = zs_to_f32<ZST>(zero, n), s = zs_to_f32<ZST>(scale, n);
-        lo = __fmul_rn(__fsub_rn((float)(b & 0xF), z), s);
-        hi = __fmul_rn(__fsub_rn((float)(b >> 4), z), s);
-      }
-      ws[nn][2 * jj] = lo;
-      ws[nn][2 * jj + 1] = hi;
-    }
-    __syncthreads();
-#pragma unroll 8
-    for (int nn = 0; nn < 32; ++nn) {
-      float a[4], b[4];
-#pragma unroll
-      for (int i = 0; i < 4; ++i) { a[i] = xs[nn][tr + i]; b[i] = ws[nn][tc + i]; }
-#pragma unroll
-      for (int i = 0; i < 4; ++i)
-#pragma unroll
-        for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(a[i], b[j], acc[i][j]);
-    }
-    __syncthreads();
-  }
-#pragma unroll
-  for (int i = 0; i < 4; ++i)
-#pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      const int64_t m = m0 + tr + i, kk = kk0 + tc + j;
-      if (m < M && kk < K) out[m * K + kk] = from_f32<XT>(acc[i][j]);
-    }
-}
-
-constexpr size_t kTicketBytes = 4096;   // 1024 tickets; split-K is only planned below 4 * #SM CTAs
-constexpr size_t kTicketRegionBytes = 16384;   // the largest ticket region of any forward kernel (f16 decode kernel)
+constexpr size_t kTicketBytes = W4_TICKET_REGION;   // 1024 tickets are used here; split-K is only planned below 4 * #SM CTAs
+constexpr size_t kTicketRegionBytes = W4_TICKET_REGION;
 
 struct FwdPlan { int ntok; int mtiles; int ncg; int ksplit; int steps_per_split; };
 
@@ -293,7 +237,7 @@ static FwdPlan plan_fwd(int64_t M, int64_t N, int64_t K) {
   int64_t want = std::max<int64_t>(1, slots / base);
   const int64_t max_split = std::max<int64_t>(1, total_steps / (2 * WWARPS));
   if (want > max_split) want = max_split;
-  if (base > (int64_t)(kTicketBytes / sizeof(int))) want = 1;
+  if (base > 1024) want = 1;
   p.steps_per_split = (int)cdiv(total_steps, want);
   p.ksplit = (int)cdiv(total_steps, p.steps_per_split);
   return p;
@@ -314,14 +258,6 @@ static int launch_fwd(const void* x, const uint8_t* packed, const void* zero, co
     w4_decode_kernel<XT, CT, 2, ZST><<<grid, WWARPS * 32, 0, s>>>((const XT*)x, packed, zero, scale, (XT*)out, M, N, K,
                                                                   p.steps_per_split, p.ksplit, partials, tickets, vec);
   return check_launch("w4_matmul");
-}
-
-template <typename XT, typename ZST>
-static int launch_tb(const void* x, const uint8_t* packed, const void* zero, const void* scale, void* out,
-                     int64_t M, int64_t N, int64_t K, cudaStream_t s) {
-  dim3 grid((unsigned)cdiv(K, 64), (unsigned)cdiv(M, 64));
-  w4_tb_kernel<XT, ZST><<<grid, 256, 0, s>>>((const XT*)x, packed, zero, scale, (XT*)out, M, N, K);
-  return check_launch("w4_matmul_tb");
 }
 
 constexpr int64_t kStreamRows = 16;          // token rows of one pass of the streaming kernel
@@ -387,14 +323,14 @@ static int w4_validate(const void* x, int x_dtype, const uint8_t* packed, const 
 
 }  // namespace jgq
 
-// Workspace layout (forward): int32 tickets first (4096 bytes, 16384 for the f16
-// decode kernel), then the kernels' fp32 slices.  The first 16384 bytes must be zero
+// Workspace layout (forward): 16384 bytes of int32 tickets and scheduling words, then
+// the kernels' fp32 slices.  The first 16384 bytes must be zero
 // before the first launch that uses a workspace; every launch leaves them zero
 // again.  The slices need no initialisation.
 // The size returned covers every activation dtype; a call is accepted with the
 // (possibly smaller) amount its own dtype needs.
 extern "C" size_t jgq_w4_matmul_workspace_bytes(int64_t M, int64_t N, int64_t K, int transpose_b) {
-  if (transpose_b) return 0;
+  if (transpose_b) return (M > 0 && N > 0 && K > 0) ? w4_tb_workspace_bytes(M, N) : 0;
   return w4_forward_need(M, N, K, -1);
 }
 
@@ -409,13 +345,10 @@ extern "C" int jgq_w4_matmul(const void* x, int x_dtype, const uint8_t* packed,
   if (M == 0) return JGQ_OK;
   cudaStream_t s = (cudaStream_t)stream;
   if (transpose_b) {
-#define JGQ_TB(XT)                                                                                       \
-  return zs_dtype == JGQ_F32 ? launch_tb<XT, float>(x, packed, zero, scale, out, M, N, K, s)             \
-                             : launch_tb<XT, __half>(x, packed, zero, scale, out, M, N, K, s)
-    if (x_dtype == JGQ_F32) { JGQ_TB(float); }
-    if (x_dtype == JGQ_F16) { JGQ_TB(__half); }
-    JGQ_TB(__nv_bfloat16);
-#undef JGQ_TB
+    const size_t need_tb = w4_tb_workspace_bytes(M, N);
+    JGQ_REQUIRE(ws && ws_bytes >= need_tb, JGQ_ERR_WORKSPACE, "w4_matmul: workspace %zu < %zu bytes", ws_bytes, need_tb);
+    JGQ_REQUIRE(aligned(ws, 256), JGQ_ERR_ALIGN, "w4_matmul: workspace must be 256-byte aligned");
+    return launch_w4_tb(x, x_dtype, packed, zero, scale, zs_dtype, out, M, N, K, ws, s);
   }
   JGQ_REQUIRE(aligned(x, 8), JGQ_ERR_ALIGN, "w4_matmul: x must be 8-byte aligned");
   const size_t need = w4_forward_need(M, N, K, x_dtype);

@@ -449,7 +449,7 @@ int launch_w4_stream(const StreamPlan& pl, const void* x, int x_dtype, const uin
   memset(&p, 0, sizeof(p));
   p.x = x; p.zero = zero; p.scale = scale; p.out = out;
   p.tickets = (int*)ws;
-  p.partials = (float*)((char*)ws + 4096);
+  p.partials = (float*)((char*)ws + W4_TICKET_REGION);
   p.M = M; p.N = N; p.K = K;
   p.ncg = pl.ncg; p.mtiles = 1; p.spc = pl.spc; p.S = pl.S; p.G = pl.G; p.maxc = pl.maxc;
   if (x_dtype == JGQ_F16) { p.emask = Biased<__half>::kMask; p.emagic = Biased<__half>::kMagic; }

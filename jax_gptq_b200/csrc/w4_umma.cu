@@ -38,7 +38,7 @@ constexpr int U_MAX_ST = 16;                   // upper bound of every ring dept
 constexpr int U_DQ_WARPS = 8;
 constexpr int U_XWARP = 2 + U_DQ_WARPS;        // the warp that loads activation tiles
 constexpr int U_THREADS = (3 + U_DQ_WARPS) * 32;
-constexpr size_t U_TICKET_BYTES = 4096;
+constexpr size_t U_TICKET_BYTES = W4_TICKET_REGION;   // 1024 tickets are used; the region is common to all forward kernels
 
 struct UmmaParams {
   const uint8_t* packed;
@@ -488,7 +488,7 @@ UmmaPlan plan_w4_umma(int64_t M, int64_t N, int64_t K, int x_dtype) {
   const int64_t base = (int64_t)pl.ncg * pl.mtiles;
   const int sms = sm_count();
   int64_t kmax = std::max<int64_t>(1, total_stages / 8);          // at least 8 stages per CTA
-  if (base > (int64_t)(U_TICKET_BYTES / sizeof(int))) kmax = 1;
+  if (base > 1024) kmax = 1;
   // Split-K only when the tiles alone cannot occupy the SMs.  A CTA costs about 13 us around its
   // stages (TMEM allocation, first loads, epilogue, slice exchange), so short CTAs lose more than
   // a partly empty last wave does: measured at 8192 x 28672, M = 128, one wave and a half of long

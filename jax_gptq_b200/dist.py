@@ -52,14 +52,39 @@ def assign_layers(costs, world):
     return owner
 
 
-def allreduce_hessian(H_sum, n_local, group=None):
+def pack_lower(H_sum, out=None):
+    """The tiles on or below the diagonal of a raw K x K sum (all that carries data before finalize) as one
+    contiguous fp32 vector: what has to travel in the all-reduce.  CUDA tensors only."""
+    from ._lib import lib, check
+    K = H_sum.shape[0]
+    n = lib.jgq_hessian_lower_elems(K)
+    if out is None:
+        out = torch.zeros(n, dtype=torch.float32, device=H_sum.device)
+    check(lib.jgq_hessian_pack_lower(H_sum.data_ptr(), K, out.data_ptr(), torch.cuda.current_stream().cuda_stream))
+    return out
+
+
+def unpack_lower(packed, H_sum):
+    from ._lib import lib, check
+    K = H_sum.shape[0]
+    check(lib.jgq_hessian_unpack_lower(packed.data_ptr(), K, H_sum.data_ptr(), torch.cuda.current_stream().cuda_stream))
+    return H_sum
+
+
+def allreduce_hessian(H_sum, n_local, group=None, lower_only=True):
     """Sum the per-rank raw second-moment sums (K x K, fp32) and sample counts over the group.
-    Returns (H_sum_global, n_global); H_sum is reduced in place."""
+    Returns (H_sum_global, n_global); H_sum is reduced in place.  On CUDA tensors with K % 4 == 0 only the
+    tiles on or below the diagonal are sent (about half the bytes); `lower_only=False` sends the square."""
     rank, world = _world(group)
     if world == 1:
         return H_sum, int(n_local)
     n = torch.tensor([float(n_local)], dtype=torch.float64, device=H_sum.device)
-    dist.all_reduce(H_sum, op=dist.ReduceOp.SUM, group=group)
+    if lower_only and H_sum.is_cuda and H_sum.shape[0] % 4 == 0 and H_sum.is_contiguous():
+        packed = pack_lower(H_sum)
+        dist.all_reduce(packed, op=dist.ReduceOp.SUM, group=group)
+        unpack_lower(packed, H_sum)
+    else:
+        dist.all_reduce(H_sum, op=dist.ReduceOp.SUM, group=group)
     dist.all_reduce(n, op=dist.ReduceOp.SUM, group=group)
     return H_sum, int(round(float(n.item())))
 
@@ -120,3 +145,129 @@ def quantized_matmul_column_sharded(x, qm_shard, group=None, gather=True, N=None
     y2 = y.reshape(-1, y.shape[-1])
     full = gather_columns(y2, None, N if N is not None else -1, group)
     return full.reshape(tuple(lead) + (full.shape[-1],))
+
+
+class ShardedPipeline:
+    """The layer loop for one model on several GPUs: calibration tokens sharded over the ranks, one NCCL
+    all-reduce of the lower triangle of every Hessian, the quantize loop sharded over output channels,
+    an all-gather of the packed column slabs.
+
+    Per linear, on every rank: Hessian of the local tokens (Hessian stream) -> pack the lower tiles ->
+    all-reduce (communication stream, first communicator) -> unpack, finalize with the global token
+    count, damp + invert (replicated: every rank needs the whole factor), quantize and pack this rank's
+    columns (a compute stream) -> all-gather of the packed slabs (second communication stream, second
+    communicator, so that a gather waiting for its quantize loop never holds up the next all-reduce).
+    The all-reduce of linear i overlaps the Hessian GEMM of linear i+1 and the sequential stages of the
+    linears before it.  Every rank issues the same collectives in the same order."""
+
+    def __init__(self, streams=6, group=None):
+        self.rank, self.world = _world(group)
+        self.group_ar = group
+        self.group_ag = dist.new_group() if self.world > 1 else None      # its own NCCL communicator
+        self.hstream = torch.cuda.Stream(priority=0)
+        self.comm_ar = torch.cuda.Stream(priority=-1)
+        self.comm_ag = torch.cuda.Stream(priority=-1)
+        self.workers = [torch.cuda.Stream(priority=-1) for _ in range(max(1, streams))]
+        self.nslots = len(self.workers) + 2
+        self.bufs = {}
+        self.stats = {'allreduce_bytes': 0, 'allgather_bytes': 0}
+
+    def _buf(self, tag, shape, dtype, zero=False):
+        key = (tag, tuple(shape), dtype)
+        t = self.bufs.get(key)
+        if t is None:
+            t = torch.zeros(tuple(shape), dtype=dtype, device='cuda')
+            self.bufs[key] = t
+        elif zero:
+            t.zero_()
+        return t
+
+    def run(self, jobs, n_total, block_size=128, damping=0.01, bits=4, gather=True):
+        """jobs: sequence of (W (K x N, replicated), xs_local (this rank's token batches)); `n_total` is the
+        global token count of every job.  Returns per job (packed (K/2 x N or this rank's slab), scale,
+        zero, (c0, c1))."""
+        from . import gptq as G
+        from ._lib import lib, check
+        world, rank = self.world, self.rank
+        main = torch.cuda.current_stream()
+        start = main.record_event()
+        for st in [self.hstream, self.comm_ar, self.comm_ag] + self.workers:
+            st.wait_event(start)
+        slot_free = [None] * self.nslots
+        results, deferred, ag_events = [], [], []
+        self.stats = {'allreduce_bytes': 0, 'allgather_bytes': 0}
+        for i, job in enumerate(jobs):
+            W, xs = job[0], job[1]
+            x_ready = job[2] if len(job) > 2 else None       # event after which xs may be read (staged copies)
+            K, N = W.shape
+            slot = i % self.nslots
+            wi = i % len(self.workers)
+            ws = self.workers[wi]
+            with torch.cuda.stream(self.hstream):
+                if slot_free[slot] is not None:
+                    self.hstream.wait_event(slot_free[slot])
+                if x_ready is not None:
+                    self.hstream.wait_event(x_ready)
+                H = self._buf(f'H{slot}', (K, K), torch.float32, zero=True)
+                hs = self._buf(f'hs{slot}', (1,), torch.int32, zero=True)
+                G._accumulate_raw(xs, H=H, status=hs)
+                if world > 1:
+                    P = self._buf(f'P{slot}', (lib.jgq_hessian_lower_elems(K),), torch.float32)
+                    pack_lower(H, out=P)
+                ev_h = self.hstream.record_event()
+            if world > 1:
+                with torch.cuda.stream(self.comm_ar):
+                    self.comm_ar.wait_event(ev_h)
+                    dist.all_reduce(P, op=dist.ReduceOp.SUM, group=self.group_ar)
+                    ev_r = self.comm_ar.record_event()
+                self.stats['allreduce_bytes'] += P.numel() * 4
+            else:
+                ev_r = ev_h
+            c0, c1 = shard_range(N, rank, world, 16) if world > 1 else (0, N)
+            with torch.cuda.stream(ws):
+                ws.wait_event(ev_r)
+                if x_ready is not None:
+                    ws.wait_event(x_ready)
+                if world > 1:
+                    unpack_lower(P, H)
+                G._finalize_H(H, n_total)
+                slab = W[:, c0:c1].contiguous() if (c0, c1) != (0, N) else W
+                ready = ws.record_event()
+                Q, params = G.gptq(slab, None, block_size=block_size, damping=damping, bits=bits,
+                                   _defer=deferred, _hess=(H, hs, ready))
+                qm = G.pack_matrix(Q, params)
+                if world > 1 and gather:
+                    # scale / zero depend on W alone (gptq.py:105-118): every rank computes all of them
+                    Wf = W if W.dtype == torch.float32 else W.float()
+                    full_params = G._col_params(Wf.contiguous())
+                    qm.scale, qm.zero = full_params['scale'], full_params['zero']
+                slot_free[slot] = ws.record_event()
+                ev_q = slot_free[slot]
+            packed, scale, zero = qm.int_weight, qm.scale, qm.zero
+            if world > 1 and gather:
+                with torch.cuda.stream(self.comm_ag):
+                    self.comm_ag.wait_event(ev_q)
+                    widths = [shard_range(N, r, world, 16) for r in range(world)]
+                    wmax = max(e - b for b, e in widths)
+                    send = packed
+                    if packed.shape[1] != wmax:
+                        send = torch.zeros((K // 2, wmax), dtype=torch.uint8, device=packed.device)
+                        send[:, :packed.shape[1]] = packed
+                    recv = torch.empty((world, K // 2, wmax), dtype=torch.uint8, device=packed.device)
+                    dist.all_gather_into_tensor(recv, send.contiguous(), group=self.group_ag)
+                    full = torch.cat([recv[r, :, :e - b] for r, (b, e) in enumerate(widths)], dim=1)
+                    for t in (packed, send, recv, full):
+                        t.record_stream(self.comm_ag)
+                    ag_events.append(self.comm_ag.record_event())
+                    self.stats['allgather_bytes'] += recv.numel()
+                results.append((full, scale, zero, (c0, c1)))
+            else:
+                results.append((packed, scale, zero, (c0, c1)))
+        for st in [self.hstream, self.comm_ar, self.comm_ag] + self.workers:
+            main.wait_event(st.record_event())
+        st_word = 0
+        if deferred:
+            for w in torch.stack(deferred).reshape(-1).tolist():
+                st_word |= int(w)
+        G._raise_status(st_word)
+        return results

@@ -131,13 +131,18 @@ def _view3(shape, axis):
 # QuantizedMatrix                                      reference gptq.py:8-42
 # --------------------------------------------------------------------------
 class QuantizedMatrix:
-    """Packed uint8 codes + per-channel zero/scale (fp32) + contraction axis."""
+    """Packed uint8 codes + per-channel zero/scale (fp32) + contraction axis.
 
-    def __init__(self, int_weight, zero, scale, contraction_axis=0):
+    ``bits`` is 4 for the reference's format (two codes per byte, gptq.py:237-249).  ``bits=3`` marks the
+    3-bit storage format of this library (eight codes in three bytes along the contraction axis), which the
+    reference does not have; `pack_matrix(..., bits=3)` produces it."""
+
+    def __init__(self, int_weight, zero, scale, contraction_axis=0, bits=4):
         self.int_weight = int_weight
         self.zero = zero
         self.scale = scale
         self.contraction_axis = contraction_axis
+        self.bits = bits
 
     @property
     def shape(self):
@@ -160,7 +165,10 @@ def quant_matrix_shape(quantized_matrix, bits=4):
     mat = quantized_matrix.int_weight
     ele_width = mat.element_size() * 8 if isinstance(mat, torch.Tensor) else mat.dtype.itemsize * 8
     shape = list(mat.shape)
-    shape[quantized_matrix.contraction_axis] *= ele_width // bits
+    if getattr(quantized_matrix, 'bits', 4) == 3:
+        shape[quantized_matrix.contraction_axis] = shape[quantized_matrix.contraction_axis] * ele_width // 3
+    else:
+        shape[quantized_matrix.contraction_axis] *= ele_width // bits
     return tuple(shape)
 
 
@@ -229,10 +237,30 @@ def _finalize_H(H, n_total):
     return H
 
 
+def _accumulate_f64(xs):
+    """fp64 form of the Hessian (gptq.py:87 with use_fp64=True): returns the finalized K x K double matrix."""
+    H, n_total = None, 0
+    for batch in xs:
+        b = _to_dev(batch)
+        if b.dtype not in _DT:
+            b = b.to(torch.float32)
+        K = b.shape[-1]
+        b = b.reshape(-1, K)
+        if not b.is_contiguous():
+            b = b.contiguous()
+        if H is None:
+            H = torch.zeros((K, K), dtype=torch.float64, device=b.device)
+        check(lib.jgq_hessian_accum_f64(b.data_ptr(), _DT[b.dtype], b.shape[0], K, H.data_ptr(), _stream()))
+        n_total += b.shape[0]
+    check(lib.jgq_hessian_finalize_f64(H.data_ptr(), H.shape[0], float(n_total), _stream()))
+    return H
+
+
 def accumulate_H(xs, use_fp64=False):
-    """(1/n) sum_t x_t x_t^T over a list of calibration batches (gptq.py:76-103)."""
+    """(1/n) sum_t x_t x_t^T over a list of calibration batches (gptq.py:76-103); fp64 with `use_fp64`."""
     if use_fp64:
-        raise NotImplementedError('use_fp64=True is not available in the CUDA path')
+        H = _accumulate_f64(xs)
+        return _out(H, all(_is_np(x) for x in xs))
     as_np = all(_is_np(x) for x in xs)
     status = torch.zeros(1, dtype=torch.int32, device=_dev())
     H, n = _accumulate_raw(xs, status=status)
@@ -278,6 +306,18 @@ def _damp_and_invert(Wf, H, damping):
     return L, status
 
 
+def _damp_and_invert_f64(Wf, H64, damping):
+    """use_fp64 form (gptq.py:186-197): H in double, L returned in fp32."""
+    K, N = Wf.shape
+    L = _tmp('L', (K, K), torch.float32)
+    status = _tmp('status', (1,), torch.int32, zero=True)
+    need = lib.jgq_damp_invert_f64_workspace_bytes(K)
+    ws = _workspace_for(need)
+    check(lib.jgq_damp_invert_f64(Wf.data_ptr(), N, H64.data_ptr(), K, float(damping), L.data_ptr(),
+                                  ws.data_ptr(), need, status.data_ptr(), _stream()))
+    return L, status
+
+
 def _quantize(Wf, L, params, block_size, out_dtype, want_codes=False):
     K, N = Wf.shape
     Q = _tmp('Q', (K, N), out_dtype)
@@ -305,13 +345,14 @@ def gptq(W, xs, block_size=128, actorder=False, damping=0.01, use_fp64=False, *,
     reference (gptq.py:182-212): Q holds the dequantised values in W's dtype and
     params = {'scale', 'zero', 'maxq'}.
 
+    ``use_fp64`` carries the Hessian and the factor of its inverse in double precision, as the
+    reference does under ``enable_x64`` (gptq.py:186-197); the loop itself stays fp32.
+
     Keyword-only extras (not in the reference): ``bits`` (3-bit uses maxq=7 with
     the same nibble container), ``H`` (a finalized Hessian to reuse, e.g. for
     linears fed by the same activation), ``return_codes`` (also return the uint8
     codes the kernel produced alongside Q).
     """
-    if use_fp64:
-        raise NotImplementedError('use_fp64=True is not available in the CUDA path')
     as_np = _is_np(W)
     Wd = _to_dev(W)
     if Wd.dim() != 2:
@@ -324,15 +365,21 @@ def gptq(W, xs, block_size=128, actorder=False, damping=0.01, use_fp64=False, *,
         raise ValueError(f'K={K} must be a multiple of block_size={block_size}')
     params = _col_params(Wf, bits)                           # gptq.py:185 (before any fix-up)
     h_status = _tmp('h_status', (1,), torch.int32, zero=True)
+    hdtype = torch.float64 if use_fp64 else torch.float32
     if _hess is not None:
         # (finalized Hessian, its status word, event) produced on another stream; used in place
         Hd, h_status, ready = _hess
         torch.cuda.current_stream().wait_event(ready)
     elif H is None:
-        Hd, n = _accumulate_raw(xs, status=h_status)
-        Hd = _finalize_H(Hd, n)                              # gptq.py:187
+        if use_fp64:
+            Hd = _accumulate_f64(xs)                         # gptq.py:186-187 under enable_x64
+        else:
+            Hd, n = _accumulate_raw(xs, status=h_status)
+            Hd = _finalize_H(Hd, n)                          # gptq.py:187
     else:
-        Hd = _to_dev(H, torch.float32).clone().contiguous()
+        Hd = _to_dev(H, hdtype).clone().contiguous()
+    if Hd.dtype != hdtype:
+        Hd = Hd.to(hdtype)
     if Hd.shape != (K, K):
         raise AssertionError(f'Hessian shape {tuple(Hd.shape)} does not match K={K}')
     perm = None
@@ -341,7 +388,7 @@ def gptq(W, xs, block_size=128, actorder=False, damping=0.01, use_fp64=False, *,
         perm = torch.flip(torch.argsort(d, stable=True), dims=(0,))
         Wf = Wf[perm, :].contiguous()
         Hd = Hd[perm][:, perm].contiguous()
-    L, status = _damp_and_invert(Wf, Hd, damping)            # gptq.py:193
+    L, status = (_damp_and_invert_f64 if use_fp64 else _damp_and_invert)(Wf, Hd, damping)   # gptq.py:193, 197
     Q, codes = _quantize(Wf, L, params, block_size, orig_dtype, return_codes)
     if perm is not None:                                     # gptq.py:177-180
         invperm = torch.argsort(perm)
@@ -363,8 +410,9 @@ def gptq(W, xs, block_size=128, actorder=False, damping=0.01, use_fp64=False, *,
 # --------------------------------------------------------------------------
 # pack / unpack                                       reference gptq.py:214-292
 # --------------------------------------------------------------------------
-def pack_along_axis(axis, w):
-    """byte j = w[2j] | w[2j+1] << 4 along `axis` (gptq.py:237-249, 282-283)."""
+def pack_along_axis(axis, w, bits=4):
+    """byte j = w[2j] | w[2j+1] << 4 along `axis` (gptq.py:237-249, 282-283).  ``bits=3`` (not in the
+    reference): eight codes -> three bytes, code i in bits [3i, 3i+3) of the little-endian 24-bit word."""
     as_np = _is_np(w)
     t = _to_dev(w)
     if axis >= t.dim():
@@ -377,13 +425,20 @@ def pack_along_axis(axis, w):
     t = t.contiguous()
     outer, alen, inner = _view3(t.shape, axis)
     shape = list(t.shape)
+    if bits == 3:
+        if alen % 8:
+            raise ValueError(f'3-bit packing needs a multiple of 8 along the packed axis, got {alen}')
+        shape[axis] = alen * 3 // 8
+        out = torch.empty(shape, dtype=torch.uint8, device=t.device)
+        check(lib.jgq_pack_int3(t.data_ptr(), code_dt, out.data_ptr(), outer, alen, inner, _stream()))
+        return _out(out, as_np)
     shape[axis] = alen // 2
     out = torch.empty(shape, dtype=torch.uint8, device=t.device)
     check(lib.jgq_pack_int4(t.data_ptr(), code_dt, out.data_ptr(), outer, alen, inner, _stream()))
     return _out(out, as_np)
 
 
-def unpack_along_axis(axis, w):
+def unpack_along_axis(axis, w, bits=4):
     """Inverse of pack_along_axis (gptq.py:251-263, 285-286)."""
     as_np = _is_np(w)
     t = _to_dev(w)
@@ -394,6 +449,11 @@ def unpack_along_axis(axis, w):
     t = t.contiguous()
     outer, plen, inner = _view3(t.shape, axis)
     shape = list(t.shape)
+    if bits == 3:
+        shape[axis] = plen * 8 // 3
+        out = torch.empty(shape, dtype=torch.uint8, device=t.device)
+        check(lib.jgq_unpack_int3(t.data_ptr(), out.data_ptr(), outer, plen, inner, _stream()))
+        return _out(out, as_np)
     shape[axis] = plen * 2
     out = torch.empty(shape, dtype=torch.uint8, device=t.device)
     check(lib.jgq_unpack_int4(t.data_ptr(), out.data_ptr(), outer, plen, inner, _stream()))
@@ -416,8 +476,9 @@ def unpack_colwise(w):
     return unpack_along_axis(0, w)
 
 
-def pack_matrix(Q, params, contraction_axis=0):
-    """codes = round(Q / scale + zero) packed along `contraction_axis` (gptq.py:214-228)."""
+def pack_matrix(Q, params, contraction_axis=0, bits=4):
+    """codes = round(Q / scale + zero) packed along `contraction_axis` (gptq.py:214-228).  ``bits=3`` stores a
+    3-bit result (maxq = 7) in the 3-bit format instead of one nibble per code."""
     as_np = _is_np(Q)
     Qd = _to_dev(Q)
     if Qd.dtype not in _DT:
@@ -435,8 +496,14 @@ def pack_matrix(Q, params, contraction_axis=0):
     packed = torch.empty(shape, dtype=torch.uint8, device=Qd.device)
     check(lib.jgq_pack_matrix(Qd.data_ptr(), _DT[Qd.dtype], scale.data_ptr(), zero.data_ptr(),
                               packed.data_ptr(), outer, alen, inner, _stream()))
+    if bits == 3:
+        # the fused kernel rounds to codes and packs nibbles; the 3-bit format is made from those codes
+        codes = unpack_along_axis(contraction_axis, packed)
+        if int(codes.max()) > 7:
+            raise ValueError('pack_matrix(bits=3): codes above 7; the matrix was not quantized to 3 bits')
+        packed = pack_along_axis(contraction_axis, codes, bits=3)
     return QuantizedMatrix(int_weight=_out(packed, as_np), zero=_out(zero, as_np), scale=_out(scale, as_np),
-                           contraction_axis=contraction_axis)
+                           contraction_axis=contraction_axis, bits=bits)
 
 
 def unpack_matrix(weight, dtype=None):
@@ -449,12 +516,33 @@ def unpack_matrix(weight, dtype=None):
     axis = weight.contraction_axis
     outer, plen, inner = _view3(packed.shape, axis)
     shape = list(packed.shape)
-    shape[axis] = plen * 2
     out_dtype = dtype or torch.float32
+    if getattr(weight, 'bits', 4) == 3:
+        shape[axis] = plen * 8 // 3
+        out = torch.empty(shape, dtype=out_dtype, device=packed.device)
+        check(lib.jgq_unpack_matrix3(packed.data_ptr(), zero.data_ptr(), scale.data_ptr(), out.data_ptr(),
+                                     _DT[out_dtype], outer, plen, inner, _stream()))
+        return _out(out, as_np)
+    shape[axis] = plen * 2
     out = torch.empty(shape, dtype=out_dtype, device=packed.device)
     check(lib.jgq_unpack_matrix(packed.data_ptr(), zero.data_ptr(), scale.data_ptr(), out.data_ptr(),
                                 _DT[out_dtype], outer, plen, inner, _stream()))
     return _out(out, as_np)
+
+
+def to_int4_layout(weight):
+    """The two-codes-per-byte QuantizedMatrix (gptq.py:246-247) of a 3-bit one: what the matmul kernels read.
+    A 4-bit matrix is returned as it is."""
+    if getattr(weight, 'bits', 4) != 3:
+        return weight
+    packed = _to_dev(weight.int_weight).contiguous()
+    axis = weight.contraction_axis
+    outer, plen, inner = _view3(packed.shape, axis)
+    shape = list(packed.shape)
+    shape[axis] = plen * 4 // 3
+    out = torch.empty(shape, dtype=torch.uint8, device=packed.device)
+    check(lib.jgq_repack_int3_to_int4(packed.data_ptr(), out.data_ptr(), outer, plen, inner, _stream()))
+    return QuantizedMatrix(out, weight.zero, weight.scale, axis, bits=4)
 
 
 # --------------------------------------------------------------------------

@@ -77,6 +77,14 @@ def quantized_matmul(x, quantized_matrix, transpose_b=False):
     xd = _to_dev(x)
     if xd.dtype not in _DT:
         xd = xd.to(torch.float32)
+    if getattr(quantized_matrix, 'bits', 4) == 3:
+        # 3-bit storage: expanded once to the nibble layout the kernels read and kept with the matrix
+        cached = getattr(quantized_matrix, '_int4', None)
+        if cached is None:
+            from .gptq import to_int4_layout
+            cached = to_int4_layout(quantized_matrix)
+            quantized_matrix._int4 = cached
+        quantized_matrix = cached
     w = _to_dev(quantized_matrix.int_weight).contiguous()
     if w.dim() != 2 or quantized_matrix.contraction_axis != 0:
         raise ValueError('quantized_matmul expects a 2-D QuantizedMatrix packed along axis 0')

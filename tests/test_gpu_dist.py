@@ -46,7 +46,16 @@ def _worker(rank, world, port, q):
         y_full = op.quantized_matmul(x, qm_full)
         y = D.quantized_matmul_column_sharded(x, qm_shard, gather=True, N=N)
         err = float((y.float() - y_full.float()).abs().max().item())
-        q.put((rank, same, ok_scale, err, tuple(y.shape)))
+        # the whole layer loop on the ranks: lower-triangle all-reduce, column-sharded quantize, all-gather
+        pipe = D.ShardedPipeline(streams=2)
+        jobs = [(W, [X[b:e]]), (W[:, :320].contiguous(), [X[b:e]])]
+        res = pipe.run(jobs, n, block_size=128)
+        torch.cuda.synchronize()
+        ref0 = G.pack_matrix(Q_full, p_full).int_weight
+        same_pipe = float((res[0][0] == ref0).float().mean().item())
+        ok_pipe = tuple(res[0][0].shape) == (K // 2, N) and tuple(res[1][0].shape) == (K // 2, 320) \
+            and bool(torch.equal(res[0][1], p_full['scale']))
+        q.put((rank, same, ok_scale, err, tuple(y.shape), same_pipe, ok_pipe))
     finally:
         dist.destroy_process_group()
 
@@ -66,7 +75,26 @@ def test_token_and_column_sharding_two_gpus():
     for p in procs:
         p.join(timeout=120)
         assert p.exitcode == 0
-    for rank, same, ok_scale, err, shape in results:
+    for rank, same, ok_scale, err, shape, same_pipe, ok_pipe in results:
         assert same >= 0.999, f'rank {rank}: identical values {same}'
         assert ok_scale
         assert err <= 2e-2 and shape == (16, 640)
+        assert same_pipe >= 0.998 and ok_pipe, f'rank {rank}: pipeline bytes identical {same_pipe}'
+
+
+def test_lower_triangle_pack_roundtrip():
+    """What the all-reduce sends: the tiles on or below the diagonal, packed and unpacked without loss."""
+    import importlib
+    D = importlib.import_module('jax_gptq_b200.dist')
+    from jax_gptq_b200 import _lib
+    for K in (128, 256, 768, 840, 1000):
+        H = torch.randn(K, K, device='cuda')
+        P = D.pack_lower(H)
+        assert P.numel() == _lib.lib.jgq_hessian_lower_elems(K)
+        H2 = torch.full((K, K), float('nan'), device='cuda')
+        D.unpack_lower(P, H2)
+        i = torch.arange(K, device='cuda')
+        keep = i[None, :] < (128 * (i // 128 + 1))[:, None]
+        assert torch.equal(H2[keep], H[keep])
+        assert bool(torch.isnan(H2[~keep]).all())
+        assert bool(keep[i[:, None] >= i[None, :]].all())          # the lower triangle is inside what travels

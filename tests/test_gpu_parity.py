@@ -90,6 +90,49 @@ def test_pack_matrix_unpack_matrix_bit_exact(G, shape, axis):
     assert np.array_equal(host(un), Q)
 
 
+def _pack3_numpy(codes, axis):
+    c = np.moveaxis(codes.astype(np.uint32), axis, 0)
+    g = c.reshape((c.shape[0] // 8, 8) + c.shape[1:])
+    w = np.zeros((g.shape[0],) + g.shape[2:], dtype=np.uint32)
+    for i in range(8):
+        w |= (g[:, i] & 7) << (3 * i)
+    out = np.stack([(w >> (8 * b)) & 0xFF for b in range(3)], axis=1).astype(np.uint8)
+    return np.moveaxis(out.reshape((g.shape[0] * 3,) + g.shape[2:]), 0, axis)
+
+
+@pytest.mark.parametrize('shape,axis', [((256, 64), 0), ((64, 40), 1), ((4, 16, 9), 1), ((8, 909), 0), ((0, 16), 0)])
+def test_pack3_unpack3_bit_exact(G, shape, axis):
+    """The 3-bit storage format (eight codes in three bytes) against a plain NumPy statement of it."""
+    rng = np.random.default_rng(14)
+    w = rng.integers(0, 8, size=shape, dtype=np.uint8)
+    packed = G.pack_along_axis(axis, dev(w), bits=3)
+    assert packed.shape[axis] == shape[axis] * 3 // 8
+    assert np.array_equal(host(packed), _pack3_numpy(w, axis))
+    assert np.array_equal(host(G.unpack_along_axis(axis, packed, bits=3)), w)
+    with pytest.raises(ValueError):
+        G.pack_along_axis(0, dev(np.zeros((12, 4), dtype=np.uint8)), bits=3)
+
+
+def test_gptq_3bit_storage_and_matmul(G):
+    """A 3-bit GPTQ result stored in the 3-bit format: 3/8 of a byte per weight, unpack_matrix gives Q back bit
+    for bit, and the matmul runs on its nibble expansion."""
+    rng = np.random.default_rng(15)
+    K, N = 256, 192
+    W = rng.standard_normal((K, N)).astype(np.float32)
+    xs = [rng.standard_normal((128, K)).astype(np.float32) for _ in range(4)]
+    Q, params = G.gptq(dev(W), [dev(x) for x in xs], block_size=64, bits=3)
+    qm3 = G.pack_matrix(Q, params, bits=3)
+    assert qm3.bits == 3 and tuple(qm3.int_weight.shape) == (K * 3 // 8, N) and qm3.shape == (K, N)
+    assert torch.equal(G.unpack_matrix(qm3), Q)
+    qm4 = G.pack_matrix(Q, params)
+    assert torch.equal(G.to_int4_layout(qm3).int_weight, qm4.int_weight)
+    x = dev(xs[0][:8]).half()
+    assert torch.equal(G.quantized_matmul(x, qm3), G.quantized_matmul(x, qm4))
+    Q4, p4 = G.gptq(dev(W), [dev(x) for x in xs], block_size=64)           # a 4-bit result does not fit
+    with pytest.raises(ValueError):
+        G.pack_matrix(Q4, p4, bits=3)
+
+
 # ------------------------------------------------------------- column params ----
 def test_col_params_literal_and_random(G):
     w = np.asarray([[0.1, 0.2, 0.3, 0.4], [-0.1, -0.1, -0.1, -0.1]], dtype=np.float32)   # tests.py:34-44
@@ -297,6 +340,56 @@ def test_gptq_actorder_and_3bit(G):
     assert (host(codes) == it['codes']).mean() >= 0.999
 
 
+def test_use_fp64_hessian_and_inverse(G):
+    """use_fp64=True (gptq.py:87, 186-197): Hessian and factor of the inverse in double precision."""
+    import importlib; gg = importlib.import_module('jax_gptq_b200.gptq')
+    rng = np.random.default_rng(58)
+    for K in (96, 200, 512):
+        xs = [(rng.standard_normal((300, K)) * np.linspace(0.2, 3.0, K)).astype(np.float32) for _ in range(3)]
+        H = G.accumulate_H([dev(x) for x in xs], use_fp64=True)
+        assert H.dtype == torch.float64
+        ref = R.accumulate_H_direct(xs, use_fp64=True)
+        assert np.allclose(host(H), ref, rtol=1e-13, atol=1e-13 * np.abs(ref).max())
+        assert np.array_equal(host(H), host(H).T)
+        W = rng.standard_normal((K, 40)).astype(np.float32)
+        W_ref, L_ref, bad = R.damp_and_invert(W, ref, 0.01)          # fp64 throughout (H is fp64)
+        assert not bad
+        Wd = dev(W)
+        L, status = gg._damp_and_invert_f64(Wd, dev(ref), 0.01)
+        assert int(status.item()) == 0 and L.dtype == torch.float32
+        assert np.allclose(host(L), L_ref.astype(np.float32), rtol=0, atol=1e-6 * np.abs(L_ref).max())
+        assert np.all(np.triu(host(L), 1) == 0)
+    # a dead feature and a matrix that is not positive definite
+    X = rng.standard_normal((400, 64)).astype(np.float32)
+    X[:, 5] = 0
+    Hd = G.accumulate_H([dev(X)], use_fp64=True)
+    W = rng.standard_normal((64, 8)).astype(np.float32)
+    Wd = dev(W)
+    L, status = gg._damp_and_invert_f64(Wd, Hd.clone(), 0.01)
+    W_ref, L_ref, _ = R.damp_and_invert(W, host(Hd), 0.01)
+    assert int(status.item()) == 0 and np.array_equal(host(Wd), W_ref)
+    assert np.allclose(host(L), L_ref.astype(np.float32), atol=1e-6 * np.abs(L_ref).max())
+    _, status = gg._damp_and_invert_f64(dev(W), dev(-np.eye(64)), 0.01)
+    assert int(status.item()) != 0
+
+
+def test_gptq_use_fp64_matches_oracle(G):
+    from jax_gptq_b200 import workloads
+    W, xs = workloads.correlated_layer(59, 384, 256, 2048)
+    Q_ref, p_ref, it = R.gptq(W, xs, block_size=128, use_fp64=True, return_internals=True)
+    Q, p, codes = G.gptq(dev(W), [dev(x) for x in xs], block_size=128, use_fp64=True, return_codes=True)
+    same = (host(codes) == it['codes']).mean()
+    print(f'use_fp64: identical codes {same:.6f}')
+    assert same >= 0.999
+    e_ref = R.reconstruction_error(W, Q_ref, xs)
+    e_got = R.reconstruction_error(W, host(Q), xs)
+    assert abs(e_got - e_ref) <= 1e-3 * e_ref
+    # act-order goes through the same fp64 matrices
+    Qa_ref, _, ita = R.gptq(W, xs, block_size=128, use_fp64=True, actorder=True, return_internals=True)
+    Qa, _, ca = G.gptq(dev(W), [dev(x) for x in xs], block_size=128, use_fp64=True, actorder=True, return_codes=True)
+    assert (host(ca) == ita['codes']).mean() >= 0.999
+
+
 def test_gptq_pack_roundtrip_integer_calibration(G):
     # reference tests.py:147-156: unpack(pack(Q)) == Q exactly, block_size 4, integer xs
     rng = np.random.default_rng(1)
@@ -392,6 +485,40 @@ def test_matmul_many_ctas_repeatable(G, M, x_dtype):
     rel = float((outs[0] - ref).norm() / ref.norm())
     assert rel <= (2e-5 if x_dtype == 'float32' else 5e-3), f'relative error {rel:.3e}'
     assert float((outs[0] - ref).abs().max()) <= 0.02 * float(ref.abs().max())
+
+
+@pytest.mark.parametrize('M,N,K,x_dtype,rings', [
+    (64, 32000, 5120, 'float16', None),          # 80 stages per CTA, eight expansion warps
+    (600, 8192, 5120, 'float16', None),          # 512-token tiles: both accumulators, four expansion slots
+    (100, 4096, 5120, 'float32', None),          # two activation planes
+    (48, 1024, 8192, 'bfloat16', None),          # few channel groups: split-K with tickets
+    (64, 16384, 5120, 'float16', '8,4,2'),       # two warps per stage, a two-deep activation ring
+    (64, 16384, 5120, 'float16', '16,8,1'),      # a one-deep activation ring
+    (128, 16384, 2560, 'float16', '8,8,3'),      # a raw ring no deeper than the expansion warps
+])
+def test_matmul_tensor_path_every_channel_group(G, M, N, K, x_dtype, rings, monkeypatch):
+    """The tensor-core kernel against an independent product (fp32 matmul of the unpacked weights), judged
+    per 128-channel group - one CTA's work - so that a single CTA with a few per cent of wrong sums cannot
+    hide in the norm of the whole output; ring depths, warps per stage, split-K, two planes and the
+    two-accumulator tile are all visited.  Five launches must agree bit for bit."""
+    if rings:
+        monkeypatch.setenv('JGQ_UMMA_RINGS', rings)
+    torch.manual_seed(7)
+    packed = torch.randint(0, 256, (K // 2, N), dtype=torch.uint8, device='cuda')
+    qm = G.QuantizedMatrix(packed, torch.randint(0, 16, (N,), device='cuda').float(), 0.001 + 0.019 * torch.rand(N, device='cuda'))
+    x = torch.randn(M, K, device='cuda').to(getattr(torch, x_dtype))
+    outs = [G.quantized_matmul(x, qm).float() for _ in range(5)]
+    for o in outs[1:]:
+        assert torch.equal(o, outs[0]), 'repeated launches must agree bit for bit'
+    ref = x.float() @ G.unpack_matrix(qm).float()
+    groups = -(-N // 128)
+    pad = groups * 128 - N
+    d = torch.nn.functional.pad(outs[0] - ref, (0, pad)).reshape(M, groups, 128)
+    r = torch.nn.functional.pad(ref, (0, pad)).reshape(M, groups, 128)
+    rel = d.norm(dim=(0, 2)) / r.norm(dim=(0, 2))
+    tol = 2e-5 if x_dtype == 'float32' else 5e-3
+    worst = int(rel.argmax())
+    assert float(rel.max()) <= tol, f'channel group {worst}: relative error {float(rel.max()):.3e}'
 
 
 def test_matmul_sweep_shape_small_m(G):
