@@ -43,13 +43,19 @@ namespace jgq {
 constexpr int HT_M = 128;                                     // rows of one MMA / one tile
 constexpr int HT_N = 256;                                     // columns of a tile
 constexpr int HT_BK = 32;                                     // tokens per stage (16-token stages measured 1.6x slower)
-constexpr int HT_CHUNK = 2;                                   // stages per short accumulation chain
+#ifndef JGQ_HT_CHUNK
+#define JGQ_HT_CHUNK 2
+#endif
+#ifndef JGQ_HT_STAGES
+#define JGQ_HT_STAGES 3
+#endif
+constexpr int HT_CHUNK = JGQ_HT_CHUNK;                        // stages per short accumulation chain
 constexpr int HT_EPI_WARPS = 8;
 constexpr int HT_THREADS = 64 + 32 * HT_EPI_WARPS;
 constexpr int HT_BOX_BYTES = 64 * HT_BK * 2;                  // 64 features x HT_BK tokens x 2 B
 constexpr int HT_PLANE_BYTES = 6 * HT_BOX_BYTES;              // A: 2 boxes, B: 4 boxes
 constexpr int HT_STAGE_BYTES = 2 * HT_PLANE_BYTES;            // 48 KB (two planes; one-plane batches use half of it)
-constexpr int HT_STAGES = 3;
+constexpr int HT_STAGES = JGQ_HT_STAGES;
 constexpr int HT_RING_BYTES = HT_STAGES * HT_STAGE_BYTES;     // 144 KB: leaves 80 KB of the SM to kernels of other streams
 // No alignment slack: the dynamic shared memory is declared 1024-byte aligned (the kernel checks it).
 constexpr int HT_BAR_BYTES = 256;
@@ -292,11 +298,269 @@ hessian_umma_kernel(const __grid_constant__ CUtensorMap map0, const __grid_const
   }
 }
 
+// =====================================================================================
+// CTA-pair form (tcgen05 cta_group::2): two CTAs on the two SMs of a pair share one 256 x 256 tile.
+//
+// Each CTA keeps 128 rows of the tile: its own A operand (128 features) and ITS HALF of the B operand
+// (128 of the tile's 256 column features); the pair's MMA (issued by the even CTA only, M = 256, N = 256)
+// reads both CTAs' shared memory, and each CTA's tensor memory receives its 128 x 256 half of the result.
+// A stage therefore costs each SM 32 KB of operands instead of 48 KB for the same 128 x 256 outputs - the
+// kernel is bound by exactly that traffic - and a tile on the diagonal loads nothing but A (its B half is
+// its A).  Everything else is the single-CTA kernel: short chains in two alternating accumulators, fp32
+// round-to-nearest long sums in the registers of eight epilogue warps per CTA.
+//
+// Barriers.  full[s] lives in the even CTA and counts the bytes of both CTAs' boxes (the odd CTA's TMA
+// loads name that barrier; its producer never arrives on it).  empty[s] and accf[b] exist in both CTAs
+// and are signalled by two tcgen05.commit each (own barrier, partner's barrier).  acce[b] lives in the even
+// CTA and takes the arrivals of all sixteen epilogue warps.  Addresses in the partner come from `mapa`.
+// No load uses multicast: every CTA fetches its own boxes.
+// =====================================================================================
+constexpr int HP_STAGES = 4;
+constexpr int HP_PLANE_BYTES = 4 * HT_BOX_BYTES;              // A: 2 boxes, B half: 2 boxes
+constexpr int HP_STAGE_BYTES = 2 * HP_PLANE_BYTES;            // 32 KB
+constexpr int HP_RING_BYTES = HP_STAGES * HP_STAGE_BYTES;     // 128 KB
+
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ uint32_t mapa_u32(uint32_t addr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+__device__ __forceinline__ void tma_load_2d_pair(void* smem_dst, const CUtensorMap* map, int c0, int c1, uint32_t bar_cluster_addr) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+      ::"r"(umma::smem_u32(smem_dst)), "l"(map), "r"(c0), "r"(c1), "r"(bar_cluster_addr)
+      : "memory");
+}
+__device__ __forceinline__ void mma_f16_ss_pair(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void mma_commit_pair(uint32_t bar_cluster_addr) {
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar_cluster_addr) : "memory");
+}
+
+__global__ void __launch_bounds__(HT_THREADS, 1)
+hessian_pair_kernel(const __grid_constant__ CUtensorMap map0, const __grid_constant__ CUtensorMap map1,
+                    const HessParams p) {
+  using namespace umma;
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  uint8_t* smem = smem_raw;
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + HP_RING_BYTES);
+  uint64_t* empty_bar = full_bar + HP_STAGES;
+  uint64_t* accf_bar = empty_bar + HP_STAGES;
+  uint64_t* acce_bar = accf_bar + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acce_bar + 2);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();           // 0: issues the pair's MMAs
+  const int pair = blockIdx.x >> 1;
+
+  // ---- which 256 x 256 tile / token slice ----
+  const int slice = pair / p.nseg;
+  int seg = pair % p.nseg;
+  int I = 0;
+  while (seg > I) { seg -= I + 1; ++I; }             // row panel I has tiles 0..I
+  const bool diag = seg == I;
+  const int row0 = I * 256 + 128 * (int)rank;        // this CTA's 128 rows
+  const int col0 = seg * 256;
+  const int colh = col0 + 128 * (int)rank;           // its half of the B operand
+  const int tok0 = slice * p.tokens_per_slice;
+  const int tok_end = min(p.n, tok0 + p.tokens_per_slice);
+  const int nstages = (tok_end - tok0 + HT_BK - 1) / HT_BK;
+  const int nchains = (nstages + HT_CHUNK - 1) / HT_CHUNK;
+
+  const bool misaligned = (smem_u32(smem) & 1023u) != 0u;
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < HP_STAGES; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
+    for (int b = 0; b < 2; ++b) { mbar_init(&accf_bar[b], 1); mbar_init(&acce_bar[b], 2 * HT_EPI_WARPS); }
+    *abort_flag = misaligned ? 1 : 0;
+    if (misaligned && p.status) atomicOr(p.status, JGQ_STATUS_LAYOUT);
+    fence_barrier_init();
+    prefetch_tensormap(&map0);
+    if (p.planes > 1) prefetch_tensormap(&map1);
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"((uint32_t)HT_TMEM_COLS) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();                                // both CTAs' barriers exist before anyone signals across
+  tc_fence_after();
+  const uint32_t tmem_acc = *tmem_slot;
+  const uint32_t full0 = mapa_u32(smem_u32(&full_bar[0]), 0);      // the even CTA's barriers, as seen from either CTA
+  const uint32_t acce0 = mapa_u32(smem_u32(&acce_bar[0]), 0);
+  const uint32_t peer_empty = mapa_u32(smem_u32(&empty_bar[0]), rank ^ 1u);
+  const uint32_t peer_accf = mapa_u32(smem_u32(&accf_bar[0]), rank ^ 1u);
+  const int boxes_b = diag ? 0 : 2;
+  const uint32_t stage_tx = (uint32_t)(p.planes * (2 + boxes_b) * HT_BOX_BYTES);
+
+  if (*abort_flag == 0) {
+  if (warp == 0) {
+    // ===================== TMA producer (both CTAs) =====================
+    int st = 0;
+    uint32_t ph = 0;
+    int issued = 0;
+    for (int kc = 0; kc < nstages; ++kc) {
+      if (kc >= HP_STAGES && !__all_sync(0xffffffffu, mbar_wait(&empty_bar[st], ph ^ 1, abort_flag))) break;
+      if (lane == 0) {
+        if (rank == 0) mbar_expect_tx(&full_bar[st], 2 * stage_tx);       // the bytes of both CTAs
+        const int tok = tok0 + kc * HT_BK;
+        uint8_t* sb = smem + st * HP_STAGE_BYTES;
+        const uint32_t bar = full0 + (uint32_t)(st * 8);
+        for (int pl = 0; pl < p.planes; ++pl) {
+          const CUtensorMap* m = pl == 0 ? &map0 : &map1;
+          uint8_t* pb = sb + pl * HP_PLANE_BYTES;
+          for (int g = 0; g < 2; ++g) tma_load_2d_pair(pb + g * HT_BOX_BYTES, m, row0 + 64 * g, tok, bar);
+          for (int g = 0; g < boxes_b; ++g) tma_load_2d_pair(pb + (2 + g) * HT_BOX_BYTES, m, colh + 64 * g, tok, bar);
+        }
+      }
+      __syncwarp();
+      issued = kc + 1;
+      if (++st == HP_STAGES) { st = 0; ph ^= 1; }
+    }
+    if (*abort_flag && issued > 0) {
+      // after a timed-out wait boxes may still be in flight: give them a bounded time to land
+      const long long t0 = clock64();
+      while (clock64() - t0 < 20000000LL) {}
+    }
+  } else if (warp == 1) {
+    // ===================== MMA issuer (even CTA only) =====================
+    if (rank == 0) {
+      const uint32_t idesc = make_idesc_f16(p.fmt, 1, 1, 256, 256);
+      const uint64_t desc0 = make_desc_sw128(0, HT_BOX_BYTES, 1024);
+      const uint32_t smem0 = smem_u32(smem);
+      const uint32_t off_b = diag ? 0u : ((uint32_t)(2 * HT_BOX_BYTES) >> 4);
+      const uint32_t off_plane = (uint32_t)HP_PLANE_BYTES >> 4;
+      const int nterms = p.planes > 1 ? (diag ? 4 : 3) : 1;
+      bool ok = true;
+      int st = 0;
+      uint32_t ph = 0;
+      uint32_t sb16 = smem0 >> 4;
+      const uint32_t stage16 = (uint32_t)HP_STAGE_BYTES >> 4;
+      const uint32_t my_empty = smem_u32(&empty_bar[0]), my_accf = smem_u32(&accf_bar[0]);
+      int kc = 0;
+      for (int c = 0; c < nchains && ok; ++c) {
+        const int b = c & 1;
+        if (c >= 2) {
+          ok = __all_sync(0xffffffffu, mbar_wait(&acce_bar[b], ((uint32_t)(c >> 1) & 1u) ^ 1u, abort_flag));
+          if (!ok) break;
+          tc_fence_after();
+        }
+        const uint32_t tacc = tmem_acc + (uint32_t)(b * HT_N);
+        const int kend = min(nstages, kc + HT_CHUNK);
+        bool first = true;
+        for (; kc < kend && ok; ++kc) {
+          ok = __all_sync(0xffffffffu, mbar_wait(&full_bar[st], ph, abort_flag));
+          if (!ok) break;
+          tc_fence_after();
+          if (elect_one()) {
+#pragma unroll
+            for (int k16 = 0; k16 < HT_BK / 16; ++k16) {
+#pragma unroll
+              for (int t = 0; t < 4; ++t) {
+                if (t < nterms) {
+                  const uint32_t pa = (t >= 2) ? off_plane : 0u, pbn = (t & 1) ? off_plane : 0u;
+                  const uint32_t acc_on = (first && k16 == 0 && t == 0) ? 0u : 1u;
+                  const uint64_t db = desc0 + (sb16 + pbn + off_b + (uint32_t)(k16 * 2048 >> 4));
+                  const uint64_t da = desc0 + (sb16 + pa + (uint32_t)(k16 * 2048 >> 4));
+                  mma_f16_ss_pair(tacc, da, db, idesc, acc_on);
+                }
+              }
+            }
+            mma_commit_pair(my_empty + (uint32_t)(st * 8));        // both CTAs' stages are free once these MMAs have read them
+            mma_commit_pair(peer_empty + (uint32_t)(st * 8));
+          }
+          __syncwarp();
+          first = false;
+          if (++st == HP_STAGES) { st = 0; ph ^= 1; sb16 = smem0 >> 4; } else { sb16 += stage16; }
+        }
+        if (ok && elect_one()) {
+          mma_commit_pair(my_accf + (uint32_t)(b * 8));
+          mma_commit_pair(peer_accf + (uint32_t)(b * 8));
+        }
+        __syncwarp();
+      }
+    }
+  } else {
+    // ===================== long accumulation + epilogue (both CTAs) =====================
+    const int e = warp - 2;
+    const int q = warp & 3;
+    const int half = e >> 2;
+    const int cbeg = half * (HT_N / 2);
+    float acc[HT_N / 2];
+#pragma unroll
+    for (int i = 0; i < HT_N / 2; ++i) acc[i] = 0.f;
+    bool ok = true;
+    for (int c = 0; c < nchains && ok; ++c) {
+      const int b = c & 1;
+      ok = __all_sync(0xffffffffu, mbar_wait(&accf_bar[b], (uint32_t)(c >> 1) & 1u, abort_flag));
+      if (!ok) break;
+      tc_fence_after();
+#pragma unroll
+      for (int cc = 0; cc < HT_N / 2; cc += 32) {
+        uint32_t r[32];
+        tmem_ld_32x32(tmem_acc + (uint32_t)(b * HT_N) + ((uint32_t)(32 * q) << 16) + (uint32_t)(cbeg + cc), r);
+        tmem_ld_wait();
+#pragma unroll
+        for (int v = 0; v < 32; ++v) acc[cc + v] = __fadd_rn(acc[cc + v], __uint_as_float(r[v]));
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster(acce0 + (uint32_t)(b * 8));
+    }
+    if (ok) {
+      float* out = p.out + (int64_t)slice * p.slice_stride;
+      const int i = row0 + 32 * q + lane;
+      if (i < p.K) {
+        float* dst = out + (int64_t)i * p.K + col0 + cbeg;
+#pragma unroll
+        for (int v = 0; v < HT_N / 8; ++v) {
+          if (col0 + cbeg + 4 * v < p.K) {          // K % 8 == 0: the four columns are inside together
+            float4 o = make_float4(acc[4 * v], acc[4 * v + 1], acc[4 * v + 2], acc[4 * v + 3]);
+            if (p.S == 1) {
+              const float4 h = *reinterpret_cast<const float4*>(dst + 4 * v);
+              o.x += h.x; o.y += h.y; o.z += h.z; o.w += h.w;
+            }
+            *reinterpret_cast<float4*>(dst + 4 * v) = o;
+          }
+        }
+      }
+    }
+  }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (threadIdx.x == 0 && *abort_flag && !misaligned && p.status) atomicOr(p.status, JGQ_STATUS_TIMEOUT);
+  cluster_sync_all();            // the partner may still signal this CTA's barriers or read its shared memory until here
+  if (warp == 1) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_acc), "r"((uint32_t)HT_TMEM_COLS) : "memory");
+  }
+}
+
 // ------------------------------------------------------------------ host ----
 static int hessian_path_override() {      // 0 = automatic, 1 = FFMA only, 2 = tensor path whenever legal
   static const int v = []() {        // initialised once, thread-safe
     const char* e = getenv("JGQ_HESSIAN_PATH");
-    return (e && !strcmp(e, "simt")) ? 1 : (e && !strcmp(e, "umma")) ? 2 : 0;
+    return (e && !strcmp(e, "simt")) ? 1 : (e && !strcmp(e, "umma")) ? 2 : (e && !strcmp(e, "umma1")) ? 3 : 0;
   }();
   return v;
 }
@@ -309,12 +573,19 @@ HessPlan plan_hessian_umma(int64_t n, int64_t K, int x_dtype) {
   if (ov != 2 && (K < 256 || n < 512)) return pl;     // tiny problems: the FFMA path is already launch-bound
   pl.use = 1;
   pl.planes = (x_dtype == JGQ_F32) ? 2 : 1;
-  pl.panel = HT_M;
+  // CTA pairs on 256 x 256 tiles from K = 512 (below that there are too few tiles to be worth it);
+  // JGQ_HESSIAN_PATH=umma1 keeps the single-CTA kernel
+  pl.panel = (K >= 512 && ov != 3) ? 256 : HT_M;
   int64_t nseg = 0;
-  const int64_t T = cdiv(K, HT_M);
-  for (int64_t I = 0; I < T; ++I) nseg += (I + 2) / 2;
+  if (pl.panel == 256) {
+    const int64_t T2 = cdiv(K, 256);
+    nseg = T2 * (T2 + 1) / 2;
+  } else {
+    const int64_t T = cdiv(K, HT_M);
+    for (int64_t I = 0; I < T; ++I) nseg += (I + 2) / 2;
+  }
   pl.nseg = (int)nseg;
-  const int sms = sm_count();
+  const int sms = pl.panel == 256 ? sm_count() / 2 : sm_count();      // a pair of CTAs takes a pair of SMs
   // Token slices only fill the SMs; with hundreds of tiles (K >= 4096) one slice is enough, and the slice
   // buffers (S x K x K fp32) are kept below 512 MB.
   int64_t smax = std::min<int64_t>(32, std::max<int64_t>(1, n / 1024));
@@ -367,6 +638,30 @@ int launch_hessian_umma(const HessPlan& pl, const void* X, int x_dtype, int64_t 
   p.out = pl.S > 1 ? part : H;
   p.slice_stride = pl.S > 1 ? K * K : 0;
   p.status = status;
+  if (pl.panel == 256) {
+    struct PairAttrTag {};
+    once_per_device<PairAttrTag>([]() {
+      cudaFuncSetAttribute(hessian_pair_kernel, cudaFuncAttributeNonPortableClusterSizeAllowed, 0);
+      cudaGetLastError();
+      return (int)cudaFuncSetAttribute(hessian_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       HP_RING_BYTES + HT_BAR_BYTES);
+    });
+    cudaLaunchConfig_t cfg;
+    memset(&cfg, 0, sizeof(cfg));
+    cfg.gridDim = dim3((unsigned)(2 * pl.nseg * pl.S));
+    cfg.blockDim = dim3(HT_THREADS);
+    cfg.dynamicSmemBytes = HP_RING_BYTES + HT_BAR_BYTES;
+    cfg.stream = s;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    const cudaError_t e = cudaLaunchKernelEx(&cfg, hessian_pair_kernel, m0, m1, p);
+    note_launches(1);
+    if (e != cudaSuccess) { cudaGetLastError(); return fail(JGQ_ERR_CUDA, "hessian_pair: %s", cudaGetErrorString(e)); }
+    return JGQ_OK;
+  }
   struct SmemAttrTag {};
   once_per_device<SmemAttrTag>([]() {
     return (int)cudaFuncSetAttribute(hessian_umma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,

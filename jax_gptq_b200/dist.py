@@ -149,19 +149,26 @@ def quantized_matmul_column_sharded(x, qm_shard, group=None, gather=True, N=None
 
 class ShardedPipeline:
     """The layer loop for one model on several GPUs: calibration tokens sharded over the ranks, one NCCL
-    all-reduce of the lower triangle of every Hessian, the quantize loop sharded over output channels,
-    an all-gather of the packed column slabs.
+    reduction of the lower triangle of every Hessian, the sequential stages of different linears on
+    different ranks, the packed results sent to everybody.
 
     Per linear, on every rank: Hessian of the local tokens (Hessian stream) -> pack the lower tiles ->
-    all-reduce (communication stream, first communicator) -> unpack, finalize with the global token
-    count, damp + invert (replicated: every rank needs the whole factor), quantize and pack this rank's
-    columns (a compute stream) -> all-gather of the packed slabs (second communication stream, second
-    communicator, so that a gather waiting for its quantize loop never holds up the next all-reduce).
-    The all-reduce of linear i overlaps the Hessian GEMM of linear i+1 and the sequential stages of the
-    linears before it.  Every rank issues the same collectives in the same order."""
+    NCCL reduce to the linear's owner (communication stream, first communicator).  The owner - chosen by a
+    greedy longest-job-first assignment that every rank computes identically - unpacks, finalizes with the
+    global token count, damps + inverts, quantizes and packs the whole linear on one of its compute streams,
+    then broadcasts the packed weights (second communication stream, second communicator, so that a broadcast
+    waiting for its quantize loop never holds up the next reduction).  The reduction of linear i overlaps the
+    Hessian GEMM of linear i+1 and the sequential stages of the linears before it.  Every rank issues the same
+    collectives in the same order.
 
-    def __init__(self, streams=6, group=None):
+    `mode='columns'` is the other split the path offers: an all-reduce, a replicated inverse on every rank,
+    the quantize loop sharded over output channels, an all-gather of the packed slabs.  It has no idle
+    ranks for a single linear but repeats the inverse N times; `mode='owner'` divides all the sequential
+    work by N as soon as there are several linears."""
+
+    def __init__(self, streams=6, group=None, mode='owner'):
         self.rank, self.world = _world(group)
+        self.mode = mode
         self.group_ar = group
         self.group_ag = dist.new_group() if self.world > 1 else None      # its own NCCL communicator
         self.hstream = torch.cuda.Stream(priority=0)
@@ -170,7 +177,7 @@ class ShardedPipeline:
         self.workers = [torch.cuda.Stream(priority=-1) for _ in range(max(1, streams))]
         self.nslots = len(self.workers) + 2
         self.bufs = {}
-        self.stats = {'allreduce_bytes': 0, 'allgather_bytes': 0}
+        self.stats = {}
 
     def _buf(self, tag, shape, dtype, zero=False):
         key = (tag, tuple(shape), dtype)
@@ -183,26 +190,32 @@ class ShardedPipeline:
         return t
 
     def run(self, jobs, n_total, block_size=128, damping=0.01, bits=4, gather=True):
-        """jobs: sequence of (W (K x N, replicated), xs_local (this rank's token batches)); `n_total` is the
-        global token count of every job.  Returns per job (packed (K/2 x N or this rank's slab), scale,
-        zero, (c0, c1))."""
+        """jobs: sequence of (W (K x N, replicated), xs_local (this rank's token batches)[, ready_event]);
+        `n_total` is the global token count of every job.  Returns per job (packed, scale, zero, (c0, c1)):
+        the whole linear's packed weights with `gather` (column range (0, N)), else what this rank
+        produced (its slab of columns, or None where it is not the owner)."""
         from . import gptq as G
-        from ._lib import lib, check
+        from ._lib import lib
         world, rank = self.world, self.rank
+        owner_mode = self.mode == 'owner' and world > 1
         main = torch.cuda.current_stream()
         start = main.record_event()
         for st in [self.hstream, self.comm_ar, self.comm_ag] + self.workers:
             st.wait_event(start)
+        jobs = list(jobs)
+        # the owner of every linear: largest sequential cost first, to the least loaded rank
+        owners = assign_layers([float(j[0].shape[0]) ** 2 * (j[0].shape[0] + j[0].shape[1]) + 1e7 for j in jobs], world)
         slot_free = [None] * self.nslots
-        results, deferred, ag_events = [], [], []
-        self.stats = {'allreduce_bytes': 0, 'allgather_bytes': 0}
+        results, deferred = [], []
+        self.stats = {'reduce_bytes': 0, 'gather_bytes': 0, 'mode': self.mode if world > 1 else 'single'}
+        nmine = 0
         for i, job in enumerate(jobs):
             W, xs = job[0], job[1]
-            x_ready = job[2] if len(job) > 2 else None       # event after which xs may be read (staged copies)
+            x_ready = job[2] if len(job) > 2 else None       # event after which W / xs may be read (staged copies)
             K, N = W.shape
             slot = i % self.nslots
-            wi = i % len(self.workers)
-            ws = self.workers[wi]
+            owner = owners[i]
+            mine = (not owner_mode) or owner == rank
             with torch.cuda.stream(self.hstream):
                 if slot_free[slot] is not None:
                     self.hstream.wait_event(slot_free[slot])
@@ -218,49 +231,66 @@ class ShardedPipeline:
             if world > 1:
                 with torch.cuda.stream(self.comm_ar):
                     self.comm_ar.wait_event(ev_h)
-                    dist.all_reduce(P, op=dist.ReduceOp.SUM, group=self.group_ar)
+                    if owner_mode:
+                        dist.reduce(P, dst=owner, op=dist.ReduceOp.SUM, group=self.group_ar)
+                    else:
+                        dist.all_reduce(P, op=dist.ReduceOp.SUM, group=self.group_ar)
                     ev_r = self.comm_ar.record_event()
-                self.stats['allreduce_bytes'] += P.numel() * 4
+                self.stats['reduce_bytes'] += P.numel() * 4
             else:
                 ev_r = ev_h
-            c0, c1 = shard_range(N, rank, world, 16) if world > 1 else (0, N)
-            with torch.cuda.stream(ws):
-                ws.wait_event(ev_r)
-                if x_ready is not None:
-                    ws.wait_event(x_ready)
-                if world > 1:
-                    unpack_lower(P, H)
-                G._finalize_H(H, n_total)
-                slab = W[:, c0:c1].contiguous() if (c0, c1) != (0, N) else W
-                ready = ws.record_event()
-                Q, params = G.gptq(slab, None, block_size=block_size, damping=damping, bits=bits,
-                                   _defer=deferred, _hess=(H, hs, ready))
-                qm = G.pack_matrix(Q, params)
-                if world > 1 and gather:
-                    # scale / zero depend on W alone (gptq.py:105-118): every rank computes all of them
-                    Wf = W if W.dtype == torch.float32 else W.float()
-                    full_params = G._col_params(Wf.contiguous())
-                    qm.scale, qm.zero = full_params['scale'], full_params['zero']
-                slot_free[slot] = ws.record_event()
-                ev_q = slot_free[slot]
-            packed, scale, zero = qm.int_weight, qm.scale, qm.zero
+            c0, c1 = (0, N)
+            if world > 1 and not owner_mode:
+                c0, c1 = shard_range(N, rank, world, 16)
+            packed = scale = zero = None
+            if mine:
+                ws = self.workers[nmine % len(self.workers)]
+                nmine += 1
+                with torch.cuda.stream(ws):
+                    ws.wait_event(ev_r)
+                    if x_ready is not None:
+                        ws.wait_event(x_ready)
+                    if world > 1:
+                        unpack_lower(P, H)
+                    G._finalize_H(H, n_total)
+                    slab = W[:, c0:c1].contiguous() if (c0, c1) != (0, N) else W
+                    ready = ws.record_event()
+                    Q, params = G.gptq(slab, None, block_size=block_size, damping=damping, bits=bits,
+                                       _defer=deferred, _hess=(H, hs, ready))
+                    qm = G.pack_matrix(Q, params)
+                    packed, scale, zero = qm.int_weight, qm.scale, qm.zero
+                    slot_free[slot] = ws.record_event()
+                    ev_q = slot_free[slot]
+            else:
+                slot_free[slot] = ev_r           # the buffers of this slot are free once the reduction has read them
+                ev_q = ev_r
             if world > 1 and gather:
                 with torch.cuda.stream(self.comm_ag):
                     self.comm_ag.wait_event(ev_q)
-                    widths = [shard_range(N, r, world, 16) for r in range(world)]
-                    wmax = max(e - b for b, e in widths)
-                    send = packed
-                    if packed.shape[1] != wmax:
-                        send = torch.zeros((K // 2, wmax), dtype=torch.uint8, device=packed.device)
-                        send[:, :packed.shape[1]] = packed
-                    recv = torch.empty((world, K // 2, wmax), dtype=torch.uint8, device=packed.device)
-                    dist.all_gather_into_tensor(recv, send.contiguous(), group=self.group_ag)
-                    full = torch.cat([recv[r, :, :e - b] for r, (b, e) in enumerate(widths)], dim=1)
-                    for t in (packed, send, recv, full):
-                        t.record_stream(self.comm_ag)
-                    ag_events.append(self.comm_ag.record_event())
-                    self.stats['allgather_bytes'] += recv.numel()
-                results.append((full, scale, zero, (c0, c1)))
+                    if x_ready is not None:
+                        self.comm_ag.wait_event(x_ready)
+                    if owner_mode:
+                        full = packed if mine else torch.empty((K // 2, N), dtype=torch.uint8, device=W.device)
+                        dist.broadcast(full, src=owner, group=self.group_ag)
+                        full.record_stream(self.comm_ag)
+                        self.stats['gather_bytes'] += full.numel()
+                    else:
+                        widths = [shard_range(N, r, world, 16) for r in range(world)]
+                        wmax = max(e - b for b, e in widths)
+                        send = packed
+                        if packed.shape[1] != wmax:
+                            send = torch.zeros((K // 2, wmax), dtype=torch.uint8, device=packed.device)
+                            send[:, :packed.shape[1]] = packed
+                        recv = torch.empty((world, K // 2, wmax), dtype=torch.uint8, device=packed.device)
+                        dist.all_gather_into_tensor(recv, send.contiguous(), group=self.group_ag)
+                        full = torch.cat([recv[r, :, :e - b] for r, (b, e) in enumerate(widths)], dim=1)
+                        for t in (packed, send, recv, full):
+                            t.record_stream(self.comm_ag)
+                        self.stats['gather_bytes'] += recv.numel()
+                    # scale / zero depend on W alone (gptq.py:105-118): every rank computes all of them
+                    Wf = W if W.dtype == torch.float32 else W.float()
+                    full_params = G._col_params(Wf.contiguous())
+                results.append((full, full_params['scale'], full_params['zero'], (0, N)))
             else:
                 results.append((packed, scale, zero, (c0, c1)))
         for st in [self.hstream, self.comm_ar, self.comm_ag] + self.workers:
@@ -269,5 +299,9 @@ class ShardedPipeline:
         if deferred:
             for w in torch.stack(deferred).reshape(-1).tolist():
                 st_word |= int(w)
+        if world > 1:            # a failure on one rank is everybody's: the status words are OR-ed over the ranks
+            t = torch.tensor([st_word], dtype=torch.int32, device='cuda')
+            dist.all_reduce(t, op=dist.ReduceOp.BOR, group=self.group_ar)
+            st_word = int(t.item())
         G._raise_status(st_word)
         return results

@@ -47,14 +47,16 @@ def _worker(rank, world, port, q):
         y = D.quantized_matmul_column_sharded(x, qm_shard, gather=True, N=N)
         err = float((y.float() - y_full.float()).abs().max().item())
         # the whole layer loop on the ranks: lower-triangle all-reduce, column-sharded quantize, all-gather
-        pipe = D.ShardedPipeline(streams=2)
         jobs = [(W, [X[b:e]]), (W[:, :320].contiguous(), [X[b:e]])]
-        res = pipe.run(jobs, n, block_size=128)
-        torch.cuda.synchronize()
         ref0 = G.pack_matrix(Q_full, p_full).int_weight
-        same_pipe = float((res[0][0] == ref0).float().mean().item())
-        ok_pipe = tuple(res[0][0].shape) == (K // 2, N) and tuple(res[1][0].shape) == (K // 2, 320) \
-            and bool(torch.equal(res[0][1], p_full['scale']))
+        same_pipe, ok_pipe = 1.0, True
+        for mode in ('owner', 'columns'):        # reduce to an owner rank + broadcast; all-reduce + column slabs + all-gather
+            pipe = D.ShardedPipeline(streams=2, mode=mode)
+            res = pipe.run(jobs, n, block_size=128)
+            torch.cuda.synchronize()
+            same_pipe = min(same_pipe, float((res[0][0] == ref0).float().mean().item()))
+            ok_pipe = ok_pipe and tuple(res[0][0].shape) == (K // 2, N) and tuple(res[1][0].shape) == (K // 2, 320) \
+                and bool(torch.equal(res[0][1], p_full['scale']))
         q.put((rank, same, ok_scale, err, tuple(y.shape), same_pipe, ok_pipe))
     finally:
         dist.destroy_process_group()
