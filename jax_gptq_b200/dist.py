@@ -299,9 +299,9 @@ class ShardedPipeline:
         if deferred:
             for w in torch.stack(deferred).reshape(-1).tolist():
                 st_word |= int(w)
-        if world > 1:            # a failure on one rank is everybody's: the status words are OR-ed over the ranks
-            t = torch.tensor([st_word], dtype=torch.int32, device='cuda')
-            dist.all_reduce(t, op=dist.ReduceOp.BOR, group=self.group_ar)
-            st_word = int(t.item())
+        if world > 1:            # a failure on one rank is everybody's: the status bits are OR-ed over the ranks
+            bits = torch.tensor([(st_word >> k) & 1 for k in range(16)], dtype=torch.int32, device='cuda')
+            dist.all_reduce(bits, op=dist.ReduceOp.MAX, group=self.group_ar)      # NCCL has no bitwise OR: MAX per bit
+            st_word = sum(int(v) << k for k, v in enumerate(bits.tolist()))
         G._raise_status(st_word)
         return results

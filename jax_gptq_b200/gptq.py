@@ -340,7 +340,7 @@ def _raise_status(st):
 
 
 def gptq(W, xs, block_size=128, actorder=False, damping=0.01, use_fp64=False, *,
-         bits=4, H=None, return_codes=False, _defer=None, _hess=None):
+         bits=4, H=None, return_codes=False, return_packed=False, _defer=None, _hess=None):
     """Quantize W (K x N) with calibration batches xs.  Returns (Q, params) like the
     reference (gptq.py:182-212): Q holds the dequantised values in W's dtype and
     params = {'scale', 'zero', 'maxq'}.
@@ -350,7 +350,10 @@ def gptq(W, xs, block_size=128, actorder=False, damping=0.01, use_fp64=False, *,
 
     Keyword-only extras (not in the reference): ``bits`` (3-bit uses maxq=7 with
     the same nibble container), ``H`` (a finalized Hessian to reuse, e.g. for
-    linears fed by the same activation), ``return_codes`` (also return the uint8
+    linears fed by the same activation), ``return_packed`` (also return the QuantizedMatrix, packed
+    straight from the integer codes the loop produced instead of recovering them from Q by
+    round(Q / scale + zero) as quantize_interpreter.py:285 / gptq.py:221 do - the same bytes, one pass
+    over one byte per weight instead of four), ``return_codes`` (also return the uint8
     codes the kernel produced alongside Q).
     """
     as_np = _is_np(W)
@@ -389,7 +392,7 @@ def gptq(W, xs, block_size=128, actorder=False, damping=0.01, use_fp64=False, *,
         Wf = Wf[perm, :].contiguous()
         Hd = Hd[perm][:, perm].contiguous()
     L, status = (_damp_and_invert_f64 if use_fp64 else _damp_and_invert)(Wf, Hd, damping)   # gptq.py:193, 197
-    Q, codes = _quantize(Wf, L, params, block_size, orig_dtype, return_codes)
+    Q, codes = _quantize(Wf, L, params, block_size, orig_dtype, return_codes or return_packed)
     if perm is not None:                                     # gptq.py:177-180
         invperm = torch.argsort(perm)
         Q = Q[invperm, :].contiguous()
@@ -402,9 +405,13 @@ def gptq(W, xs, block_size=128, actorder=False, damping=0.01, use_fp64=False, *,
         _raise_status(int(combined.item()))                  # gptq.py:194-196 (one host sync per call)
     out_params = {'scale': _out(params['scale'], as_np), 'zero': _out(params['zero'], as_np),
                   'maxq': params['maxq']}
+    extras = ()
+    if return_packed:
+        packed = pack_along_axis(0, codes)       # the nibble container, whatever `bits` (like pack_matrix's default)
+        extras += (QuantizedMatrix(_out(packed, as_np), out_params['zero'], out_params['scale'], 0),)
     if return_codes:
-        return _out(Q, as_np), out_params, _out(codes, as_np)
-    return _out(Q, as_np), out_params
+        extras += (_out(codes, as_np),)
+    return (_out(Q, as_np), out_params) + extras
 
 
 # --------------------------------------------------------------------------
@@ -700,11 +707,12 @@ def gptq_many(jobs, block_size=128, actorder=False, damping=0.01, bits=4, pack=T
                     ws.wait_event(ev)
                 _ARENA = arenas[wi]
                 try:
-                    Q, params = gptq(Wd, xd, block_size=block_size, actorder=actorder, damping=damping, bits=bits,
-                                     _defer=deferred, _hess=hess)
+                    got = gptq(Wd, xd, block_size=block_size, actorder=actorder, damping=damping, bits=bits,
+                               return_packed=pack, _defer=deferred, _hess=hess)
+                    Q, params = got[0], got[1]
                 finally:
                     _ARENA = None
-                res = pack_matrix(Q, params) if pack else (Q.clone(), params)
+                res = got[2] if pack else (Q.clone(), params)      # packed from the loop's own codes
                 if out_host is not None and pack:
                     p, s, z = out_host[i]
                     p.copy_(res.int_weight, non_blocking=True)

@@ -73,7 +73,7 @@ def test_token_and_column_sharding_two_gpus():
     procs = [ctx.Process(target=_worker, args=(r, world, port, q)) for r in range(world)]
     for p in procs:
         p.start()
-    results = [q.get(timeout=300) for _ in range(world)]
+    results = [q.get(timeout=150) for _ in range(world)]
     for p in procs:
         p.join(timeout=120)
         assert p.exitcode == 0

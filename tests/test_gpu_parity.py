@@ -402,6 +402,19 @@ def test_gptq_pack_roundtrip_integer_calibration(G):
     assert (host(G.unpack_along_axis(0, packed.int_weight)) == it['codes']).mean() >= 0.999
 
 
+def test_gptq_return_packed_equals_pack_matrix(G):
+    """Packing straight from the loop's integer codes gives the bytes that round(Q / scale + zero) gives
+    (gptq.py:221), for fp32 and bf16 weights."""
+    rng = np.random.default_rng(54)
+    for dt in (torch.float32, torch.bfloat16):
+        W = torch.from_numpy((0.02 * rng.standard_normal((256, 320))).astype(np.float32)).cuda().to(dt)
+        xs = [dev(rng.standard_normal((256, 256)).astype(np.float32)) for _ in range(2)]
+        Q, p, qm = G.gptq(W, xs, block_size=128, return_packed=True)
+        ref = G.pack_matrix(Q, p)
+        assert Q.dtype == dt and torch.equal(qm.int_weight, ref.int_weight)
+        assert torch.equal(qm.scale, ref.scale) and torch.equal(qm.zero, ref.zero) and qm.shape == (256, 320)
+
+
 def test_gptq_half_weights_and_numpy_io(G):
     rng = np.random.default_rng(53)
     W = (0.02 * rng.standard_normal((128, 256))).astype(np.float16)
