@@ -579,7 +579,7 @@ def run_ours(args):
     peak_tf = float(peaks.get('bf16_tflops', 1590.0))
     peak_sus = float(peaks.get('bf16_tflops_sustained', 1400.0))
     achieved_tf = flops / (h_ms * 1e-3) / 1e12
-    traffic, traffic_src = profile_figure('hessian_umma_k3072_gpt2_block.md', 'dram_bytes_per_launch')
+    traffic, traffic_src = profile_figure('hessian_pair_k3072_gpt2_block.md', 'dram_bytes_per_launch')
     roofline = {'kernel': 'hessian_accum (H += X^T X, K=3072, n=65536, 16 batches)', 'bound': 'tensor',
                 'achieved': achieved_tf, 'peak': peak_tf, 'unit': 'TFLOP/s', 'frac': achieved_tf / peak_tf,
                 'peak_source': ('MEASURED_PEAKS.json bf16_tflops (burst: the stage is timed in isolation)' if peaks

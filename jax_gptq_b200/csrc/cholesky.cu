@@ -20,6 +20,8 @@
 #include "common.cuh"
 #include "sgemm.cuh"
 #include <algorithm>
+#include <cstdlib>
+#include <cstring>
 
 namespace jgq {
 
@@ -76,12 +78,12 @@ __global__ void zero_dead_rows_kernel(float* __restrict__ W, int K, int64_t N,
     W[(int64_t)r * N + c] = 0.f;
 }
 
-// ---- one panel step: factor + invert the 64x64 diagonal block, then one tile of work ----
-// Every CTA of the step factors the (same) diagonal block itself - identical arithmetic,
-// identical bits - so that the panel tiles need no separate launch behind the factorization.
-// The 64x64 block is processed in 16-wide sub-blocks: a single warp factors and inverts a
-// 16x16 block with register rows and shuffles (no block-wide barrier inside), the rest is
-// small shared-memory products.
+// ---- one panel step: factor + invert the 64x64 diagonal block (one CTA), then the step's tiles ----
+// The diagonal block is factored by a single CTA and its inverse handed to the tile kernel through
+// X; the tile kernel is launched with programmatic stream serialization, so its CTAs are already
+// placed (and have fetched their own tiles) when the diagonal kernel ends.  The 64x64 block is
+// processed in 16-wide sub-blocks: a single warp factors and inverts a 16x16 block with register
+// rows and shuffles (no block-wide barrier inside), the rest is small shared-memory products.
 
 // 16x16 Cholesky + inverse of the lower-triangular factor, one warp; lanes 16..31 mirror 0..15.
 __device__ __forceinline__ bool leaf16(float (*a)[CPAD], float (*inv)[CPAD], const int c0) {
@@ -127,7 +129,7 @@ __device__ __forceinline__ bool leaf16(float (*a)[CPAD], float (*inv)[CPAD], con
 }
 
 __global__ void __launch_bounds__(256)
-chol_step_kernel(float* __restrict__ A, float* __restrict__ X, int K, int kb, int tiles_below,
+chol_diag_kernel(const float* __restrict__ A, float* __restrict__ X, int K, int kb,
                  int32_t* __restrict__ status) {
   __shared__ float a[CB][CPAD];
   __shared__ float inv[CB][CPAD];
@@ -149,7 +151,7 @@ chol_step_kernel(float* __restrict__ A, float* __restrict__ X, int K, int kb, in
     const int c0 = 16 * s;
     if (warp == 0) {
       const bool bad = leaf16(a, inv, c0);
-      if (bad && tid == 0 && blockIdx.x == 0) atomicOr(status, JGQ_STATUS_NOT_PD);
+      if (bad && tid == 0) atomicOr(status, JGQ_STATUS_NOT_PD);
     }
     __syncthreads();
     const int rows = CB - (c0 + 16);
@@ -225,28 +227,46 @@ chol_step_kernel(float* __restrict__ A, float* __restrict__ X, int K, int kb, in
     }
   }
 
-  const int bid = blockIdx.x;
-  if (bid == 0) {
-    // The inverse of the diagonal block is part of the result X.  The factor itself is not
-    // written back: nothing reads it after this step, and the other CTAs of this launch may
-    // still be loading the unfactored block from A.
-    for (int idx = tid; idx < nb * nb; idx += 256) {
-      const int i = idx / nb, j = idx % nb;
-      X[(int64_t)(r0 + i) * K + r0 + j] = inv[i][j];
-    }
-    return;
+  // The tile kernel of this step may be scheduled from here on; it still waits for this grid to end.
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  // The inverse of the diagonal block is part of the result X, and what the tiles of this step read.
+  // The factor itself is not written back: nothing reads it after this step.
+  for (int idx = tid; idx < nb * nb; idx += 256) {
+    const int i = idx / nb, j = idx % nb;
+    X[(int64_t)(r0 + i) * K + r0 + j] = inv[i][j];
   }
+}
+
+// One 64x64 tile of a panel step per CTA: (2) a tile of the panel below the diagonal block, or (4) a tile
+// of row block kb of the inverse.  Launched with programmatic stream serialization behind chol_diag_kernel:
+// the CTA fetches its own tile (complete before the diagonal kernel began) and only then waits for the
+// diagonal kernel's result.
+__global__ void __launch_bounds__(256)
+chol_tiles_kernel(float* __restrict__ A, float* __restrict__ X, int K, int kb, int tiles_below) {
+  __shared__ float a[CB][CPAD];
+  __shared__ float inv[CB][CPAD];
+  const int r0 = kb * CB;
+  const int nb = min(CB, K - r0);
+  const int tid = threadIdx.x;
+  const int bid = blockIdx.x;
   const int tr = (tid >> 4) * 4, tc = (tid & 15) * 4;
+  const bool below = bid < tiles_below;
+  const int p0 = (kb + 1) * CB + bid * CB;                 // (2): first row of the panel tile
+  const int c0 = (bid - tiles_below) * CB;                 // (4): first column of the row-block tile
+  for (int idx = tid; idx < CB * CB; idx += 256) {
+    const int i = idx / CB, j = idx % CB;
+    if (below) a[i][j] = (p0 + i < K && j < nb) ? A[(int64_t)(p0 + i) * K + r0 + j] : 0.f;
+    else       a[i][j] = (i < nb) ? X[(int64_t)(r0 + i) * K + c0 + j] : 0.f;
+  }
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  for (int idx = tid; idx < CB * CB; idx += 256) {
+    const int i = idx / CB, j = idx % CB;
+    inv[i][j] = (i < nb && j <= i) ? X[(int64_t)(r0 + i) * K + r0 + j] : 0.f;
+  }
+  __syncthreads();
   float acc[4][4] = {};
-  if (bid <= tiles_below) {
+  if (below) {
     // (2) panel tile below the diagonal block:  tile <- tile * inv^T
-    const int p0 = (kb + 1) * CB + (bid - 1) * CB;
-    __syncthreads();
-    for (int idx = tid; idx < CB * CB; idx += 256) {
-      const int i = idx / CB, j = idx % CB;
-      a[i][j] = (p0 + i < K && j < nb) ? A[(int64_t)(p0 + i) * K + r0 + j] : 0.f;
-    }
-    __syncthreads();
     for (int m = 0; m < nb; ++m) {
       float pv[4], qv[4];
 #pragma unroll
@@ -263,13 +283,6 @@ chol_step_kernel(float* __restrict__ A, float* __restrict__ X, int K, int kb, in
         if (p0 + tr + i < K && tc + j < nb) A[(int64_t)(p0 + tr + i) * K + r0 + tc + j] = acc[i][j];
   } else {
     // (4) row block kb of the inverse:  X[kb, jt] <- -inv * S[kb, jt]
-    const int c0 = (bid - 1 - tiles_below) * CB;
-    __syncthreads();
-    for (int idx = tid; idx < CB * CB; idx += 256) {
-      const int i = idx / CB, j = idx % CB;
-      a[i][j] = (i < nb) ? X[(int64_t)(r0 + i) * K + c0 + j] : 0.f;
-    }
-    __syncthreads();
     for (int m = 0; m < nb; ++m) {
       float pv[4], qv[4];
 #pragma unroll
@@ -341,7 +354,8 @@ extern "C" int jgq_damp_invert(float* W, int64_t N, float* H, int64_t K, float d
   prefer_shared_carveout<diag_stats_kernel>();
   prefer_shared_carveout<build_reversed_kernel>();
   prefer_shared_carveout<zero_dead_rows_kernel>();
-  prefer_shared_carveout<chol_step_kernel>();
+  prefer_shared_carveout<chol_diag_kernel>();
+  prefer_shared_carveout<chol_tiles_kernel>();
   prefer_shared_carveout<reverse_transpose_kernel>();
   diag_stats_kernel<<<1, 1024, 0, s>>>(H, Ki, damping, dead, damp_add);
   JGQ_LAUNCHED();
@@ -370,8 +384,23 @@ extern "C" int jgq_damp_invert(float* W, int64_t N, float* H, int64_t K, float d
       const int below = Ki - r1;
       const int nb = std::min(CB, Ki - kb * CB);
       const int tiles_below = below > 0 ? (int)cdiv(below, CB) : 0;
-      chol_step_kernel<<<(unsigned)(1 + tiles_below + kb), 256, 0, s>>>(A, X, Ki, kb, tiles_below, dev_status);
+      chol_diag_kernel<<<1, 256, 0, s>>>(A, X, Ki, kb, dev_status);
       JGQ_LAUNCHED();
+      if (tiles_below + kb > 0) {
+        cudaLaunchConfig_t cfg;
+        memset(&cfg, 0, sizeof(cfg));
+        cfg.gridDim = dim3((unsigned)(tiles_below + kb));
+        cfg.blockDim = dim3(256);
+        cfg.stream = s;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[0].val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+        const cudaError_t e = cudaLaunchKernelEx(&cfg, chol_tiles_kernel, A, X, Ki, kb, tiles_below);
+        note_launches(1);
+        if (e != cudaSuccess) { cudaGetLastError(); return fail(JGQ_ERR_CUDA, "damp_invert: %s", cudaGetErrorString(e)); }
+      }
       if (c_end > r1) {
         // (3) A[r1:, r1:c_end] -= P P[r1:c_end]^T (lower tiles) and (5) S[r1:c_end, :r1] += P[r1:c_end] X[k, :r1]
         const float* P = A + (int64_t)r1 * K + (int64_t)kb * CB;

@@ -572,8 +572,9 @@ def gptq_many(jobs, block_size=128, actorder=False, damping=0.01, bits=4, pack=T
     * jobs are issued round-robin on `streams` compute streams, so the latency-bound parts of
       one layer (Cholesky panels, the sequential quantize loop) overlap the Hessian GEMM of the
       next ones; each stream has its own scratch buffers;
-    * with `hessian_stream` the Hessian GEMMs, which fill every SM, all go to one stream of lower
-      priority and the compute streams get the higher priority, so that the many short kernels of
+    * with `hessian_stream` the Hessian GEMMs, which fill every SM, go to two streams of lower priority
+      that take turns (the HBM-bound operand split of one linear overlaps the tensor-core kernel of the
+      previous one) and the compute streams get the higher priority, so that the many short kernels of
       the latency-bound parts are placed first whenever an SM frees up;
     * the NaN / not-positive-definite status words are read once, after all jobs were issued.
 
@@ -592,16 +593,17 @@ def gptq_many(jobs, block_size=128, actorder=False, damping=0.01, bits=4, pack=T
     if state is None:
         state = {'copier': torch.cuda.Stream(),
                  'workers': [torch.cuda.Stream(priority=-1 if hessian_stream else 0) for _ in range(nw)],
-                 'hstream': torch.cuda.Stream(priority=0) if hessian_stream else None,
-                 'harena': _Arena(),
+                 'hstreams': [torch.cuda.Stream(priority=0) for _ in range(2)] if hessian_stream else None,
+                 'harenas': [_Arena(), _Arena()],
                  'arenas': [_Arena() for _ in range(nw)]}
         _arena_cache[key] = state
-    copier, workers, arenas, hstream = state['copier'], state['workers'], state['arenas'], state['hstream']
-    harena = state['harena']
+    copier, workers, arenas, hstreams = state['copier'], state['workers'], state['arenas'], state['hstreams']
+    harenas = state['harenas']
+    hstream = hstreams[0] if hstreams is not None else None
     main = torch.cuda.current_stream()
     start = main.record_event()
     copier.wait_event(start)
-    for w in workers + ([hstream] if hstream is not None else []):
+    for w in workers + (hstreams if hstreams is not None else []):
         w.wait_event(start)          # inputs produced on the caller's stream are complete for every stream used here
     done = [None] * nw               # completion event of the last job issued on each worker
 
@@ -683,6 +685,9 @@ def gptq_many(jobs, block_size=128, actorder=False, damping=0.01, bits=4, pack=T
             hess = None
             if hstream is not None:
                 slot = pos % nslots
+                # Two Hessian streams take turns: the operand split (HBM-bound) and the slice reduction of one
+                # linear run beside the tensor-core kernel of the previous one; each has its own scratch.
+                hstream, harena = hstreams[pos % 2], harenas[pos % 2]
                 with torch.cuda.stream(hstream):
                     if ev is not None:
                         hstream.wait_event(ev)
@@ -735,8 +740,9 @@ def gptq_many(jobs, block_size=128, actorder=False, damping=0.01, bits=4, pack=T
         _ARENA = None
     for w in workers:
         main.wait_event(w.record_event())
-    if hstream is not None:
-        main.wait_event(hstream.record_event())
+    if hstreams is not None:
+        for h in hstreams:
+            main.wait_event(h.record_event())
     main.wait_event(copier.record_event())
     if _issued_hook is not None:
         _issued_hook()                   # every launch of the call has been issued; nothing has been waited for
@@ -744,8 +750,7 @@ def gptq_many(jobs, block_size=128, actorder=False, damping=0.01, bits=4, pack=T
     if deferred:                         # the words are bit sets: OR them (synchronises with every worker)
         for w in torch.stack(deferred).reshape(-1).tolist():
             st |= int(w)
-    for a in arenas:
+    for a in arenas + harenas:
         a.release()
-    harena.release()
     _raise_status(st)
     return results
