@@ -344,7 +344,11 @@ extern "C" int jgq_damp_invert(float* W, int64_t N, float* H, int64_t K, float d
   JGQ_REQUIRE(ws_bytes >= jgq_damp_invert_workspace_bytes(K), JGQ_ERR_WORKSPACE,
               "damp_invert: workspace %zu < %zu bytes", ws_bytes, jgq_damp_invert_workspace_bytes(K));
   JGQ_REQUIRE(aligned(ws, 256), JGQ_ERR_ALIGN, "damp_invert: workspace must be 256-byte aligned");
-  cudaStream_t s = (cudaStream_t)stream;
+  // A few launches per 64-wide panel whose arguments depend on these values alone: replayed as a graph when they recur
+  struct { int tag; float damping; int64_t K, N; const void *W, *H, *L, *ws, *status; } key;
+  memset(&key, 0, sizeof(key));
+  key.tag = 1; key.damping = damping; key.K = K; key.N = N; key.W = W; key.H = H; key.L = L; key.ws = ws; key.status = dev_status;
+  return run_replayed(key, (cudaStream_t)stream, [&](cudaStream_t s) -> int {
   const int Ki = (int)K;
   float* A = (float*)ws;
   uint8_t* dead = (uint8_t*)ws + align_up((size_t)K * K * sizeof(float), 256);
@@ -430,4 +434,5 @@ extern "C" int jgq_damp_invert(float* W, int64_t N, float* H, int64_t K, float d
     reverse_transpose_kernel<<<grd, blk, 0, s>>>(X, L, Ki, dev_status);
   }
   return check_launch("damp_invert");
+  });
 }

@@ -252,11 +252,17 @@ extern "C" int jgq_gptq_quantize(float* W, const float* L, const float* scale, c
   JGQ_REQUIRE(ws_bytes >= jgq_gptq_quantize_workspace_bytes(K, N, block_size), JGQ_ERR_WORKSPACE,
               "gptq_quantize: workspace %zu < %zu bytes", ws_bytes, jgq_gptq_quantize_workspace_bytes(K, N, block_size));
   JGQ_REQUIRE(aligned(ws, 16), JGQ_ERR_ALIGN, "gptq_quantize: workspace must be 16-byte aligned");
-  cudaStream_t s = (cudaStream_t)stream;
   float* E = (float*)ws;
-  switch (q_dtype) {
-    case JGQ_F32:  return run_quantize<float>(W, L, scale, zero, (int)K, N, block_size, maxq, (float*)Q, codes, E, s);
-    case JGQ_F16:  return run_quantize<__half>(W, L, scale, zero, (int)K, N, block_size, maxq, (__half*)Q, codes, E, s);
-    default:       return run_quantize<__nv_bfloat16>(W, L, scale, zero, (int)K, N, block_size, maxq, (__nv_bfloat16*)Q, codes, E, s);
-  }
+  // 2 K / block_size launches whose arguments depend on these values alone: replayed as a graph when they recur
+  struct { int tag; int block_size, maxq, q_dtype; int64_t K, N; const void *W, *L, *scale, *zero, *Q, *codes, *E; } key;
+  memset(&key, 0, sizeof(key));
+  key.tag = 2; key.block_size = block_size; key.maxq = maxq; key.q_dtype = q_dtype; key.K = K; key.N = N;
+  key.W = W; key.L = L; key.scale = scale; key.zero = zero; key.Q = Q; key.codes = codes; key.E = E;
+  return run_replayed(key, (cudaStream_t)stream, [&](cudaStream_t s) {
+    switch (q_dtype) {
+      case JGQ_F32:  return run_quantize<float>(W, L, scale, zero, (int)K, N, block_size, maxq, (float*)Q, codes, E, s);
+      case JGQ_F16:  return run_quantize<__half>(W, L, scale, zero, (int)K, N, block_size, maxq, (__half*)Q, codes, E, s);
+      default:       return run_quantize<__nv_bfloat16>(W, L, scale, zero, (int)K, N, block_size, maxq, (__nv_bfloat16*)Q, codes, E, s);
+    }
+  });
 }

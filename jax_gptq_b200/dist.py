@@ -171,10 +171,11 @@ class ShardedPipeline:
         self.mode = mode
         self.group_ar = group
         self.group_ag = dist.new_group() if self.world > 1 else None      # its own NCCL communicator
-        self.hstream = torch.cuda.Stream(priority=0)
+        self.hstreams = [torch.cuda.Stream(priority=0) for _ in range(2)]     # take turns, like gptq_many's
         self.comm_ar = torch.cuda.Stream(priority=-1)
         self.comm_ag = torch.cuda.Stream(priority=-1)
         self.workers = [torch.cuda.Stream(priority=-1) for _ in range(max(1, streams))]
+        self.arenas = None                # one per worker, created on first use (fixed addresses: replayable stages)
         self.nslots = len(self.workers) + 2
         self.bufs = {}
         self.stats = {}
@@ -200,34 +201,47 @@ class ShardedPipeline:
         owner_mode = self.mode == 'owner' and world > 1
         main = torch.cuda.current_stream()
         start = main.record_event()
-        for st in [self.hstream, self.comm_ar, self.comm_ag] + self.workers:
+        for st in self.hstreams + [self.comm_ar, self.comm_ag] + self.workers:
             st.wait_event(start)
         jobs = list(jobs)
+        if self.arenas is None:
+            self.arenas = [G._Arena() for _ in self.workers]
+            self.harenas = [G._Arena() for _ in self.hstreams]
         # the owner of every linear: largest sequential cost first, to the least loaded rank
-        owners = assign_layers([float(j[0].shape[0]) ** 2 * (j[0].shape[0] + j[0].shape[1]) + 1e7 for j in jobs], world)
+        costs = [float(j[0].shape[0]) ** 2 * (j[0].shape[0] + j[0].shape[1]) + 1e7 for j in jobs]
+        owners = assign_layers(costs, world)
+        # issue order (the same on every rank): expensive linears first, so that their long sequential stages run
+        # beside the remaining Hessians instead of after them
+        order = sorted(range(len(jobs)), key=lambda i: (-costs[i], i))
         slot_free = [None] * self.nslots
-        results, deferred = [], []
+        results, deferred = [None] * len(jobs), []
         self.stats = {'reduce_bytes': 0, 'gather_bytes': 0, 'mode': self.mode if world > 1 else 'single'}
         nmine = 0
-        for i, job in enumerate(jobs):
+        for pos, i in enumerate(order):
+            job = jobs[i]
             W, xs = job[0], job[1]
             x_ready = job[2] if len(job) > 2 else None       # event after which W / xs may be read (staged copies)
             K, N = W.shape
-            slot = i % self.nslots
+            slot = pos % self.nslots
             owner = owners[i]
             mine = (not owner_mode) or owner == rank
-            with torch.cuda.stream(self.hstream):
+            hstream = self.hstreams[pos % 2]
+            with torch.cuda.stream(hstream):
                 if slot_free[slot] is not None:
-                    self.hstream.wait_event(slot_free[slot])
+                    hstream.wait_event(slot_free[slot])
                 if x_ready is not None:
-                    self.hstream.wait_event(x_ready)
+                    hstream.wait_event(x_ready)
                 H = self._buf(f'H{slot}', (K, K), torch.float32, zero=True)
                 hs = self._buf(f'hs{slot}', (1,), torch.int32, zero=True)
-                G._accumulate_raw(xs, H=H, status=hs)
+                G._ARENA = self.harenas[pos % 2]
+                try:
+                    G._accumulate_raw(xs, H=H, status=hs)
+                finally:
+                    G._ARENA = None
                 if world > 1:
                     P = self._buf(f'P{slot}', (lib.jgq_hessian_lower_elems(K),), torch.float32)
                     pack_lower(H, out=P)
-                ev_h = self.hstream.record_event()
+                ev_h = hstream.record_event()
             if world > 1:
                 with torch.cuda.stream(self.comm_ar):
                     self.comm_ar.wait_event(ev_h)
@@ -244,7 +258,8 @@ class ShardedPipeline:
                 c0, c1 = shard_range(N, rank, world, 16)
             packed = scale = zero = None
             if mine:
-                ws = self.workers[nmine % len(self.workers)]
+                wi = nmine % len(self.workers)
+                ws = self.workers[wi]
                 nmine += 1
                 with torch.cuda.stream(ws):
                     ws.wait_event(ev_r)
@@ -255,9 +270,12 @@ class ShardedPipeline:
                     G._finalize_H(H, n_total)
                     slab = W[:, c0:c1].contiguous() if (c0, c1) != (0, N) else W
                     ready = ws.record_event()
-                    Q, params = G.gptq(slab, None, block_size=block_size, damping=damping, bits=bits,
-                                       _defer=deferred, _hess=(H, hs, ready))
-                    qm = G.pack_matrix(Q, params)
+                    G._ARENA = self.arenas[wi]
+                    try:
+                        _, _, qm = G.gptq(slab, None, block_size=block_size, damping=damping, bits=bits,
+                                          return_packed=True, _defer=deferred, _hess=(H, hs, ready))
+                    finally:
+                        G._ARENA = None
                     packed, scale, zero = qm.int_weight, qm.scale, qm.zero
                     slot_free[slot] = ws.record_event()
                     ev_q = slot_free[slot]
@@ -290,10 +308,10 @@ class ShardedPipeline:
                     # scale / zero depend on W alone (gptq.py:105-118): every rank computes all of them
                     Wf = W if W.dtype == torch.float32 else W.float()
                     full_params = G._col_params(Wf.contiguous())
-                results.append((full, full_params['scale'], full_params['zero'], (0, N)))
+                results[i] = (full, full_params['scale'], full_params['zero'], (0, N))
             else:
-                results.append((packed, scale, zero, (c0, c1)))
-        for st in [self.hstream, self.comm_ar, self.comm_ag] + self.workers:
+                results[i] = (packed, scale, zero, (c0, c1))
+        for st in self.hstreams + [self.comm_ar, self.comm_ag] + self.workers:
             main.wait_event(st.record_event())
         st_word = 0
         if deferred:
@@ -303,5 +321,7 @@ class ShardedPipeline:
             bits = torch.tensor([(st_word >> k) & 1 for k in range(16)], dtype=torch.int32, device='cuda')
             dist.all_reduce(bits, op=dist.ReduceOp.MAX, group=self.group_ar)      # NCCL has no bitwise OR: MAX per bit
             st_word = sum(int(v) << k for k, v in enumerate(bits.tolist()))
+        for a in self.arenas + self.harenas:
+            a.release()                  # the status read above synchronised with every stream used here
         G._raise_status(st_word)
         return results

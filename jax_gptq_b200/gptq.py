@@ -321,7 +321,7 @@ def _damp_and_invert_f64(Wf, H64, damping):
 def _quantize(Wf, L, params, block_size, out_dtype, want_codes=False):
     K, N = Wf.shape
     Q = _tmp('Q', (K, N), out_dtype)
-    codes = torch.empty((K, N), dtype=torch.uint8, device=Wf.device) if want_codes else None
+    codes = _tmp('codes', (K, N), torch.uint8) if want_codes else None
     need = lib.jgq_gptq_quantize_workspace_bytes(K, N, block_size)
     ws = _workspace_for(need)
     check(lib.jgq_gptq_quantize(Wf.data_ptr(), L.data_ptr(), params['scale'].data_ptr(),
@@ -392,7 +392,18 @@ def gptq(W, xs, block_size=128, actorder=False, damping=0.01, use_fp64=False, *,
         Wf = Wf[perm, :].contiguous()
         Hd = Hd[perm][:, perm].contiguous()
     L, status = (_damp_and_invert_f64 if use_fp64 else _damp_and_invert)(Wf, Hd, damping)   # gptq.py:193, 197
-    Q, codes = _quantize(Wf, L, params, block_size, orig_dtype, return_codes or return_packed)
+    loop_params = params
+    if _ARENA is not None:
+        # Inside a job pipeline every buffer the two sequential stages touch sits at a fixed address per
+        # compute stream, so that the library can replay their launch sequences (recorded once per shape
+        # and stream) instead of enqueueing them kernel by kernel.
+        loop_params = {'scale': _tmp('scale', (N,), torch.float32), 'zero': _tmp('zero', (N,), torch.float32),
+                       'maxq': params['maxq']}
+        loop_params['scale'].copy_(params['scale'])
+        loop_params['zero'].copy_(params['zero'])
+    Q, codes = _quantize(Wf, L, loop_params, block_size, orig_dtype, return_codes or return_packed)
+    if return_codes and _ARENA is not None and codes is not None:
+        codes = codes.clone()            # the arena's buffer is reused by the stream's next job
     if perm is not None:                                     # gptq.py:177-180
         invperm = torch.argsort(perm)
         Q = Q[invperm, :].contiguous()

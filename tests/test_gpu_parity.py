@@ -211,6 +211,54 @@ def test_damp_invert_matches_oracle(G, K):
     assert np.array_equal(host(Wd), W_ref)
 
 
+def test_replayed_stage_sequences_equal_direct_launches(G):
+    """The sequential stages record their launch sequence on the second call with identical arguments and
+    replay it afterwards: every call must give the first (directly launched) call's bits, count the same
+    number of launches, and still report a Hessian that is not positive definite through the status word."""
+    import importlib; gg = importlib.import_module('jax_gptq_b200.gptq')
+    from jax_gptq_b200 import _lib
+    lib, check = _lib.lib, _lib.check
+    rng = np.random.default_rng(77)
+    K, N, bs = 704, 200, 64                                   # ragged last panel, several outer blocks
+    X = rng.standard_normal((3 * K, K)).astype(np.float32)
+    H0 = dev(R.accumulate_H([X]))
+    W0 = dev(rng.standard_normal((K, N)).astype(np.float32))
+    params = gg._col_params(W0.clone())
+    W, H, L = torch.empty_like(W0), torch.empty_like(H0), torch.empty_like(H0)
+    Q = torch.empty_like(W0)
+    codes = torch.empty((K, N), dtype=torch.uint8, device='cuda')
+    status = torch.zeros(1, dtype=torch.int32, device='cuda')
+    need_d = lib.jgq_damp_invert_workspace_bytes(K)
+    need_q = lib.jgq_gptq_quantize_workspace_bytes(K, N, bs)
+    ws_d = torch.empty(need_d, dtype=torch.uint8, device='cuda')
+    ws_q = torch.empty(need_q, dtype=torch.uint8, device='cuda')
+    torch.cuda.synchronize()
+    side = torch.cuda.Stream()                                # the legacy default stream is never recorded
+    outs, counts = [], []
+    for call in range(4):
+        with torch.cuda.stream(side):
+            W.copy_(W0); H.copy_(H0); status.zero_()
+            l0 = lib.jgq_launch_count()
+            check(lib.jgq_damp_invert(W.data_ptr(), N, H.data_ptr(), K, 0.01, L.data_ptr(), ws_d.data_ptr(), need_d,
+                                      status.data_ptr(), side.cuda_stream))
+            check(lib.jgq_gptq_quantize(W.data_ptr(), L.data_ptr(), params['scale'].data_ptr(), params['zero'].data_ptr(),
+                                        K, N, bs, params['maxq'], Q.data_ptr(), _lib.F32, codes.data_ptr(),
+                                        ws_q.data_ptr(), need_q, side.cuda_stream))
+            counts.append(lib.jgq_launch_count() - l0)
+        side.synchronize()
+        assert int(status.item()) == 0
+        outs.append((L.clone(), Q.clone(), codes.clone()))
+    assert len(set(counts)) == 1 and counts[0] > 2 * (K // bs)
+    for L_i, Q_i, c_i in outs[1:]:
+        assert torch.equal(L_i, outs[0][0]) and torch.equal(Q_i, outs[0][1]) and torch.equal(c_i, outs[0][2])
+    with torch.cuda.stream(side):                             # the replayed sequence still reports through `status`
+        W.copy_(W0); H.copy_(-torch.eye(K, device='cuda')); status.zero_()
+        check(lib.jgq_damp_invert(W.data_ptr(), N, H.data_ptr(), K, 0.01, L.data_ptr(), ws_d.data_ptr(), need_d,
+                                  status.data_ptr(), side.cuda_stream))
+    side.synchronize()
+    assert int(status.item()) != 0
+
+
 def test_damp_invert_dead_feature_and_not_pd(G):
     import importlib; gg = importlib.import_module('jax_gptq_b200.gptq')
     rng = np.random.default_rng(33)
