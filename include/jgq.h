@@ -117,6 +117,13 @@ size_t jgq_hessian_lower_elems(int64_t K);
 int jgq_hessian_pack_lower(const float* H, int64_t K, float* packed, void* stream);
 int jgq_hessian_unpack_lower(const float* packed, int64_t K, float* H, void* stream);
 
+/* ---- activation order (gptq.py:170-180): the loop runs on W[perm, :] and H[perm][:, perm], its outputs are put back
+ * with the inverse permutation.  jgq_permute_sym: out[i][j] = H[perm[i]][perm[j]] in one pass (K x K fp32, out != H).
+ * jgq_gather_rows: row i of dst = row index[i] of src, rows of row_bytes bytes (W, Q and the integer codes alike;
+ * at most 65535 rows, dst != src).  perm / index: int64 on the device, as an argsort returns them. */
+int jgq_permute_sym(const float* H, int64_t K, const int64_t* perm, float* out, void* stream);
+int jgq_gather_rows(const void* src, int64_t rows, int64_t row_bytes, const int64_t* index, void* dst, void* stream);
+
 /* ---- damping + Cholesky factor of the inverse (gptq.py:44-48, 155-168) ----
  * In: W (K x N fp32, rows of dead features are zeroed in place), H (K x K fp32,
  * destroyed).  Out: L (K x K fp32, lower, L L^T = (H + damp)^-1, upper = 0),

@@ -37,6 +37,8 @@ SIGNATURES = {
     'jgq_hessian_lower_elems': (_sz, [_i64]),
     'jgq_hessian_pack_lower': (_int, [_vp, _i64, _vp, _vp]),
     'jgq_hessian_unpack_lower': (_int, [_vp, _i64, _vp, _vp]),
+    'jgq_permute_sym': (_int, [_vp, _i64, _vp, _vp, _vp]),
+    'jgq_gather_rows': (_int, [_vp, _i64, _i64, _vp, _vp, _vp]),
     'jgq_damp_invert_workspace_bytes': (_sz, [_i64]),
     'jgq_damp_invert': (_int, [_vp, _i64, _vp, _i64, C.c_float, _vp, _vp, _sz, _vp, _vp]),
     'jgq_hessian_accum_f64': (_int, [_vp, _int, _i64, _i64, _vp, _vp]),

@@ -315,8 +315,8 @@ class ShardedPipeline:
             main.wait_event(st.record_event())
         st_word = 0
         if deferred:
-            for w in torch.stack(deferred).reshape(-1).tolist():
-                st_word |= int(w)
+            for w, hw in torch.stack(deferred).tolist():       # (stage status, Hessian status) per job
+                st_word |= int(w) | (int(hw) << 8)
         if world > 1:            # a failure on one rank is everybody's: the status bits are OR-ed over the ranks
             bits = torch.tensor([(st_word >> k) & 1 for k in range(16)], dtype=torch.int32, device='cuda')
             dist.all_reduce(bits, op=dist.ReduceOp.MAX, group=self.group_ar)      # NCCL has no bitwise OR: MAX per bit

@@ -180,19 +180,31 @@ def _merge_adjacent(xs):
     chunks of a captured activation) are handed to the kernel as one batch: same sum,
     fewer and longer launches."""
     out = []
+    run = None          # [first tensor, rows so far, K, address one past the run, dtype]
+
+    def flush():
+        nonlocal run
+        if run is not None:
+            first, rows, K = run[0], run[1], run[2]
+            out.append(first if rows * K == first.numel() else torch.as_strided(first, (rows, K), (K, 1)))
+            run = None
+
     for b in xs:
-        if (out and isinstance(b, torch.Tensor) and isinstance(out[-1], torch.Tensor)
-                and b.is_cuda and out[-1].is_cuda and b.dtype == out[-1].dtype
-                and b.is_contiguous() and out[-1].is_contiguous() and b.dim() >= 2 and out[-1].dim() >= 2
-                and b.shape[-1] == out[-1].shape[-1]
-                and b.untyped_storage().data_ptr() == out[-1].untyped_storage().data_ptr()
-                and b.data_ptr() == out[-1].data_ptr() + out[-1].numel() * out[-1].element_size()):
-            prev = out[-1]
-            K = prev.shape[-1]
-            rows = prev.numel() // K + b.numel() // K
-            out[-1] = torch.as_strided(prev, (rows, K), (K, 1))
+        if isinstance(b, torch.Tensor) and b.is_cuda and b.dim() >= 2 and b.shape[-1] > 0 and b.is_contiguous():
+            K = b.shape[-1]
+            p = b.data_ptr()
+            nbytes = b.numel() * b.element_size()
+            if (run is not None and run[3] == p and run[2] == K and run[4] == b.dtype
+                    and b.untyped_storage().data_ptr() == run[0].untyped_storage().data_ptr()):
+                run[1] += b.numel() // K
+                run[3] = p + nbytes
+                continue
+            flush()
+            run = [b, b.numel() // K, K, p + nbytes, b.dtype]
         else:
+            flush()
             out.append(b)
+    flush()
     return out
 
 
@@ -367,7 +379,7 @@ def gptq(W, xs, block_size=128, actorder=False, damping=0.01, use_fp64=False, *,
     if K % block_size != 0:
         raise ValueError(f'K={K} must be a multiple of block_size={block_size}')
     params = _col_params(Wf, bits)                           # gptq.py:185 (before any fix-up)
-    h_status = _tmp('h_status', (1,), torch.int32, zero=True)
+    h_status = _tmp('h_status', (1,), torch.int32, zero=True) if _hess is None else None
     hdtype = torch.float64 if use_fp64 else torch.float32
     if _hess is not None:
         # (finalized Hessian, its status word, event) produced on another stream; used in place
@@ -388,9 +400,16 @@ def gptq(W, xs, block_size=128, actorder=False, damping=0.01, use_fp64=False, *,
     perm = None
     if actorder:                                             # gptq.py:170-175
         d = torch.diagonal(Hd)
-        perm = torch.flip(torch.argsort(d, stable=True), dims=(0,))
-        Wf = Wf[perm, :].contiguous()
-        Hd = Hd[perm][:, perm].contiguous()
+        perm = torch.flip(torch.argsort(d, stable=True), dims=(0,)).contiguous()
+        if Hd.dtype == torch.float32:
+            Wp = _tmp('Wperm', (K, N), torch.float32)
+            Hp = _tmp('Hperm', (K, K), torch.float32)
+            check(lib.jgq_gather_rows(Wf.data_ptr(), K, N * 4, perm.data_ptr(), Wp.data_ptr(), _stream()))
+            check(lib.jgq_permute_sym(Hd.data_ptr(), K, perm.data_ptr(), Hp.data_ptr(), _stream()))
+            Wf, Hd = Wp, Hp
+        else:
+            Wf = Wf[perm, :].contiguous()
+            Hd = Hd[perm][:, perm].contiguous()
     L, status = (_damp_and_invert_f64 if use_fp64 else _damp_and_invert)(Wf, Hd, damping)   # gptq.py:193, 197
     loop_params = params
     if _ARENA is not None:
@@ -406,14 +425,20 @@ def gptq(W, xs, block_size=128, actorder=False, damping=0.01, use_fp64=False, *,
         codes = codes.clone()            # the arena's buffer is reused by the stream's next job
     if perm is not None:                                     # gptq.py:177-180
         invperm = torch.argsort(perm)
-        Q = Q[invperm, :].contiguous()
+        Qo = torch.empty_like(Q)
+        check(lib.jgq_gather_rows(Q.data_ptr(), K, N * Q.element_size(), invperm.data_ptr(), Qo.data_ptr(), _stream()))
+        Q = Qo
         if codes is not None:
-            codes = codes[invperm, :].contiguous()
-    combined = status | (h_status << 8)
+            co = torch.empty_like(codes)
+            check(lib.jgq_gather_rows(codes.data_ptr(), K, N, invperm.data_ptr(), co.data_ptr(), _stream()))
+            codes = co
     if _defer is not None:
-        _defer.append(combined)          # the caller checks the status words after its own synchronisation
+        # the caller checks the status words after its own synchronisation; they sit in reused buffers, so
+        # their values are copied out here (one small launch)
+        _defer.append(torch.stack((status.reshape(()), h_status.reshape(()))))
     else:
-        _raise_status(int(combined.item()))                  # gptq.py:194-196 (one host sync per call)
+        st_host = torch.stack((status.reshape(()), h_status.reshape(()))).tolist()     # gptq.py:194-196 (one host sync per call)
+        _raise_status(int(st_host[0]) | (int(st_host[1]) << 8))
     out_params = {'scale': _out(params['scale'], as_np), 'zero': _out(params['zero'], as_np),
                   'maxq': params['maxq']}
     extras = ()
@@ -587,6 +612,9 @@ def gptq_many(jobs, block_size=128, actorder=False, damping=0.01, bits=4, pack=T
       that take turns (the HBM-bound operand split of one linear overlaps the tensor-core kernel of the
       previous one) and the compute streams get the higher priority, so that the many short kernels of
       the latency-bound parts are placed first whenever an SM frees up;
+    * jobs fed by the very same calibration batches (the same arrays: q/k/v projections, gate/up
+      projections) share one Hessian: it is accumulated once, kept, and copied to each of them (with
+      `hessian_stream`; the reference accumulates it once per matmul, quantize_interpreter.py:200-226);
     * the NaN / not-positive-definite status words are read once, after all jobs were issued.
 
     `out_host`, if given, is a list of ``(packed, scale, zero)`` pinned host tensors that receive
@@ -606,6 +634,7 @@ def gptq_many(jobs, block_size=128, actorder=False, damping=0.01, bits=4, pack=T
                  'workers': [torch.cuda.Stream(priority=-1 if hessian_stream else 0) for _ in range(nw)],
                  'hstreams': [torch.cuda.Stream(priority=0) for _ in range(2)] if hessian_stream else None,
                  'harenas': [_Arena(), _Arena()],
+                 'keep': _Arena(),
                  'arenas': [_Arena() for _ in range(nw)]}
         _arena_cache[key] = state
     copier, workers, arenas, hstreams = state['copier'], state['workers'], state['arenas'], state['hstreams']
@@ -618,12 +647,13 @@ def gptq_many(jobs, block_size=128, actorder=False, damping=0.01, bits=4, pack=T
         w.wait_event(start)          # inputs produced on the caller's stream are complete for every stream used here
     done = [None] * nw               # completion event of the last job issued on each worker
 
-    def stage(job, wi):
+    def stage(job, wi, need_x=True):
         """Device copies of a job's inputs.  Host inputs are copied on the copy stream into the
-        worker's arena (after the worker's previous job, which used the same buffers, has finished)."""
+        worker's arena (after the worker's previous job, which used the same buffers, has finished).
+        `need_x` False: the job takes its Hessian from another job with the same batches, only W is staged."""
         W, xs = job
         arena = arenas[wi]
-        xs = list(xs)
+        xs = list(xs) if need_x else []
         w_host = not (isinstance(W, torch.Tensor) and W.is_cuda)
         on_host = [not (isinstance(x, torch.Tensor) and x.is_cuda) for x in xs]
         x_host = bool(xs) and all(on_host)
@@ -678,17 +708,52 @@ def gptq_many(jobs, block_size=128, actorder=False, damping=0.01, bits=4, pack=T
     owner = [0] * len(jobs)
     # issue order: with a Hessian stream the expensive jobs go first, so that their long sequential
     # parts run beside the remaining Hessian GEMMs instead of after them
-    order = sorted(range(len(jobs)), key=lambda i: -cost(jobs[i])) if hstream is not None else list(range(len(jobs)))
+    # Jobs with identical calibration batches form a group (one Hessian); groups are issued together.
+    def xkey(job):
+        parts = []
+        for x in job[1]:
+            if isinstance(x, torch.Tensor):
+                parts.append((x.device.type, x.data_ptr(), tuple(x.shape), tuple(x.stride()), x.dtype))
+            elif isinstance(x, np.ndarray):
+                parts.append(('np', x.__array_interface__['data'][0], x.shape, x.strides, x.dtype.str))
+            else:
+                return None
+        return tuple(parts) if parts else None
+    group_of, members = [None] * len(jobs), {}
+    if hstream is not None:
+        for i, job in enumerate(jobs):
+            k = xkey(job)
+            if k is not None:
+                members.setdefault((k, int(job[0].shape[0])), []).append(i)
+        for g in members.values():
+            if len(g) > 1:
+                for i in g:
+                    group_of[i] = g
+    if hstream is not None:
+        gcost = lambda i: max(cost(jobs[j]) for j in group_of[i]) if group_of[i] else cost(jobs[i])
+        gfirst = lambda i: group_of[i][0] if group_of[i] else i
+        order = sorted(range(len(jobs)), key=lambda i: (-gcost(i), gfirst(i), -cost(jobs[i]), i))
+    else:
+        order = list(range(len(jobs)))
     for i in order:
         wi = min(range(nw), key=lambda j: (load[j], j))
         owner[i] = wi
         load[wi] += cost(jobs[i])
+    leader = {}                      # id(group) -> the first job of the group in issue order
+    for i in order:
+        if group_of[i] is not None:
+            leader.setdefault(id(group_of[i]), i)
+    is_follower = lambda i: group_of[i] is not None and leader[id(group_of[i])] != i
+    keep = state['keep']
+    keep_users = [[], []]            # events of the copies that still read each kept Hessian
+    keep_ready = {}                  # id(group) -> (kept H, kept status, event, ring slot)
+    ngroups = 0
     nslots = nw + 2                  # Hessians that may exist at a time (finished or being used)
     slot_free = [None] * nslots
 
     results, deferred = [None] * len(jobs), []
     try:
-        nxt = stage(jobs[order[0]], owner[order[0]])
+        nxt = stage(jobs[order[0]], owner[order[0]], not is_follower(order[0]))
         for pos, i in enumerate(order):
             Wd, xd, ev = nxt
             wi = owner[i]
@@ -706,11 +771,31 @@ def gptq_many(jobs, block_size=128, actorder=False, damping=0.01, bits=4, pack=T
                         hstream.wait_event(slot_free[slot])
                     _ARENA = harena
                     try:
-                        K = int(_to_dev(xd[0]).shape[-1])
-                        hs = harena.get(f'hstatus{slot}', (1,), torch.int32, zero=True)
-                        Hbuf = harena.get(f'H{slot}', (K, K), torch.float32, zero=True)
-                        Hd, n = _accumulate_raw(xd, H=Hbuf, status=hs)
-                        Hd = _finalize_H(Hd, n)
+                        K = int(jobs[i][0].shape[0])
+                        grp = group_of[i]
+                        hs = harena.get(f'hstatus{slot}', (1,), torch.int32, zero=grp is None)
+                        Hbuf = harena.get(f'H{slot}', (K, K), torch.float32, zero=grp is None)
+                        if grp is None:
+                            Hd, n = _accumulate_raw(xd, H=Hbuf, status=hs)
+                            Hd = _finalize_H(Hd, n)
+                        else:
+                            if leader[id(grp)] == i:
+                                ring = ngroups % 2
+                                ngroups += 1
+                                for e in keep_users[ring]:
+                                    hstream.wait_event(e)      # the copies out of this kept buffer are done
+                                keep_users[ring] = []
+                                hk = keep.get(f'hstatus{ring}', (1,), torch.int32, zero=True)
+                                Hk = keep.get(f'H{ring}', (K, K), torch.float32, zero=True)
+                                Hk, n = _accumulate_raw(xd, H=Hk, status=hk)
+                                Hk = _finalize_H(Hk, n)
+                                keep_ready[id(grp)] = (Hk, hk, hstream.record_event(), ring)
+                            Hk, hk, ev_keep, ring = keep_ready[id(grp)]
+                            hstream.wait_event(ev_keep)
+                            Hbuf.copy_(Hk)                     # damp + inverse destroys its Hessian: every job gets its own
+                            hs.copy_(hk)
+                            keep_users[ring].append(hstream.record_event())
+                            Hd = Hbuf
                     finally:
                         _ARENA = None
                     hess = (Hd, hs, hstream.record_event())
@@ -746,7 +831,7 @@ def gptq_many(jobs, block_size=128, actorder=False, damping=0.01, bits=4, pack=T
             results[i] = res
             if pos + 1 < len(order):
                 j = order[pos + 1]
-                nxt = stage(jobs[j], owner[j])
+                nxt = stage(jobs[j], owner[j], not is_follower(j))
     finally:
         _ARENA = None
     for w in workers:
@@ -759,9 +844,9 @@ def gptq_many(jobs, block_size=128, actorder=False, damping=0.01, bits=4, pack=T
         _issued_hook()                   # every launch of the call has been issued; nothing has been waited for
     st = 0
     if deferred:                         # the words are bit sets: OR them (synchronises with every worker)
-        for w in torch.stack(deferred).reshape(-1).tolist():
-            st |= int(w)
-    for a in arenas + harenas:
+        for w, hw in torch.stack(deferred).tolist():           # (stage status, Hessian status) per job
+            st |= int(w) | (int(hw) << 8)
+    for a in arenas + harenas + [keep]:
         a.release()
     _raise_status(st)
     return results

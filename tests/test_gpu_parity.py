@@ -376,6 +376,28 @@ def test_gptq_correlated_activations(G):
     print(f'correlated: identical codes {same:.6f}, recon rel diff {rel:.2e}')
 
 
+@pytest.mark.parametrize('K,N', [(96, 40), (768, 909), (1024, 16)])
+def test_actorder_gathers_equal_indexing(G, K, N):
+    """gptq.py:170-180 as kernels: H[perm][:, perm] in one pass, row gathers of fp32 / bf16 / uint8 rows."""
+    from jax_gptq_b200 import _lib
+    lib, check = _lib.lib, _lib.check
+    g = torch.Generator(device='cuda').manual_seed(K + N)
+    H = torch.randn((K, K), generator=g, device='cuda')
+    perm = torch.randperm(K, generator=g, device='cuda')
+    out = torch.empty_like(H)
+    s = torch.cuda.current_stream().cuda_stream
+    check(lib.jgq_permute_sym(H.data_ptr(), K, perm.data_ptr(), out.data_ptr(), s))
+    assert torch.equal(out, H[perm][:, perm])
+    for t in (torch.randn((K, N), generator=g, device='cuda'),
+              torch.randn((K, N), generator=g, device='cuda').bfloat16(),
+              torch.randint(0, 16, (K, N), generator=g, device='cuda', dtype=torch.uint8)):
+        dst = torch.empty_like(t)
+        check(lib.jgq_gather_rows(t.data_ptr(), K, N * t.element_size(), perm.data_ptr(), dst.data_ptr(), s))
+        assert torch.equal(dst, t[perm])
+    assert lib.jgq_gather_rows(H.data_ptr(), K, K * 4, perm.data_ptr(), H.data_ptr(), s) == -1      # in place: refused
+    assert lib.jgq_gather_rows(None, 0, 16, None, None, s) == 0                                       # nothing to do
+
+
 def test_gptq_actorder_and_3bit(G):
     rng = np.random.default_rng(52)
     W = rng.standard_normal((256, 96)).astype(np.float32)
@@ -703,6 +725,43 @@ def test_gptq_many_actorder_and_bits(G):
             for a, b in zip(got, seq):
                 assert torch.equal(a.int_weight, b.int_weight)
                 assert torch.equal(a.scale, b.scale) and torch.equal(a.zero, b.zero)
+
+
+def test_gptq_many_shares_hessians_of_identical_inputs(G):
+    """Linears fed by the very same batches (q/k/v, gate/up) get one Hessian accumulation; every one of them
+    still returns what a call of its own returns, for device- and host-resident batches, several times over
+    (kept buffers are recycled between groups)."""
+    from jax_gptq_b200 import _lib
+    rng = np.random.default_rng(321)
+    groups = []
+    for K, Ns in [(256, (96, 64, 160)), (128, (80, 48)), (384, (64, 64)), (256, (32,))]:
+        # one batch per group: staged host batches are merged into one kernel call, which sums in another order
+        xs = [(rng.standard_normal((768, K)) * np.linspace(0.5, 2.0, K)).astype(np.float32)]
+        groups.append((xs, [(0.02 * rng.standard_normal((K, N))).astype(np.float32) for N in Ns]))
+    seq, jobs_dev, jobs_host = [], [], []
+    for xs, Ws in groups:
+        xd = [dev(x) for x in xs]
+        xh = [torch.from_numpy(x).pin_memory() for x in xs]
+        for W in Ws:
+            Q, p = G.gptq(dev(W), xd, block_size=64)
+            seq.append(G.pack_matrix(Q, p))
+            jobs_dev.append((dev(W), xd))
+            jobs_host.append((torch.from_numpy(W).pin_memory(), xh))
+    for jobs in (jobs_dev, jobs_host):
+        for streams in (2, 5):
+            l0 = _lib.lib.jgq_launch_count()
+            got = G.gptq_many(jobs, block_size=64, streams=streams)
+            torch.cuda.synchronize()
+            shared = _lib.lib.jgq_launch_count() - l0
+            for a, b in zip(got, seq):
+                assert torch.equal(a.int_weight, b.int_weight)
+                assert torch.equal(a.scale, b.scale) and torch.equal(a.zero, b.zero)
+    # the same jobs with private copies of the batches accumulate eight Hessians instead of four
+    private = [(W, [x.clone() for x in xs]) for W, xs in jobs_dev]
+    l0 = _lib.lib.jgq_launch_count()
+    G.gptq_many(private, block_size=64, streams=5)
+    torch.cuda.synchronize()
+    assert _lib.lib.jgq_launch_count() - l0 > shared
 
 
 def test_gptq_many_matches_sequential(G):
