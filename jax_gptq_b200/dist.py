@@ -52,6 +52,10 @@ def assign_layers(costs, world):
     return owner
 
 
+def _raw_stream():
+    return torch._C._cuda_getCurrentRawStream(torch.cuda.current_device())
+
+
 def pack_lower(H_sum, out=None):
     """The tiles on or below the diagonal of a raw K x K sum (all that carries data before finalize) as one
     contiguous fp32 vector: what has to travel in the all-reduce.  CUDA tensors only."""
@@ -60,14 +64,14 @@ def pack_lower(H_sum, out=None):
     n = lib.jgq_hessian_lower_elems(K)
     if out is None:
         out = torch.zeros(n, dtype=torch.float32, device=H_sum.device)
-    check(lib.jgq_hessian_pack_lower(H_sum.data_ptr(), K, out.data_ptr(), torch.cuda.current_stream().cuda_stream))
+    check(lib.jgq_hessian_pack_lower(H_sum.data_ptr(), K, out.data_ptr(), _raw_stream()))
     return out
 
 
 def unpack_lower(packed, H_sum):
     from ._lib import lib, check
     K = H_sum.shape[0]
-    check(lib.jgq_hessian_unpack_lower(packed.data_ptr(), K, H_sum.data_ptr(), torch.cuda.current_stream().cuda_stream))
+    check(lib.jgq_hessian_unpack_lower(packed.data_ptr(), K, H_sum.data_ptr(), _raw_stream()))
     return H_sum
 
 

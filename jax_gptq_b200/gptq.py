@@ -23,7 +23,8 @@ _MAX_HESSIAN_SCRATCH = 1 << 30   # calibration batches are fed in row chunks who
 # plumbing
 # --------------------------------------------------------------------------
 def _stream():
-    return torch.cuda.current_stream().cuda_stream
+    # the raw handle of torch's current stream (the Stream object costs ten times the lookup)
+    return torch._C._cuda_getCurrentRawStream(torch.cuda.current_device())
 
 
 def _dev():
@@ -75,28 +76,43 @@ def _workspace(nbytes, zeroed=False, tag='ws'):
     return buf
 
 
+_ELEMENT_SIZE = {torch.float32: 4, torch.float64: 8, torch.float16: 2, torch.bfloat16: 2, torch.uint8: 1,
+                 torch.int8: 1, torch.int16: 2, torch.int32: 4, torch.int64: 8, torch.bool: 1}
+
+
 class _Arena:
     """Named, grow-only device buffers for the temporaries of one compute stream.  While an arena
     is active (`gptq_many`), the temporaries of `gptq` come from it instead of the allocator, so
     a steady stream of jobs performs no device allocation at all.  Outgrown buffers are kept
-    until `release()` (called after a device synchronisation)."""
+    until `release()` (called after a device synchronisation).  The typed views handed out are
+    cached per (name, shape, dtype): a job loop asks for the same ones over and over."""
 
     def __init__(self):
         self.bufs = {}
+        self.views = {}
         self.old = []
 
     def get(self, tag, shape, dtype, zero=False):
-        n = 1
-        for d in shape:
-            n *= int(d)
-        nbytes = max(n * torch.empty((), dtype=dtype).element_size(), 16)
-        buf = self.bufs.get(tag)
-        if buf is None or buf.numel() < nbytes:
-            if buf is not None:
-                self.old.append(buf)
-            buf = torch.empty(int(nbytes * 1.25) + 256, dtype=torch.uint8, device=_dev())
-            self.bufs[tag] = buf
-        t = buf[:nbytes].view(dtype)[:n].view(*shape) if n else torch.empty(shape, dtype=dtype, device=_dev())
+        if type(shape) is not tuple:
+            shape = tuple(int(d) for d in shape)
+        views = self.views.get(tag)
+        t = views.get((shape, dtype)) if views is not None else None
+        if t is None:
+            n = 1
+            for d in shape:
+                n *= int(d)
+            nbytes = max(n * _ELEMENT_SIZE[dtype], 16)
+            buf = self.bufs.get(tag)
+            if buf is None or buf.numel() < nbytes:
+                if buf is not None:
+                    self.old.append(buf)
+                buf = torch.empty(int(nbytes * 1.25) + 256, dtype=torch.uint8, device=_dev())
+                self.bufs[tag] = buf
+                self.views[tag] = views = {}          # views of the outgrown buffer are not handed out again
+            elif views is None:
+                self.views[tag] = views = {}
+            t = buf[:nbytes].view(dtype)[:n].view(*shape) if n else torch.empty(shape, dtype=dtype, device=_dev())
+            views[(shape, dtype)] = t
         if zero:
             t.zero_()
         return t
