@@ -873,6 +873,13 @@ def bench_w4(torch, G, dev, peaks, cases=None, no_settled=False):
     gen = torch.Generator(device=dev).manual_seed(3003)
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     shapes = ((4096, 4096), (4096, 11008), (11008, 4096), (8192, 28672))
+    ref_us = {}       # the reference's Triton kernel on a B200, recorded by tests/golden/make_kernel_golden.py
+    try:
+        for r in json.load(open(os.path.join(ROOT, 'tests', 'golden', 'triton_ref_times.json')))['rows']:
+            ref_us[(r['K'], r['N'], r['M'])] = r['triton_ref_us']
+    except (OSError, ValueError, KeyError):
+        pass
+    from jax_gptq_b200 import _lib
     if cases:
         shapes = tuple(dict.fromkeys((k, n) for k, n, _ in cases))
     for K, N in shapes:
@@ -930,7 +937,30 @@ def bench_w4(torch, G, dev, peaks, cases=None, no_settled=False):
             gbs = bytes_alg / (ms * 1e-3) / 1e9
             tflops = 2.0 * M * K * N / (ms * 1e-3) / 1e12
             rows.append({'K': K, 'N': N, 'M': M, 'us': ms * 1e3, 'us_host_loop': ms_loop * 1e3, 'GBps': gbs, 'hbm_frac': gbs / hbm,
-                        'TFLOPs': tflops, 'tensor_frac': tflops / tf})
+                        'TFLOPs': tflops, 'tensor_frac': tflops / tf, 'triton_ref_us': ref_us.get((K, N, M))})
+        if not cases:
+            # the backward product x (M x N) @ W^T -> (M x K), M = 2048 (kernel.py:142-253)
+            M = 2048
+            xt = torch.randn((M, N), generator=gen, device=dev).half()
+            need = _lib.lib.jgq_w4_matmul_workspace_bytes(M, N, K, _lib.W4_TRANSPOSE_B)
+            ws = torch.zeros(max(need, 1), dtype=torch.uint8, device=dev)
+            out = torch.empty((M, K), dtype=torch.float16, device=dev)
+            st = torch.cuda.current_stream().cuda_stream
+            def launch_t(i):
+                _lib.check(_lib.lib.jgq_w4_matmul(xt.data_ptr(), _lib.F16, packed[i % nbuf].data_ptr(), zero.data_ptr(),
+                                                  scale.data_ptr(), _lib.F16, out.data_ptr(), M, N, K, _lib.W4_TRANSPOSE_B,
+                                                  ws.data_ptr(), need, st))
+            for i in range(2):
+                launch_t(i)
+            torch.cuda.synchronize()
+            e0.record()
+            for i in range(3):
+                launch_t(i)
+            e1.record()
+            torch.cuda.synchronize()
+            ms = e0.elapsed_time(e1) / 3
+            tflops = 2.0 * M * K * N / (ms * 1e-3) / 1e12
+            rows.append({'K': K, 'N': N, 'M': M, 'transpose_b': True, 'us': ms * 1e3, 'TFLOPs': tflops, 'tensor_frac': tflops / tf})
         del packed, qms
         torch.cuda.empty_cache()
     return rows

@@ -1,4 +1,4 @@
-// Packed-int4 forward matmul for a handful of f16 token rows (M <= 8): the decode kernel.
+// Packed-int4 forward matmul for a handful of f16 token rows (M <= 16): the decode kernel.
 //
 // HBM-bound: every packed byte is read once, by TMA, in 128-byte-row boxes (128 output channels
 // wide, GV_ROWS byte rows deep) written with the 128-byte swizzle; each CTA keeps GV_NST boxes in
@@ -47,7 +47,7 @@ namespace jgq {
 constexpr int GV_NST = 3;                      // boxes in flight per CTA
 constexpr int GV_THREADS = WWARPS * 32;
 constexpr int GV_TICKET_BYTES = W4_TICKET_REGION;   // one ticket per (channel group, warp): 1024 groups
-constexpr int GV_XS_TOKENS = 8;                // sum_k x slots per slice
+constexpr int GV_XS_TOKENS = 16;               // sum_k x slots per slice
 
 struct GemvParams {
   const __half* x; const void* zero; const void* scale; __half* out;
@@ -84,9 +84,10 @@ __device__ __forceinline__ void mma_f16(float (&d)[4], uint32_t a0, uint32_t a1,
                : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
-// NT: token rows staged per warp (1, 2, 4 or 8 >= M).  ROWS: byte rows per stage (64 or 128).
+// NT: token rows staged per warp (1, 2, 4, 8 or 16 >= M); the MMA's n dimension holds eight of them, sixteen
+// rows are two such groups fed from the same expanded weights.  ROWS: byte rows per stage (64 or 128).
 template <int NT, int ROWS, typename ZST>
-__global__ void __launch_bounds__(GV_THREADS, NT <= 2 ? 4 : 3)
+__global__ void __launch_bounds__(GV_THREADS, NT <= 2 ? 4 : (NT <= 8 ? 3 : 2))
 w4_gemv_kernel(const __grid_constant__ CUtensorMap wmap, const GemvParams p) {
   using namespace umma;
   constexpr int STAGE_BYTES = ROWS * WCOLS;
@@ -142,17 +143,25 @@ w4_gemv_kernel(const __grid_constant__ CUtensorMap wmap, const GemvParams p) {
   if (!p.early && threadIdx.x == 0)
     for (int j = 0; j < GV_NST && j < nstage; ++j) issue_stage(j);
 
-  float acc[2][4], accx[4];
+  constexpr int NG = NT > 8 ? 2 : 1;             // groups of eight token rows
+  float acc[NG][2][4], accx[NG][4];
   auto clear_acc = [&]() {
 #pragma unroll
-    for (int i = 0; i < 4; ++i) { acc[0][i] = 0.f; acc[1][i] = 0.f; accx[i] = 0.f; }
+    for (int q = 0; q < NG; ++q)
+#pragma unroll
+      for (int i = 0; i < 4; ++i) { acc[q][0][i] = 0.f; acc[q][1][i] = 0.f; accx[q][i] = 0.f; }
   };
   clear_acc();
 
   const uint32_t ring_u32 = smem_u32(ring);
   const uint32_t xs_warp = smem_u32(xs_all) + warp * XWARP;
-  // this lane's operand pairs: token row g when present, else the row of zeros
-  const uint32_t xs_read = (g < p.M && g < NT ? xs_warp + g * XROW : smem_u32(xs_all) + WWARPS * XWARP) + t * 8;
+  // this lane's operand pairs: token row g (+ 8 in the second group) when present, else the row of zeros
+  uint32_t xs_read[NG];
+#pragma unroll
+  for (int q = 0; q < NG; ++q) {
+    const int row = g + 8 * q;
+    xs_read[q] = (row < p.M && row < NT ? xs_warp + row * XROW : smem_u32(xs_all) + WWARPS * XWARP) + t * 8;
+  }
   // byte rows 8*sl + 2t and + 1 of a step, 32-bit word of channels 32*warp + 4g .. + 3; the 16-byte chunk
   // index is xor-ed with (row & 7) by the swizzle, and row & 7 does not depend on the step
   const uint32_t chunk = 2 * warp + (g >> 2), inchunk = 4 * (g & 3);
@@ -199,12 +208,17 @@ w4_gemv_kernel(const __grid_constant__ CUtensorMap wmap, const GemvParams p) {
       for (int sl = 0; sl < STEPS; ++sl) {
         const uint32_t w1 = lds32(tile + sl * (8 * WCOLS) + off0);
         const uint32_t w2 = lds32(tile + sl * (8 * WCOLS) + off1);
-        const uint2 xb = lds64(xs_read + sl * 32);
         const uint32_t p0 = __byte_perm(w1, w2, 0x4400), p1 = __byte_perm(w1, w2, 0x5511);
         const uint32_t p2 = __byte_perm(w1, w2, 0x6622), p3 = __byte_perm(w1, w2, 0x7733);
-        mma_f16(acc[0], p0 & 0x000F000Fu, p1 & 0x000F000Fu, p0 & 0x00F000F0u, p1 & 0x00F000F0u, xb.x, xb.y);
-        mma_f16(acc[1], p2 & 0x000F000Fu, p3 & 0x000F000Fu, p2 & 0x00F000F0u, p3 & 0x00F000F0u, xb.x, xb.y);
-        mma_f16(accx, ones_lo, ones_lo, ones_hi, ones_hi, xb.x, xb.y);
+        const uint32_t a00 = p0 & 0x000F000Fu, a01 = p1 & 0x000F000Fu, a02 = p0 & 0x00F000F0u, a03 = p1 & 0x00F000F0u;
+        const uint32_t a10 = p2 & 0x000F000Fu, a11 = p3 & 0x000F000Fu, a12 = p2 & 0x00F000F0u, a13 = p3 & 0x00F000F0u;
+#pragma unroll
+        for (int q = 0; q < NG; ++q) {
+          const uint2 xb = lds64(xs_read[q] + sl * 32);
+          mma_f16(acc[q][0], a00, a01, a02, a03, xb.x, xb.y);
+          mma_f16(acc[q][1], a10, a11, a12, a13, xb.x, xb.y);
+          mma_f16(accx[q], ones_lo, ones_lo, ones_hi, ones_hi, xb.x, xb.y);
+        }
       }
       __syncwarp();
       if (lane == 0) {
@@ -234,26 +248,30 @@ w4_gemv_kernel(const __grid_constant__ CUtensorMap wmap, const GemvParams p) {
     const int last_c = gemv_cta_of((int64_t)(cg + 1) * p.spc - 1, p.S, p.G);
     const int ncontrib = last_c - first_c + 1;
     const float poison = (alive && !*abort_flag) ? 0.f : __int_as_float(0x7fc00000);
-    float4 v[2];
-    float xsum[2];
+    float4 v[NG][2];
+    float xsum[NG][2];
 #pragma unroll
-    for (int e = 0; e < 2; ++e) {
-      v[e] = make_float4(acc[0][e] + poison, acc[0][2 + e] + poison, acc[1][e] + poison, acc[1][2 + e] + poison);
-      xsum[e] = accx[e];
-    }
+    for (int q = 0; q < NG; ++q)
+#pragma unroll
+      for (int e = 0; e < 2; ++e) {
+        v[q][e] = make_float4(acc[q][0][e] + poison, acc[q][0][2 + e] + poison, acc[q][1][e] + poison, acc[q][1][2 + e] + poison);
+        xsum[q][e] = accx[q][e];
+      }
     bool write_out = true;
     if (ncontrib > 1) {
       constexpr int SL = NT * 32 + GV_XS_TOKENS;        // floats per (slot, warp): NT token rows x 32 channels, then sum_k x
       float* base = p.partials + ((int64_t)cg * p.maxc * WWARPS + warp) * SL;
       float* mine = base + (int64_t)(blockIdx.x - first_c) * WWARPS * SL;
 #pragma unroll
-      for (int e = 0; e < 2; ++e) {
-        const int tok = 2 * t + e;
-        if (tok < p.M && tok < NT) {
-          *reinterpret_cast<float4*>(mine + tok * 32 + 4 * g) = v[e];
-          if (g == 0) mine[NT * 32 + tok] = xsum[e];
+      for (int q = 0; q < NG; ++q)
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+          const int tok = 8 * q + 2 * t + e;
+          if (tok < p.M && tok < NT) {
+            *reinterpret_cast<float4*>(mine + tok * 32 + 4 * g) = v[q][e];
+            if (g == 0) mine[NT * 32 + tok] = xsum[q][e];
+          }
         }
-      }
       __threadfence();
       __syncwarp();
       int last = 0;
@@ -267,19 +285,21 @@ w4_gemv_kernel(const __grid_constant__ CUtensorMap wmap, const GemvParams p) {
       if (write_out) {
         __threadfence();
 #pragma unroll
-        for (int e = 0; e < 2; ++e) {
-          const int tok = 2 * t + e;
-          v[e] = make_float4(0.f, 0.f, 0.f, 0.f);
-          xsum[e] = 0.f;
-          if (tok < p.M && tok < NT) {
-            for (int zc = 0; zc < ncontrib; ++zc) {            // slices are added in CTA order: deterministic
-              const float* src = base + (int64_t)zc * WWARPS * SL;
-              const float4 a = __ldcg(reinterpret_cast<const float4*>(src + tok * 32 + 4 * g));
-              v[e].x += a.x; v[e].y += a.y; v[e].z += a.z; v[e].w += a.w;
-              xsum[e] += __ldcg(src + NT * 32 + tok);
+        for (int q = 0; q < NG; ++q)
+#pragma unroll
+          for (int e = 0; e < 2; ++e) {
+            const int tok = 8 * q + 2 * t + e;
+            v[q][e] = make_float4(0.f, 0.f, 0.f, 0.f);
+            xsum[q][e] = 0.f;
+            if (tok < p.M && tok < NT) {
+              for (int zc = 0; zc < ncontrib; ++zc) {            // slices are added in CTA order: deterministic
+                const float* src = base + (int64_t)zc * WWARPS * SL;
+                const float4 a = __ldcg(reinterpret_cast<const float4*>(src + tok * 32 + 4 * g));
+                v[q][e].x += a.x; v[q][e].y += a.y; v[q][e].z += a.z; v[q][e].w += a.w;
+                xsum[q][e] += __ldcg(src + NT * 32 + tok);
+              }
             }
           }
-        }
       }
     }
     if (write_out && n0 < p.N) {               // N % 16 == 0: the four channels are inside together
@@ -287,18 +307,20 @@ w4_gemv_kernel(const __grid_constant__ CUtensorMap wmap, const GemvParams p) {
 #pragma unroll
       for (int i = 0; i < 4; ++i) { sc[i] = zs_to_f32<ZST>(p.scale, n0 + i); z[i] = zs_to_f32<ZST>(p.zero, n0 + i); }
 #pragma unroll
-      for (int e = 0; e < 2; ++e) {
-        const int tok = 2 * t + e;
-        if (tok < p.M && tok < NT) {
-          const float o0 = sc[0] * (kUp * v[e].x - z[0] * xsum[e]), o1 = sc[1] * (kUp * v[e].y - z[1] * xsum[e]);
-          const float o2 = sc[2] * (kUp * v[e].z - z[2] * xsum[e]), o3 = sc[3] * (kUp * v[e].w - z[3] * xsum[e]);
-          const __half2 h01 = __floats2half2_rn(o0, o1), h23 = __floats2half2_rn(o2, o3);
-          uint2 pk;
-          pk.x = *reinterpret_cast<const uint32_t*>(&h01);
-          pk.y = *reinterpret_cast<const uint32_t*>(&h23);
-          *reinterpret_cast<uint2*>(p.out + (int64_t)tok * p.N + n0) = pk;
+      for (int q = 0; q < NG; ++q)
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+          const int tok = 8 * q + 2 * t + e;
+          if (tok < p.M && tok < NT) {
+            const float o0 = sc[0] * (kUp * v[q][e].x - z[0] * xsum[q][e]), o1 = sc[1] * (kUp * v[q][e].y - z[1] * xsum[q][e]);
+            const float o2 = sc[2] * (kUp * v[q][e].z - z[2] * xsum[q][e]), o3 = sc[3] * (kUp * v[q][e].w - z[3] * xsum[q][e]);
+            const __half2 h01 = __floats2half2_rn(o0, o1), h23 = __floats2half2_rn(o2, o3);
+            uint2 pk;
+            pk.x = *reinterpret_cast<const uint32_t*>(&h01);
+            pk.y = *reinterpret_cast<const uint32_t*>(&h23);
+            *reinterpret_cast<uint2*>(p.out + (int64_t)tok * p.N + n0) = pk;
+          }
         }
-      }
     }
     clear_acc();
   }
@@ -330,18 +352,18 @@ static int gemv_rows_override() {       // JGQ_GEMV_ROWS=64|128: byte rows per s
 GemvPlan plan_w4_gemv(int64_t M, int64_t N, int64_t K) {
   GemvPlan pl;
   memset(&pl, 0, sizeof(pl));
-  if (M < 1 || M > 8 || N % 16 != 0 || K % 8 != 0) return pl;
+  if (M < 1 || M > 16 || N % 16 != 0 || K % 8 != 0) return pl;
   pl.ncg = (int)cdiv(N, WCOLS);
   if (pl.ncg * WWARPS > GV_TICKET_BYTES / (int)sizeof(int)) return pl;
   pl.use = 1;
-  pl.nt = M <= 1 ? 1 : M <= 2 ? 2 : M <= 4 ? 4 : 8;
+  pl.nt = M <= 1 ? 1 : M <= 2 ? 2 : M <= 4 ? 4 : M <= 8 ? 8 : 16;
   pl.rows = gemv_rows_override() ? gemv_rows_override() : 128;
   pl.spc = (int)cdiv(K / 2, pl.rows);
   pl.S = (int64_t)pl.ncg * pl.spc;
   const int xrow = (pl.rows / 2) * 8 + 32;
   pl.smem_bytes = GV_NST * pl.rows * WCOLS + 1024 + (WWARPS * pl.nt + 1) * xrow;
   const int by_smem = (227 * 1024) / (pl.smem_bytes + 1024 + 128);
-  const int per_sm = std::max(1, std::min(pl.nt <= 2 ? 4 : 3, by_smem));
+  const int per_sm = std::max(1, std::min(pl.nt <= 2 ? 4 : (pl.nt <= 8 ? 3 : 2), by_smem));
   pl.G = (int)std::min<int64_t>(per_sm * (int64_t)sm_count(), std::max<int64_t>(1, pl.S / 2));   // one resident wave
   const int64_t per = pl.S / pl.G;                    // every CTA streams per or per + 1 stages
   pl.maxc = (int)cdiv(pl.spc, per) + 1;
@@ -398,7 +420,7 @@ int launch_w4_gemv(const GemvPlan& pl, const void* x, const uint8_t* packed, con
       return zf ? launch_gemv_inst<NT_, 64, float>(pl, p, wmap, s) : launch_gemv_inst<NT_, 64, __half>(pl, p, wmap, s);   \
     return zf ? launch_gemv_inst<NT_, 128, float>(pl, p, wmap, s) : launch_gemv_inst<NT_, 128, __half>(pl, p, wmap, s);   \
   }
-  JGQ_GEMV(1) JGQ_GEMV(2) JGQ_GEMV(4) JGQ_GEMV(8)
+  JGQ_GEMV(1) JGQ_GEMV(2) JGQ_GEMV(4) JGQ_GEMV(8) JGQ_GEMV(16)
 #undef JGQ_GEMV
   return fail(JGQ_ERR_ARG, "w4_gemv: bad plan");
 }

@@ -33,7 +33,7 @@ size_t w4_tb_workspace_bytes(int64_t M, int64_t N);
 int launch_w4_tb(const void* x, int x_dtype, const uint8_t* packed, const void* zero, const void* scale, int zs_dtype,
                  void* out, int64_t M, int64_t N, int64_t K, void* ws, cudaStream_t s);
 
-// f16 decode kernel for M <= 8 (w4_gemv.cu)
+// f16 decode kernel for M <= 16 (w4_gemv.cu)
 struct GemvPlan {
   int use; int nt; int rows; int ncg; int spc; int64_t S; int G; int maxc;
   size_t part_bytes;     // slices in the workspace (after the ticket region)

@@ -534,7 +534,7 @@ def test_matmul_reference_kernel_shapes(G, M, N, K, transpose):
     _check_mm(G, qm, x, transpose)
 
 
-@pytest.mark.parametrize('M', [1, 2, 8, 16, 17, 40, 300, 600])
+@pytest.mark.parametrize('M', [1, 2, 8, 9, 12, 16, 17, 40, 300, 600])
 @pytest.mark.parametrize('x_dtype', ['float16', 'bfloat16', 'float32'])
 def test_matmul_decode_sizes(G, M, x_dtype):
     rng = np.random.default_rng(70 + M)
