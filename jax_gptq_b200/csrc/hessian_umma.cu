@@ -69,6 +69,7 @@ struct HessParams {
   float* out;              // H (S == 1, accumulated into) or slice buffers (S > 1, overwritten)
   int64_t slice_stride;    // elements between slice buffers
   int32_t* status;
+  int withhold_first_chain;   // test hook: the MMA warp never signals its first finished chain (see launch_hessian_umma)
 };
 
 template <typename T>
@@ -238,7 +239,7 @@ hessian_umma_kernel(const __grid_constant__ CUtensorMap map0, const __grid_const
         first = false;
         if (++st == HT_STAGES) { st = 0; ph ^= 1; sb16 = smem0 >> 4; } else { sb16 += stage16; }
       }
-      if (ok && elect_one()) mma_commit(&accf_bar[b]);    // the chain is complete once its MMAs are
+      if (ok && !(p.withhold_first_chain && c == 0) && elect_one()) mma_commit(&accf_bar[b]);    // the chain is complete once its MMAs are
       __syncwarp();
     }
   } else {
@@ -496,7 +497,7 @@ hessian_pair_kernel(const __grid_constant__ CUtensorMap map0, const __grid_const
           first = false;
           if (++st == HP_STAGES) { st = 0; ph ^= 1; sb16 = smem0 >> 4; } else { sb16 += stage16; }
         }
-        if (ok && elect_one()) {
+        if (ok && !(p.withhold_first_chain && c == 0) && elect_one()) {
           mma_commit_pair(my_accf + (uint32_t)(b * 8));
           mma_commit_pair(peer_accf + (uint32_t)(b * 8));
         }
@@ -643,6 +644,10 @@ int launch_hessian_umma(const HessPlan& pl, const void* X, int x_dtype, int64_t 
   p.out = pl.S > 1 ? part : H;
   p.slice_stride = pl.S > 1 ? K * K : 0;
   p.status = status;
+  // Test hook for the bounded waits: with JGQ_TEST_WITHHOLD_COMMIT set (read at every launch) the MMA warp keeps its
+  // first "chain finished" signal to itself; the waits of every role then run out their budget, the kernel returns
+  // without writing H and reports JGQ_STATUS_TIMEOUT.  Nothing faults and nothing spins without a limit.
+  p.withhold_first_chain = getenv("JGQ_TEST_WITHHOLD_COMMIT") ? 1 : 0;
   if (pl.panel == 256) {
     struct PairAttrTag {};
     once_per_device<PairAttrTag>([]() {

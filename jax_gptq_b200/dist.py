@@ -159,9 +159,10 @@ class ShardedPipeline:
     Per linear, on every rank: Hessian of the local tokens (Hessian stream) -> pack the lower tiles ->
     NCCL reduce to the linear's owner (communication stream, first communicator).  The owner - chosen by a
     greedy longest-job-first assignment that every rank computes identically - unpacks, finalizes with the
-    global token count, damps + inverts, quantizes and packs the whole linear on one of its compute streams,
-    then broadcasts the packed weights (second communication stream, second communicator, so that a broadcast
-    waiting for its quantize loop never holds up the next reduction).  The reduction of linear i overlaps the
+    global token count, damps + inverts, quantizes and packs the whole linear on one of its compute streams
+    and puts the result into its output buffer, which it broadcasts once, after its last linear (second
+    communication stream, second communicator, so that it never holds up a reduction): one collective per
+    rank, not one per linear.  The reduction of linear i overlaps the
     Hessian GEMM of linear i+1 and the sequential stages of the linears before it.  Every rank issues the same
     collectives in the same order.
 
@@ -221,6 +222,29 @@ class ShardedPipeline:
         results, deferred = [None] * len(jobs), []
         self.stats = {'reduce_bytes': 0, 'gather_bytes': 0, 'mode': self.mode if world > 1 else 'single'}
         nmine = 0
+        # Owner mode with `gather`: every owner collects its packed linears (bytes, then scale, then zero) in ONE
+        # buffer laid out identically on all ranks and broadcasts it once, after its last linear - one collective
+        # per rank instead of one per linear (the per-call host cost of a collective is what limits many ranks).
+        flat, place, mine_done = None, {}, []
+        if owner_mode and gather:
+            sizes = [0] * world
+            for i in order:
+                K, N = jobs[i][0].shape
+                o = owners[i]
+                a = sizes[o]
+                b = a + (K // 2) * N
+                b4 = (b + 255) // 256 * 256
+                place[i] = (a, b4, b4 + 4 * N)
+                sizes[o] = (b4 + 8 * N + 255) // 256 * 256
+            flat = [torch.empty(max(sz, 1), dtype=torch.uint8, device='cuda') for sz in sizes]
+            self.stats['gather_bytes'] = sum(sizes)
+
+        def views(i):
+            K, N = jobs[i][0].shape
+            a, bs, bz = place[i]
+            buf = flat[owners[i]]
+            return (buf[a:a + (K // 2) * N].view(K // 2, N), buf[bs:bs + 4 * N].view(torch.float32),
+                    buf[bz:bz + 4 * N].view(torch.float32))
         for pos, i in enumerate(order):
             job = jobs[i]
             W, xs = job[0], job[1]
@@ -281,40 +305,50 @@ class ShardedPipeline:
                     finally:
                         G._ARENA = None
                     packed, scale, zero = qm.int_weight, qm.scale, qm.zero
+                    if flat is not None:
+                        vp, vs, vz = views(i)
+                        vp.copy_(packed)
+                        vs.copy_(scale)
+                        vz.copy_(zero)
                     slot_free[slot] = ws.record_event()
                     ev_q = slot_free[slot]
+                    mine_done.append(ev_q)
             else:
                 slot_free[slot] = ev_r           # the buffers of this slot are free once the reduction has read them
                 ev_q = ev_r
-            if world > 1 and gather:
+            if flat is not None:
+                results[i] = views(i) + ((0, N),)
+            elif world > 1 and gather:
                 with torch.cuda.stream(self.comm_ag):
                     self.comm_ag.wait_event(ev_q)
                     if x_ready is not None:
                         self.comm_ag.wait_event(x_ready)
-                    if owner_mode:
-                        full = packed if mine else torch.empty((K // 2, N), dtype=torch.uint8, device=W.device)
-                        dist.broadcast(full, src=owner, group=self.group_ag)
-                        full.record_stream(self.comm_ag)
-                        self.stats['gather_bytes'] += full.numel()
-                    else:
-                        widths = [shard_range(N, r, world, 16) for r in range(world)]
-                        wmax = max(e - b for b, e in widths)
-                        send = packed
-                        if packed.shape[1] != wmax:
-                            send = torch.zeros((K // 2, wmax), dtype=torch.uint8, device=packed.device)
-                            send[:, :packed.shape[1]] = packed
-                        recv = torch.empty((world, K // 2, wmax), dtype=torch.uint8, device=packed.device)
-                        dist.all_gather_into_tensor(recv, send.contiguous(), group=self.group_ag)
-                        full = torch.cat([recv[r, :, :e - b] for r, (b, e) in enumerate(widths)], dim=1)
-                        for t in (packed, send, recv, full):
-                            t.record_stream(self.comm_ag)
-                        self.stats['gather_bytes'] += recv.numel()
+                    widths = [shard_range(N, r, world, 16) for r in range(world)]
+                    wmax = max(e - b for b, e in widths)
+                    send = packed
+                    if packed.shape[1] != wmax:
+                        send = torch.zeros((K // 2, wmax), dtype=torch.uint8, device=packed.device)
+                        send[:, :packed.shape[1]] = packed
+                    recv = torch.empty((world, K // 2, wmax), dtype=torch.uint8, device=packed.device)
+                    dist.all_gather_into_tensor(recv, send.contiguous(), group=self.group_ag)
+                    full = torch.cat([recv[r, :, :e - b] for r, (b, e) in enumerate(widths)], dim=1)
+                    for t in (packed, send, recv, full):
+                        t.record_stream(self.comm_ag)
+                    self.stats['gather_bytes'] += recv.numel()
                     # scale / zero depend on W alone (gptq.py:105-118): every rank computes all of them
                     Wf = W if W.dtype == torch.float32 else W.float()
                     full_params = G._col_params(Wf.contiguous())
                 results[i] = (full, full_params['scale'], full_params['zero'], (0, N))
             else:
                 results[i] = (packed, scale, zero, (c0, c1))
+        if flat is not None:
+            with torch.cuda.stream(self.comm_ag):
+                for e in mine_done:
+                    self.comm_ag.wait_event(e)
+                for r in range(world):
+                    if flat[r].numel() > 1:
+                        dist.broadcast(flat[r], src=r, group=self.group_ag)
+                        flat[r].record_stream(self.comm_ag)
         for st in self.hstreams + [self.comm_ar, self.comm_ag] + self.workers:
             main.wait_event(st.record_event())
         st_word = 0

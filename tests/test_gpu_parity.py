@@ -186,6 +186,28 @@ def test_accumulate_H_large_split(G):
     assert np.allclose(a, ref, atol=3e-6, rtol=1e-5)
 
 
+@pytest.mark.parametrize('K', [256, 512])        # the single-CTA kernel and the CTA-pair kernel
+def test_hessian_bounded_wait_reports_timeout(G, K, monkeypatch):
+    """Every device-side wait of the tensor-core Hessian kernel has a clock budget.  With the test hook that
+    withholds one barrier signal the waits run out (about two seconds), the kernel returns, the call raises
+    through the status word, and the very next call - same process, same context - is correct again."""
+    import importlib; gg = importlib.import_module('jax_gptq_b200.gptq')
+    g = torch.Generator(device='cuda').manual_seed(5 + K)
+    X = torch.randn((2048, K), generator=g, device='cuda')
+    monkeypatch.setenv('JGQ_TEST_WITHHOLD_COMMIT', '1')
+    with pytest.raises(RuntimeError, match='timed out'):
+        G.accumulate_H([X])
+    monkeypatch.delenv('JGQ_TEST_WITHHOLD_COMMIT')
+    H = G.accumulate_H([X])
+    ref = (X.double().T @ X.double() / X.shape[0])
+    d = torch.sqrt(torch.outer(torch.diagonal(ref), torch.diagonal(ref)))
+    assert float(((H.double() - ref).abs() / d).max()) < 1e-5
+    # and another kernel family still runs in this context
+    W = torch.randn((K, 64), generator=g, device='cuda')
+    p = G.get_col_quantize_params(W)
+    assert bool(torch.isfinite(p['scale']).all())
+
+
 # ------------------------------------------------------- damp + Cholesky inverse ----
 @pytest.mark.parametrize('K', [32, 64, 100, 256, 768, 840, 1536, 3072])      # 840: ragged last panel inside an outer block; 3072: the benchmark's largest
 def test_damp_invert_matches_oracle(G, K):
