@@ -528,7 +528,7 @@ def run_ours(args):
             hi = ((got >> 4) == (ref_packed >> 4)).float().mean()
             same.append(float((lo + hi) / 2))
         sharded = {'collective': 'NCCL reduce (sum, fp32) of the lower block triangle of every Hessian to the linear\'s owner rank, '
-                                 'one per linear; broadcast of the packed weights on a second communicator',
+                                 'one per linear; one broadcast per owner rank of its packed linears (bytes, scale, zero) on a second communicator',
                    'mode': pipe.stats.get('mode'),
                    'reduce_bytes_per_step': pipe.stats['reduce_bytes'], 'broadcast_bytes_per_step': pipe.stats['gather_bytes'],
                    'reduce_ms_alone_per_step': ar_ms, 'reduce_share_of_step': ar_ms / ms_max,
