@@ -77,8 +77,8 @@ struct GemmSmem {
 };
 
 template <bool A_KC, bool B_KC>
-__device__ __forceinline__ void sgemm_body(const GemmParams& p, const int zsplit, GemmSmem& sm) {
-  const int m0 = blockIdx.y * GBM, n0 = blockIdx.x * GBN;
+__device__ __forceinline__ void sgemm_body(const GemmParams& p, const int zsplit, GemmSmem& sm, const int tile_m, const int tile_n) {
+  const int m0 = tile_m * GBM, n0 = tile_n * GBN;
   if (m0 >= p.M || n0 >= p.N) return;
   if (p.tri && n0 > m0 + GBM - 1) return;
   const int kbeg = zsplit * p.k_chunk;
@@ -188,8 +188,8 @@ __device__ __forceinline__ void mma_tf32(float (&d)[4], const uint32_t (&a)[4], 
 }
 
 template <bool A_KC, bool B_KC>
-__device__ __forceinline__ void sgemm_body_tc(const GemmParams& p, const int zsplit, GemmSmem& sm) {
-  const int m0 = blockIdx.y * GBM, n0 = blockIdx.x * GBN;
+__device__ __forceinline__ void sgemm_body_tc(const GemmParams& p, const int zsplit, GemmSmem& sm, const int tile_m, const int tile_n) {
+  const int m0 = tile_m * GBM, n0 = tile_n * GBN;
   if (m0 >= p.M || n0 >= p.N) return;
   if (p.tri && n0 > m0 + GBM - 1) return;
   const int kbeg = zsplit * p.k_chunk;
@@ -289,20 +289,24 @@ template <bool A_KC, bool B_KC>
 __global__ void __launch_bounds__(GTHREADS, 2)
 sgemm_kernel(const GemmParams p) {
   __shared__ __align__(16) GemmSmem sm;
-  if (p.tc) sgemm_body_tc<A_KC, B_KC>(p, blockIdx.z, sm);
-  else      sgemm_body<A_KC, B_KC>(p, blockIdx.z, sm);
+  if (p.tc) sgemm_body_tc<A_KC, B_KC>(p, blockIdx.z, sm, blockIdx.y, blockIdx.x);
+  else      sgemm_body<A_KC, B_KC>(p, blockIdx.z, sm, blockIdx.y, blockIdx.x);
 }
 
-// Two independent products in one launch (blockIdx.z selects the problem); A has the
-// contraction index contiguous in both, B's layout is a per-problem flag.
-struct GemmDualParams { GemmParams p[2]; int b_kc[2]; };
+// Two independent products in one launch; A has the contraction index contiguous in both, B's layout
+// is a per-problem flag.  The grid is the plain list of both problems' tiles (the first problem's
+// first): the two shapes are typically a tall strip and a wide strip, and a common 2-D grid over
+// both would be mostly CTAs with nothing to do.
+struct GemmDualParams { GemmParams p[2]; int b_kc[2]; int tiles0; int tn[2]; };
 
 static __global__ void __launch_bounds__(GTHREADS, 2)
 sgemm_dual_kernel(const GemmDualParams dp) {
   __shared__ __align__(16) GemmSmem sm;
-  const int z = blockIdx.z;
-  if (dp.b_kc[z]) sgemm_body<true, true>(dp.p[z], 0, sm);
-  else            sgemm_body<true, false>(dp.p[z], 0, sm);
+  const int z = (int)blockIdx.x >= dp.tiles0 ? 1 : 0;
+  const int t = (int)blockIdx.x - (z ? dp.tiles0 : 0);
+  const int tile_m = t / dp.tn[z], tile_n = t % dp.tn[z];
+  if (dp.b_kc[z]) sgemm_body<true, true>(dp.p[z], 0, sm, tile_m, tile_n);
+  else            sgemm_body<true, false>(dp.p[z], 0, sm, tile_m, tile_n);
 }
 
 // Host-side launcher.  `splits` > 1 slices the contraction range over blockIdx.z,
@@ -324,11 +328,17 @@ inline GemmParams make_gemm_params(const float* A, int64_t lda, const float* B, 
 inline int launch_sgemm_dual(const GemmParams& p0, bool b_kc0, const GemmParams& p1, bool b_kc1, cudaStream_t s) {
   GemmDualParams dp;
   dp.p[0] = p0; dp.p[1] = p1; dp.b_kc[0] = b_kc0; dp.b_kc[1] = b_kc1;
-  const int gx = (int)std::max(cdiv(std::max(p0.N, 0), GBN), cdiv(std::max(p1.N, 0), GBN));
-  const int gy = (int)std::max(cdiv(std::max(p0.M, 0), GBM), cdiv(std::max(p1.M, 0), GBM));
-  if (gx <= 0 || gy <= 0) return JGQ_OK;
+  int tiles[2];
+  const GemmParams* pp[2] = {&p0, &p1};
+  for (int z = 0; z < 2; ++z) {
+    const bool live = pp[z]->M > 0 && pp[z]->N > 0;
+    dp.tn[z] = live ? (int)cdiv(pp[z]->N, GBN) : 1;
+    tiles[z] = live ? (int)cdiv(pp[z]->M, GBM) * dp.tn[z] : 0;
+  }
+  dp.tiles0 = tiles[0];
+  if (tiles[0] + tiles[1] <= 0) return JGQ_OK;
   prefer_shared_carveout<sgemm_dual_kernel>();
-  sgemm_dual_kernel<<<dim3((unsigned)gx, (unsigned)gy, 2), GTHREADS, 0, s>>>(dp);
+  sgemm_dual_kernel<<<(unsigned)(tiles[0] + tiles[1]), GTHREADS, 0, s>>>(dp);
   return check_launch("sgemm_dual");
 }
 
