@@ -477,6 +477,8 @@ def run_ours(args):
     # ---- N > 1: one model, tokens sharded over the ranks (strong scaling) ----
     replicas = None
     sharded = None
+    layer_parallel = None
+    headline_split = None
     if world > 1:
         from jax_gptq_b200 import dist as D
         replicas = {'value': value, 'unit': UNIT, 'ms_per_step': ms_max, 'scaling': 'weak',
@@ -532,11 +534,51 @@ def run_ours(args):
                    'mode': pipe.stats.get('mode'),
                    'reduce_bytes_per_step': pipe.stats['reduce_bytes'], 'broadcast_bytes_per_step': pipe.stats['gather_bytes'],
                    'reduce_ms_alone_per_step': ar_ms, 'reduce_share_of_step': ar_ms / ms_max,
+                   'host_issue_ms_rank0_last_step': pipe.stats.get('host_issue_ms'),
                    'tokens_per_rank': e - b,
                    'check_same_codes_block0_vs_single_gpu': same,
                    'check_note': 'the sharded Hessian differs from the single-GPU one by fp32 summation order only; on the K = 3072 '
                                  'layer that moves about as many codes as the oracle\'s own rounding floor (see parity)',
                    'check_ok': bool(min(same) >= 0.998)}
+
+        # ---- the other split of one model: linears (not tokens) sharded over the ranks, no Hessian travels ----
+        pipe_l = D.ShardedPipeline(streams=args.streams, mode='layers')
+
+        def full_jobs():
+            return [(weights[name], list(captured[name].chunk(CALIB_BATCHES)))
+                    for weights, captured in zip(model, acts) for name, _, _ in LINEARS]
+
+        def step_layers():
+            return pipe_l.run(full_jobs(), n_tok, block_size=BLOCK_SIZE, damping=DAMP)
+        for _ in range(args.warmup):
+            out_l = step_layers()
+        barrier()
+        launches0 = lib.jgq_launch_count()
+        e0.record()
+        for _ in range(args.steps):
+            out_l = step_layers()
+        e1.record()
+        torch.cuda.synchronize()
+        launches_l = lib.jgq_launch_count() - launches0
+        t = torch.tensor([e0.elapsed_time(e1) / args.steps], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms_layers = float(t.item())
+        same_l = []
+        for j, (name, _, _) in enumerate(LINEARS):          # same tokens, same kernels: the bytes must be the single-GPU ones
+            Q1, p1 = gg.gptq(model[0][name], list(acts[0][name].chunk(CALIB_BATCHES)), block_size=BLOCK_SIZE, damping=DAMP)
+            same_l.append(bool(torch.equal(out_l[j][0], G.pack_matrix(Q1, p1).int_weight)))
+        layer_parallel = {'value': total_weights / (ms_layers * 1e-3), 'unit': UNIT, 'ms_per_step': ms_layers, 'scaling': 'strong',
+                          'what': f'one model on {world} GPUs, every linear quantized entirely by its owner rank from all of its '
+                                  'tokens (activations resident on every rank); the only collectives are the owners\' result '
+                                  'broadcasts', 'broadcast_bytes_per_step': pipe_l.stats['gather_bytes'],
+                          'host_issue_ms_rank0_last_step': pipe_l.stats.get('host_issue_ms'),
+                          'check_block0_bit_identical_to_single_gpu': same_l, 'check_ok': all(same_l)}
+        sharded['value'] = value
+        sharded['ms_per_step'] = ms_max
+        headline_split = 'tokens'
+        if ms_layers < ms_max and all(same_l):
+            # the headline is the faster split of the SAME job (one model, N GPUs); the token split stays under `sharded`
+            value, ms_max, launches, headline_split = layer_parallel['value'], ms_layers, launches_l, 'layers'
 
     # ---- the same work issued one linear at a time, in the order the calibration forward needs the
     # quantized weights (layer l+1's input depends on layer l's result): nothing overlaps ----
@@ -661,8 +703,10 @@ def run_ours(args):
                 'vs_baseline': None, 'dtype': 'f32', 'data': 'synthetic',
                 'config': {'workload': workload_name(layers), 'weights_per_step': total_weights,
                            'l2': 'inputs larger than L2 (each linear reads 0.2-0.8 GB of activations)',
-                           'parallelism': (f'one model on {world} GPUs: calibration tokens sharded, Hessians all-reduced (NCCL), '
-                                           'quantize loop sharded over output channels, packed slabs all-gathered'
+                           'parallelism': ((f'one model on {world} GPUs, both splits measured, headline = the faster one: '
+                                            + ('linears sharded over the ranks (each quantized by its owner from all tokens), results broadcast'
+                                               if headline_split == 'layers' else
+                                               'calibration tokens sharded, Hessians reduced to an owner rank per linear (NCCL), results broadcast'))
                                            if world > 1 else 'one GPU'),
                            'linears_in_flight_per_gpu': args.streams,
                            'resident_activation_bytes_per_gpu': acts_dev_bytes, 'setup_seconds': setup_s},
@@ -672,7 +716,8 @@ def run_ours(args):
                 'value_note': 'the 48 linears are issued as independent jobs (calibration inputs captured beforehand); '
                               'ms_per_step_one_linear_at_a_time is the same work with nothing overlapped, the order a '
                               'calibration forward with quantized weights in place imposes',
-                'parity': parity, 'replicas': replicas, 'sharded': sharded, 'w4_matmul_sharded': w4_sharded}
+                'parity': parity, 'replicas': replicas, 'sharded': sharded, 'layer_parallel': layer_parallel,
+                'w4_matmul_sharded': w4_sharded}
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()

@@ -169,7 +169,13 @@ class ShardedPipeline:
     `mode='columns'` is the other split the path offers: an all-reduce, a replicated inverse on every rank,
     the quantize loop sharded over output channels, an all-gather of the packed slabs.  It has no idle
     ranks for a single linear but repeats the inverse N times; `mode='owner'` divides all the sequential
-    work by N as soon as there are several linears."""
+    work by N as soon as there are several linears.
+
+    `mode='layers'` shards the LINEARS instead of the tokens: every linear is quantized entirely by its
+    owner rank (`gptq_many` on the owner's subset, with all of that linear's calibration tokens, which
+    every rank passes or at least its owner does), no Hessian travels, and the only collectives are the
+    owners' result broadcasts.  For a model of many small linears this is the faster split - a Hessian over
+    1/N of the tokens keeps its fixed costs - while a single large linear needs the token split."""
 
     def __init__(self, streams=6, group=None, mode='owner'):
         self.rank, self.world = _world(group)
@@ -195,6 +201,66 @@ class ShardedPipeline:
             t.zero_()
         return t
 
+    def _run_layers(self, jobs, block_size, damping, bits, gather):
+        """Linears sharded over the ranks: this rank quantizes the ones it owns, from all their tokens."""
+        from . import gptq as G
+        import time
+        t_begin = time.perf_counter()
+        world, rank = self.world, self.rank
+        # a linear costs its Hessian (K^2 n) plus its sequential stages (K^2 (K + N)), in comparable units
+        def cost(j):
+            K, N = j[0].shape
+            n = sum(int(x.shape[0]) if x.dim() == 2 else int(x.numel() // x.shape[-1]) for x in j[1]) if j[1] else 0
+            return float(K) * K * (0.07 * n + K + N) + 1e7        # measured: a token of the Hessian weighs ~0.07 of a (K + N) unit
+        owners = assign_layers([cost(j) for j in jobs], world)
+        mine = [i for i in range(len(jobs)) if owners[i] == rank]
+        failure = None
+        try:
+            got = G.gptq_many([(jobs[i][0], jobs[i][1]) for i in mine], block_size=block_size, damping=damping, bits=bits,
+                              pack=True, streams=len(self.workers))
+        except (ValueError, RuntimeError) as e:      # a failure on one rank is everybody's (the others would wait forever)
+            failure, got = e, []
+        flag = torch.tensor([1 if failure is not None else 0], dtype=torch.int32, device='cuda')
+        dist.all_reduce(flag, op=dist.ReduceOp.MAX, group=self.group_ar)
+        if int(flag.item()):
+            raise failure if failure is not None else ValueError('NaN when computing Hinv on another rank. Features NaN?')
+        self.stats = {'reduce_bytes': 0, 'gather_bytes': 0, 'mode': 'layers'}
+        results = [None] * len(jobs)
+        for i, qm in zip(mine, got):
+            K, N = jobs[i][0].shape
+            results[i] = (qm.int_weight, qm.scale, qm.zero, (0, N))
+        if gather:
+            # one buffer per owner (packed bytes, scale, zero of its linears), the same layout on every rank
+            sizes, place = [0] * world, {}
+            for i, j in enumerate(jobs):
+                K, N = j[0].shape
+                o = owners[i]
+                a = sizes[o]
+                b4 = (a + (K // 2) * N + 255) // 256 * 256
+                place[i] = (a, b4, b4 + 4 * N)
+                sizes[o] = (b4 + 8 * N + 255) // 256 * 256
+            flat = [torch.empty(max(sz, 1), dtype=torch.uint8, device='cuda') for sz in sizes]
+            self.stats['gather_bytes'] = sum(sizes)
+
+            def views(i):
+                K, N = jobs[i][0].shape
+                a, bs, bz = place[i]
+                buf = flat[owners[i]]
+                return (buf[a:a + (K // 2) * N].view(K // 2, N), buf[bs:bs + 4 * N].view(torch.float32),
+                        buf[bz:bz + 4 * N].view(torch.float32))
+            for i in mine:
+                vp, vs, vz = views(i)
+                vp.copy_(results[i][0])
+                vs.copy_(results[i][1])
+                vz.copy_(results[i][2])
+            for r in range(world):
+                if sizes[r] > 0:
+                    dist.broadcast(flat[r], src=r, group=self.group_ag)
+            for i in range(len(jobs)):
+                results[i] = views(i) + ((0, jobs[i][0].shape[1]),)
+        self.stats['host_issue_ms'] = 1e3 * (time.perf_counter() - t_begin)
+        return results
+
     def run(self, jobs, n_total, block_size=128, damping=0.01, bits=4, gather=True):
         """jobs: sequence of (W (K x N, replicated), xs_local (this rank's token batches)[, ready_event]);
         `n_total` is the global token count of every job.  Returns per job (packed, scale, zero, (c0, c1)):
@@ -202,7 +268,11 @@ class ShardedPipeline:
         produced (its slab of columns, or None where it is not the owner)."""
         from . import gptq as G
         from ._lib import lib
+        import time
+        t_begin = time.perf_counter()
         world, rank = self.world, self.rank
+        if self.mode == 'layers' and world > 1:
+            return self._run_layers(list(jobs), block_size, damping, bits, gather)
         owner_mode = self.mode == 'owner' and world > 1
         main = torch.cuda.current_stream()
         start = main.record_event()
@@ -351,6 +421,7 @@ class ShardedPipeline:
                         flat[r].record_stream(self.comm_ag)
         for st in self.hstreams + [self.comm_ar, self.comm_ag] + self.workers:
             main.wait_event(st.record_event())
+        self.stats['host_issue_ms'] = 1e3 * (time.perf_counter() - t_begin)    # everything enqueued, nothing waited for yet
         st_word = 0
         if deferred:
             for w, hw in torch.stack(deferred).tolist():       # (stage status, Hessian status) per job

@@ -57,6 +57,14 @@ def _worker(rank, world, port, q):
             same_pipe = min(same_pipe, float((res[0][0] == ref0).float().mean().item()))
             ok_pipe = ok_pipe and tuple(res[0][0].shape) == (K // 2, N) and tuple(res[1][0].shape) == (K // 2, 320) \
                 and bool(torch.equal(res[0][1], p_full['scale']))
+        # linears (not tokens) sharded: every linear entirely on its owner, from all tokens - the single-GPU bytes
+        pipe = D.ShardedPipeline(streams=2, mode='layers')
+        jobs_full = [(W, [X]), (W[:, :320].contiguous(), [X]), (W[:, 320:].contiguous(), [X])]
+        res = pipe.run(jobs_full, n, block_size=128)
+        torch.cuda.synchronize()
+        Q1, p1 = G.gptq(jobs_full[2][0], [X], block_size=128)
+        ok_pipe = ok_pipe and bool(torch.equal(res[0][0], ref0)) and bool(torch.equal(res[0][1], p_full['scale'])) \
+            and bool(torch.equal(res[2][0], G.pack_matrix(Q1, p1).int_weight)) and tuple(res[1][0].shape) == (K // 2, 320)
         q.put((rank, same, ok_scale, err, tuple(y.shape), same_pipe, ok_pipe))
     finally:
         dist.destroy_process_group()
