@@ -127,7 +127,12 @@ int jgq_gather_rows(const void* src, int64_t rows, int64_t row_bytes, const int6
 /* ---- damping + Cholesky factor of the inverse (gptq.py:44-48, 155-168) ----
  * In: W (K x N fp32, rows of dead features are zeroed in place), H (K x K fp32,
  * destroyed).  Out: L (K x K fp32, lower, L L^T = (H + damp)^-1, upper = 0),
- * *dev_status |= JGQ_STATUS_NOT_PD / JGQ_STATUS_NAN (mirrors any_nan). */
+ * *dev_status |= JGQ_STATUS_NOT_PD / JGQ_STATUS_NAN (mirrors any_nan).
+ * Launch-sequence replay (this entry point and jgq_gptq_quantize): a call whose arguments - pointers, shapes,
+ * scalars - equal those of an earlier call on the same device is recorded into a CUDA graph with stream capture
+ * (second such call) and launched as that graph from then on; the first call always launches kernel by kernel.
+ * Same stream order and results either way.  Not applied on the legacy default stream, inside a caller's own
+ * capture, or with JGQ_GRAPHS=0 in the environment. */
 size_t jgq_damp_invert_workspace_bytes(int64_t K);
 int jgq_damp_invert(float* W, int64_t N, float* H, int64_t K, float damping, float* L,
                     void* ws, size_t ws_bytes, int32_t* dev_status, void* stream);
