@@ -52,5 +52,11 @@ def test_validation_errors_without_gpu(jlib):
     assert lib.jgq_damp_invert_workspace_bytes(768) >= 768 * 768 * 4
     assert lib.jgq_damp_invert(1, 8, 1, 768, 0.01, 1, 256, 16, 1, None) == -3
     assert lib.jgq_hessian_finalize(1, 16, 0.0, None) == -1
+    # activation-order gathers: in-place calls and more rows than a grid dimension holds are refused, empty ones accepted
+    assert lib.jgq_gather_rows(256, 8, 64, 512, 256, None) == -1
+    assert lib.jgq_gather_rows(256, 70000, 64, 512, 1024, None) == -5
+    assert lib.jgq_gather_rows(None, 0, 64, None, None, None) == 0
+    assert lib.jgq_permute_sym(256, 16, 512, 256, None) == -1
+    assert lib.jgq_permute_sym(256, 0, 512, 1024, None) == -1
     with pytest.raises(jlib.JgqError):
         jlib.check(-1)
